@@ -1,0 +1,97 @@
+// Uniform neighbour sampling without replacement over a CSC graph - the GPU stand-in for the
+// `csr_sampling(indptr, indices, seeds, num_pick, replace=False)` operator the reference imports from
+// its (absent) ShmTensor submodule (call sites examples/dataloader.py:174-175,287-288): for every seed,
+// all in-neighbours when it has at most num_pick of them, otherwise num_pick distinct ones, each subset
+// equally likely.  Output is a CSC over the seeds holding GLOBAL neighbour ids.
+//
+// Two launches around a prefix sum the caller owns: `f2c_sample_degrees` writes min(deg, num_pick) per
+// seed, `f2c_sample_neighbors` fills the indices at the offsets of the scanned degrees.  One thread
+// per seed runs Floyd's subset algorithm (num_pick <= 64 draws, chosen positions kept in registers /
+// local memory); draws come from Philox4x32-10 keyed by the caller's seed with the seed node's
+// position as counter, so a sample is reproducible and independent of launch geometry.
+#include "common.cuh"
+
+namespace f2c {
+
+constexpr int kMaxPick = 64;
+
+template <typename IdxT>
+__global__ void __launch_bounds__(256) sample_degrees_kernel(const IdxT* __restrict__ indptr, const IdxT* __restrict__ seeds,
+                                                             IdxT* __restrict__ out_deg, int64_t n_seeds, int num_pick) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n_seeds) return;
+  int64_t v = (int64_t)seeds[i];
+  int64_t d = (int64_t)indptr[v + 1] - (int64_t)indptr[v];
+  out_deg[i] = (IdxT)(d < num_pick ? d : num_pick);
+}
+
+template <typename IdxT>
+__global__ void __launch_bounds__(256) sample_neighbors_kernel(const IdxT* __restrict__ indptr, const IdxT* __restrict__ indices,
+                                                               const IdxT* __restrict__ seeds, const IdxT* __restrict__ out_indptr,
+                                                               IdxT* __restrict__ out_indices, int64_t n_seeds, int num_pick,
+                                                               uint64_t rng_seed, uint64_t rng_offset) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n_seeds) return;
+  const int64_t v = (int64_t)seeds[i];
+  const int64_t begin = (int64_t)indptr[v];
+  const int64_t d = (int64_t)indptr[v + 1] - begin;
+  IdxT* out = out_indices + (int64_t)out_indptr[i];
+  if (d <= num_pick) {
+    for (int64_t t = 0; t < d; ++t) out[t] = indices[begin + t];
+    return;
+  }
+  // Floyd: for j = d-k .. d-1: t = U{0..j}; take t unless already taken, then take j.
+  Philox ph(rng_seed, rng_offset);
+  int64_t chosen[kMaxPick];
+  uint4 r = make_uint4(0, 0, 0, 0);
+  for (int s = 0; s < num_pick; ++s) {
+    if ((s & 1) == 0) r = ph((uint64_t)i * (kMaxPick / 2) + (uint64_t)(s >> 1));
+    const uint64_t bits = (s & 1) == 0 ? ((uint64_t)r.x << 32 | r.y) : ((uint64_t)r.z << 32 | r.w);
+    const int64_t j = d - num_pick + s;
+    // multiply-shift maps 64 random bits to [0, j]; the bias is below 2^-32 for any graph that fits in memory
+    int64_t t = (int64_t)__umul64hi(bits, (uint64_t)(j + 1));
+    bool taken = false;
+    for (int q = 0; q < s; ++q) taken |= chosen[q] == t;
+    chosen[s] = taken ? j : t;
+  }
+  for (int s = 0; s < num_pick; ++s) out[s] = indices[begin + chosen[s]];
+}
+
+}  // namespace f2c
+
+using namespace f2c;
+
+extern "C" int f2c_sample_degrees(const void* indptr, const void* seeds, void* out_deg, int index_dtype, int64_t n_seeds,
+                                  int num_pick, void* stream) {
+  F2C_REQUIRE(is_index_dtype(index_dtype), F2C_ERR_UNSUPPORTED, "sample_degrees: ids must be int32 or int64");
+  F2C_REQUIRE(n_seeds >= 0 && num_pick >= 1 && num_pick <= kMaxPick, F2C_ERR_LIMIT, "sample_degrees: num_pick must be in [1, %d]", kMaxPick);
+  if (n_seeds == 0) return F2C_OK;
+  F2C_REQUIRE(indptr && seeds && out_deg, F2C_ERR_INVALID, "sample_degrees: null pointer");
+  unsigned grid = (unsigned)ceil_div(n_seeds, 256);
+  cudaStream_t st = (cudaStream_t)stream;
+  if (index_dtype == F2C_I32)
+    sample_degrees_kernel<int32_t><<<grid, 256, 0, st>>>((const int32_t*)indptr, (const int32_t*)seeds, (int32_t*)out_deg, n_seeds, num_pick);
+  else
+    sample_degrees_kernel<int64_t><<<grid, 256, 0, st>>>((const int64_t*)indptr, (const int64_t*)seeds, (int64_t*)out_deg, n_seeds, num_pick);
+  return check_launch("sample_degrees");
+}
+
+extern "C" int f2c_sample_neighbors(const void* indptr, const void* indices, const void* seeds, const void* out_indptr,
+                                    void* out_indices, int index_dtype, int64_t n_seeds, int num_pick, uint64_t rng_seed,
+                                    uint64_t rng_offset, void* stream) {
+  F2C_REQUIRE(is_index_dtype(index_dtype), F2C_ERR_UNSUPPORTED, "sample_neighbors: ids must be int32 or int64");
+  F2C_REQUIRE(n_seeds >= 0 && num_pick >= 1 && num_pick <= kMaxPick, F2C_ERR_LIMIT, "sample_neighbors: num_pick must be in [1, %d]", kMaxPick);
+  if (n_seeds == 0) return F2C_OK;
+  F2C_REQUIRE(indptr && seeds && out_indptr, F2C_ERR_INVALID, "sample_neighbors: null pointer");
+  unsigned grid = (unsigned)ceil_div(n_seeds, 256);
+  cudaStream_t st = (cudaStream_t)stream;
+  if (index_dtype == F2C_I32)
+    sample_neighbors_kernel<int32_t><<<grid, 256, 0, st>>>((const int32_t*)indptr, (const int32_t*)indices, (const int32_t*)seeds,
+                                                           (const int32_t*)out_indptr, (int32_t*)out_indices, n_seeds, num_pick,
+                                                           rng_seed, rng_offset);
+  else
+    sample_neighbors_kernel<int64_t><<<grid, 256, 0, st>>>((const int64_t*)indptr, (const int64_t*)indices, (const int64_t*)seeds,
+                                                           (const int64_t*)out_indptr, (int64_t*)out_indices, n_seeds, num_pick,
+                                                           rng_seed, rng_offset);
+  return check_launch("sample_neighbors");
+}

@@ -1,0 +1,108 @@
+// Vector (product) quantisation decode: out[i, j] = codebooks[s][codes[i, s]][j - s*cs], s = j / cs
+// (reference operator vq_decompress, src/vq_quantization.cu:5-60).
+//
+// A pure gather bound by the fp32 output stream (4 B per element against 1/cs code bytes); the
+// codebooks (<= a few hundred KB) are served by L1/L2 through the read-only path.  Each thread
+// emits one float4 when the slice width and feat_dim are multiples of four.  A code outside
+// [0, length) cannot be told from a valid one by the reference (it reads out of bounds); here it is
+// clamped to the last centroid so that a bad table cannot fault the device.
+#include "common.cuh"
+
+namespace f2c {
+
+template <typename CodeT>
+__device__ __forceinline__ uint32_t load_code(const void* codes, int64_t pos, uint32_t length) {
+  int v = (int)reinterpret_cast<const CodeT*>(codes)[pos];
+  uint32_t u = (uint32_t)v;
+  return u < length ? u : length - 1;
+}
+
+__device__ __forceinline__ float4 load_cb4(const float* p) { return __ldg(reinterpret_cast<const float4*>(p)); }
+__device__ __forceinline__ float4 load_cb4(const __half* p) {
+  uint2 raw = __ldg(reinterpret_cast<const uint2*>(p));
+  __half2 a = *reinterpret_cast<__half2*>(&raw.x), b = *reinterpret_cast<__half2*>(&raw.y);
+  float2 fa = __half22float2(a), fb = __half22float2(b);
+  return make_float4(fa.x, fa.y, fb.x, fb.y);
+}
+__device__ __forceinline__ float load_cb1(const float* p) { return __ldg(p); }
+__device__ __forceinline__ float load_cb1(const __half* p) { return __half2float(__ldg(p)); }
+
+template <typename CodeT, typename CbT>
+__global__ void __launch_bounds__(256) vq_decompress_vec_kernel(const void* __restrict__ codes, const CbT* __restrict__ cbs,
+                                                                float* __restrict__ out, int64_t n_vec, int vec_per_row,
+                                                                int n_cb, uint32_t length, int cs, int feat_dim) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n_vec) return;
+  int64_t row = i / vec_per_row;
+  int j = (int)(i % vec_per_row) * 4;
+  int s = j / cs, off = j - s * cs;
+  uint32_t code = load_code<CodeT>(codes, row * n_cb + s, length);
+  float4 v = load_cb4(cbs + ((int64_t)s * length + code) * cs + off);
+  stg_cs_f4(out + row * feat_dim + j, v);
+}
+
+template <typename CodeT, typename CbT>
+__global__ void __launch_bounds__(256) vq_decompress_scalar_kernel(const void* __restrict__ codes, const CbT* __restrict__ cbs,
+                                                                   float* __restrict__ out, int64_t numel, int n_cb,
+                                                                   uint32_t length, int cs, int feat_dim) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= numel) return;
+  int64_t row = i / feat_dim;
+  int j = (int)(i % feat_dim);
+  int s = j / cs, off = j - s * cs;
+  uint32_t code = load_code<CodeT>(codes, row * n_cb + s, length);
+  out[i] = load_cb1(cbs + ((int64_t)s * length + code) * cs + off);
+}
+
+template <typename CodeT, typename CbT>
+static int launch_vq_decompress(const void* codes, const void* cbs, float* out, int64_t rows, int64_t n_cb, int64_t length,
+                                int64_t cs, int64_t D, cudaStream_t st) {
+  int64_t numel = rows * D;
+  if (numel == 0) return F2C_OK;
+  bool vec = cs % 4 == 0 && D % 4 == 0 && aligned(out, 16) && aligned(cbs, 4 * sizeof(CbT));
+  if (vec) {
+    int64_t n_vec = numel / 4;
+    vq_decompress_vec_kernel<CodeT, CbT><<<(unsigned)ceil_div(n_vec, 256), 256, 0, st>>>(
+        codes, (const CbT*)cbs, out, n_vec, (int)(D / 4), (int)n_cb, (uint32_t)length, (int)cs, (int)D);
+  } else {
+    vq_decompress_scalar_kernel<CodeT, CbT><<<(unsigned)ceil_div(numel, 256), 256, 0, st>>>(
+        codes, (const CbT*)cbs, out, numel, (int)n_cb, (uint32_t)length, (int)cs, (int)D);
+  }
+  return check_launch("vq_decompress");
+}
+
+int validate_vq(const char* op, int code_dtype, int64_t n_cb, int64_t length, int64_t cs, int64_t feat_dim) {
+  F2C_REQUIRE(is_code_dtype(code_dtype), F2C_ERR_UNSUPPORTED, "%s: codes must be uint8, int8 or int16", op);
+  F2C_REQUIRE(n_cb >= 1 && length >= 1 && cs >= 1 && feat_dim >= 0, F2C_ERR_INVALID, "%s: bad codebook shape", op);
+  F2C_REQUIRE(feat_dim <= n_cb * cs, F2C_ERR_INVALID, "%s: feat_dim %lld exceeds n_codebooks*column_slice = %lld", op,
+              (long long)feat_dim, (long long)(n_cb * cs));
+  F2C_REQUIRE(feat_dim < (1ll << 24) && length < (1ll << 31) && cs < (1ll << 24) && n_cb < (1ll << 24), F2C_ERR_LIMIT,
+              "%s: shape too large", op);
+  return F2C_OK;
+}
+
+}  // namespace f2c
+
+using namespace f2c;
+
+extern "C" int f2c_vq_decompress(const void* codes, int code_dtype, const void* codebooks, int codebook_dtype, float* out,
+                                 int64_t rows, int64_t n_codebooks, int64_t length, int64_t column_slice,
+                                 int64_t feat_dim, void* stream) {
+  F2C_REQUIRE(rows >= 0, F2C_ERR_INVALID, "vq_decompress: negative size");
+  int rc = validate_vq("vq_decompress", code_dtype, n_codebooks, length, column_slice, feat_dim);
+  if (rc) return rc;
+  F2C_REQUIRE(codebook_dtype == F2C_F32 || codebook_dtype == F2C_F16, F2C_ERR_UNSUPPORTED,
+              "vq_decompress: codebooks must be float32 or float16");
+  F2C_REQUIRE(rows * feat_dim == 0 || (codes && out && codebooks), F2C_ERR_INVALID, "vq_decompress: null pointer");
+  cudaStream_t st = (cudaStream_t)stream;
+#define F2C_VQ(T, C) return launch_vq_decompress<T, C>(codes, codebooks, out, rows, n_codebooks, length, column_slice, feat_dim, st)
+  if (codebook_dtype == F2C_F32) {
+    if (code_dtype == F2C_U8) F2C_VQ(uint8_t, float);
+    if (code_dtype == F2C_I8) F2C_VQ(int8_t, float);
+    F2C_VQ(int16_t, float);
+  }
+  if (code_dtype == F2C_U8) F2C_VQ(uint8_t, __half);
+  if (code_dtype == F2C_I8) F2C_VQ(int8_t, __half);
+  F2C_VQ(int16_t, __half);
+#undef F2C_VQ
+}

@@ -1,0 +1,367 @@
+"""The ``F2CGTLib`` operator surface (gpzlx1/F2CGT src/pybind.cu:7-47) over the B200 C-ABI library.
+
+Same names, positional/keyword arguments and return conventions as the reference's pybind11 module:
+inputs are CUDA tensors that are only borrowed, outputs are fresh tensors on the input's device.
+Differences, all additive:
+  * work is queued on the caller's current CUDA stream (the reference always uses the legacy
+    default stream, e.g. src/fusion_spmm.cu:261);
+  * bad arguments raise ``RuntimeError`` instead of aborting the process (src/common.h:29,51,64,80,102)
+    or reading out of bounds;
+  * operators the reference's callers use but its module does not bind: ``fusion_decompress``
+    (tests/test_fusion_decompress.py:40), ``dropout_inplace`` (src/fusion_dropout.cu:21),
+    ``two_level_decompress_spmm_csr`` and the ``reduce=`` / ``dropout=`` keywords.
+
+torch is used for memory and streams only; every computation is a kernel of libf2cgt_b200.so.
+"""
+import torch
+
+from . import _lib
+from ._lib import lib, check, Epilogue
+
+_DT = {torch.uint8: _lib.U8, torch.int8: _lib.I8, torch.int16: _lib.I16, torch.int32: _lib.I32,
+       torch.int64: _lib.I64, torch.float16: _lib.F16, torch.float32: _lib.F32, torch.float64: _lib.F64}
+_REDUCE = {"mean": _lib.MEAN, "sum": _lib.SUM}
+
+
+def _metric(name):
+    # src/kmeans.cu:107-112: "cosine" selects the cosine distance, any other string the squared L2
+    return _lib.COSINE if name == "cosine" else _lib.L2
+
+
+def _chk(t, name, dtypes=None):
+    if not isinstance(t, torch.Tensor):
+        raise TypeError(f"{name} must be a torch.Tensor")
+    if not t.is_cuda:
+        raise RuntimeError(f"{name} must be a CUDA tensor")
+    if not t.is_contiguous():
+        raise RuntimeError(f"{name} must be contiguous")
+    if dtypes is not None and t.dtype not in dtypes:
+        raise RuntimeError(f"{name} has unsupported dtype {t.dtype}")
+    return t
+
+
+def _stream(t):
+    return torch.cuda.current_stream(t.device).cuda_stream
+
+
+def _ptr(t):
+    return t.data_ptr() if t is not None else 0
+
+
+class _on:
+    """Make the tensor's device current for the duration of a call (kernels launch on it)."""
+
+    def __init__(self, t):
+        self.g = torch.cuda.device(t.device)
+
+    def __enter__(self):
+        self.g.__enter__()
+
+    def __exit__(self, *a):
+        return self.g.__exit__(*a)
+
+
+def _epilogue(dropout):
+    """dropout = None or dict(p=..., seed=..., offset=0, training=True, scale=False)."""
+    if dropout is None:
+        return None
+    return Epilogue(float(dropout["p"]), int(dropout.get("training", True)), int(dropout.get("scale", False)),
+                    int(dropout.get("seed", 0)) & 0xFFFFFFFFFFFFFFFF, int(dropout.get("offset", 0)))
+
+
+# ------------------------------------------------------------------ bit packing
+def packbits(unpack, target_bits):
+    """src/packbits.cu:44-64.  unpack uint8 [rows, dim] -> uint8 [rows, ceil(dim*bits/8)]."""
+    _chk(unpack, "unpack", (torch.uint8,))
+    if unpack.dim() != 2:
+        raise RuntimeError("unpack must be 2-D")
+    if target_bits not in (1, 2, 4):
+        raise RuntimeError(f"TARGET_BITS can only be [1,2,4] for packbits (got {target_bits})")
+    per = 8 // target_bits
+    rows, dim = unpack.shape
+    pack = torch.empty((rows, (dim + per - 1) // per), dtype=torch.uint8, device=unpack.device)
+    with _on(unpack):
+        check(lib.f2c_packbits(_ptr(unpack), _ptr(pack), rows, dim, target_bits, _stream(unpack)))
+    return pack
+
+
+def unpackbits(pack, target_bits, unpack_dim):
+    """src/packbits.cu:97-114."""
+    _chk(pack, "pack", (torch.uint8, torch.int8))
+    if pack.dim() != 2:
+        raise RuntimeError("pack must be 2-D")
+    unpack = torch.empty((pack.shape[0], unpack_dim), dtype=torch.uint8, device=pack.device)
+    with _on(pack):
+        check(lib.f2c_unpackbits(_ptr(pack), _ptr(unpack), pack.shape[0], pack.shape[1], unpack_dim, target_bits,
+                                 _stream(pack)))
+    return unpack
+
+
+# ------------------------------------------------------------------ scalar quantisation
+def sq_compress(src, codebooks, target_bits, column_slice):
+    """src/sq_quantization.cu:65-83.  Returns float32 codes with the shape of ``src``; the caller casts
+    (``.to(uint8)`` + packbits, ``.to(int8)`` or ``.to(int16)``, examples/process_compress.py:131-139)."""
+    _chk(src, "src", (torch.float32,))
+    _chk(codebooks, "codebooks", (torch.float32,))
+    if src.dim() != 2 or codebooks.dim() != 2 or codebooks.shape[1] != 5:
+        raise RuntimeError("src must be [rows, feat_dim] and codebooks [n, 5]")
+    out = torch.empty_like(src)
+    with _on(src):
+        check(lib.f2c_sq_compress(_ptr(src), _ptr(out), _ptr(codebooks), codebooks.shape[0], src.shape[0], src.shape[1],
+                                  target_bits, column_slice, _stream(src)))
+    return out
+
+
+def sq_decompress(compress_data, codebooks, target_bits, column_slice, feat_dim):
+    """src/sq_quantization.cu:158-182.  Codes [rows, src_dim] -> float32 [rows, feat_dim]."""
+    _chk(compress_data, "compress_data", (torch.uint8, torch.int8, torch.int16))
+    _chk(codebooks, "codebooks", (torch.float32,))
+    if compress_data.dim() != 2:
+        raise RuntimeError("compress_data must be 2-D")
+    rows, src_dim = compress_data.shape
+    out = torch.empty((rows, feat_dim), dtype=torch.float32, device=compress_data.device)
+    with _on(compress_data):
+        check(lib.f2c_sq_decompress(_ptr(compress_data), _DT[compress_data.dtype], _ptr(codebooks), codebooks.shape[0],
+                                    _ptr(out), rows, src_dim, feat_dim, target_bits, column_slice, _stream(compress_data)))
+    return out
+
+
+# ------------------------------------------------------------------ vector quantisation
+def vq_decompress(index_tensor, codebooks, feat_dim):
+    """src/vq_quantization.cu:35-60.  Codes [rows, n_cb], codebooks [n_cb, K, cs] (fp32/fp16) -> fp32."""
+    _chk(index_tensor, "index_tensor", (torch.uint8, torch.int8, torch.int16))
+    _chk(codebooks, "codebooks", (torch.float32, torch.float16))
+    if index_tensor.dim() != 2 or codebooks.dim() != 3 or index_tensor.shape[1] != codebooks.shape[0]:
+        raise RuntimeError("index_tensor must be [rows, n_codebooks] and codebooks [n_codebooks, length, column_slice]")
+    rows = index_tensor.shape[0]
+    n_cb, K, cs = codebooks.shape
+    out = torch.empty((rows, feat_dim), dtype=torch.float32, device=index_tensor.device)
+    with _on(index_tensor):
+        check(lib.f2c_vq_decompress(_ptr(index_tensor), _DT[index_tensor.dtype], _ptr(codebooks), _DT[codebooks.dtype],
+                                    _ptr(out), rows, n_cb, K, cs, feat_dim, _stream(index_tensor)))
+    return out
+
+
+# ------------------------------------------------------------------ aggregation
+def _csc(indptr, indices):
+    _chk(indptr, "indptr", (torch.int32, torch.int64))
+    _chk(indices, "indices", (torch.int32, torch.int64))
+    if indptr.dtype != indices.dtype:
+        raise RuntimeError("indptr and indices must have the same dtype")
+    if indptr.dim() != 1 or indptr.numel() < 1:
+        raise RuntimeError("indptr must be 1-D with at least one element")
+    return indptr.numel() - 1
+
+
+def spmm_csr(feat, indptr, indices, reduce="mean"):
+    """src/fusion_spmm.cu:45-70.  Mean of neighbour rows; output has the dtype of ``feat``."""
+    _chk(feat, "feat", (torch.float32, torch.float16, torch.float64))
+    n_dst = _csc(indptr, indices)
+    if feat.dim() != 2:
+        raise RuntimeError("feat must be 2-D")
+    out = torch.empty((n_dst, feat.shape[1]), dtype=feat.dtype, device=feat.device)
+    with _on(feat):
+        check(lib.f2c_spmm_csr(_ptr(feat), _DT[feat.dtype], _ptr(indptr), _ptr(indices), _DT[indptr.dtype], _ptr(out), n_dst,
+                               feat.shape[1], _REDUCE[reduce], _stream(feat)))
+    return out
+
+
+def sq_decompress_spmm_csr(compress_feat, codebooks, indptr, indices, target_bit, column_slice, feat_dim, reduce="mean",
+                           dropout=None):
+    """src/fusion_spmm.cu:240-272.  Fused SQ decode + mean aggregation -> float32 [n_dst, feat_dim]."""
+    _chk(compress_feat, "compress_feat", (torch.uint8, torch.int8, torch.int16))
+    _chk(codebooks, "codebooks", (torch.float32,))
+    n_dst = _csc(indptr, indices)
+    if compress_feat.dim() != 2:
+        raise RuntimeError("compress_feat must be 2-D")
+    out = torch.empty((n_dst, feat_dim), dtype=torch.float32, device=compress_feat.device)
+    ep = _epilogue(dropout)
+    with _on(compress_feat):
+        check(lib.f2c_sq_spmm_csr(_ptr(compress_feat), _DT[compress_feat.dtype], _ptr(codebooks), codebooks.shape[0],
+                                  _ptr(indptr), _ptr(indices), _DT[indptr.dtype], _ptr(out), n_dst, compress_feat.shape[1],
+                                  feat_dim, target_bit, column_slice, _REDUCE[reduce], ep, _stream(compress_feat)))
+    return out
+
+
+def vq_decompress_spmm_csr(compress_feat, codebooks, indptr, indices, feat_dim, reduce="mean", dropout=None):
+    """src/fusion_spmm.cu:107-141.  Fused VQ decode + mean aggregation -> float32 [n_dst, feat_dim]."""
+    _chk(compress_feat, "compress_feat", (torch.uint8, torch.int8, torch.int16))
+    _chk(codebooks, "codebooks", (torch.float32,))
+    n_dst = _csc(indptr, indices)
+    if compress_feat.dim() != 2 or codebooks.dim() != 3 or compress_feat.shape[1] != codebooks.shape[0]:
+        raise RuntimeError("compress_feat must be [rows, n_codebooks] and codebooks [n_codebooks, length, column_slice]")
+    n_cb, K, cs = codebooks.shape
+    out = torch.empty((n_dst, feat_dim), dtype=torch.float32, device=compress_feat.device)
+    ep = _epilogue(dropout)
+    with _on(compress_feat):
+        check(lib.f2c_vq_spmm_csr(_ptr(compress_feat), _DT[compress_feat.dtype], _ptr(codebooks), _ptr(indptr), _ptr(indices),
+                                  _DT[indptr.dtype], _ptr(out), n_dst, n_cb, K, cs, feat_dim, _REDUCE[reduce], ep,
+                                  _stream(compress_feat)))
+    return out
+
+
+def fusion_decompress(sq_data, sq_codebooks, target_bits, column_slice, vq_data, vq_codebooks, feat_dim):
+    """cat(sq_decompress(sq_data, ...), vq_decompress(vq_data, ...)) in one launch
+    (tests/test_fusion_decompress.py:32-43)."""
+    _chk(sq_data, "sq_data", (torch.uint8, torch.int8, torch.int16))
+    _chk(sq_codebooks, "sq_codebooks", (torch.float32,))
+    _chk(vq_data, "vq_data", (torch.uint8, torch.int8, torch.int16))
+    _chk(vq_codebooks, "vq_codebooks", (torch.float32,))
+    n_cb, K, cs = vq_codebooks.shape
+    out = torch.empty((sq_data.shape[0] + vq_data.shape[0], feat_dim), dtype=torch.float32, device=sq_data.device)
+    with _on(sq_data):
+        check(lib.f2c_hybrid_decompress(_ptr(sq_data), _DT[sq_data.dtype], _ptr(sq_codebooks), sq_codebooks.shape[0],
+                                        target_bits, column_slice, sq_data.shape[0], sq_data.shape[1], _ptr(vq_data),
+                                        _DT[vq_data.dtype], _ptr(vq_codebooks), vq_data.shape[0], n_cb, K, cs, _ptr(out),
+                                        feat_dim, _stream(sq_data)))
+    return out
+
+
+def two_level_decompress_spmm_csr(sq_data, sq_codebooks, target_bits, column_slice, vq_data, vq_codebooks, slot, indptr,
+                                  indices, feat_dim, reduce="mean", dropout=None):
+    """Two-level aggregation in one launch.  Source row s is decoded from row ``slot[s]`` of the SQ table
+    when ``slot[s] >= 0`` (int32), from row s of the VQ table otherwise; then the reference mean."""
+    _chk(sq_data, "sq_data", (torch.uint8, torch.int8, torch.int16))
+    _chk(sq_codebooks, "sq_codebooks", (torch.float32,))
+    _chk(vq_data, "vq_data", (torch.uint8, torch.int8, torch.int16))
+    _chk(vq_codebooks, "vq_codebooks", (torch.float32,))
+    _chk(slot, "slot", (torch.int32,))
+    n_dst = _csc(indptr, indices)
+    n_cb, K, cs = vq_codebooks.shape
+    out = torch.empty((n_dst, feat_dim), dtype=torch.float32, device=vq_data.device)
+    ep = _epilogue(dropout)
+    with _on(vq_data):
+        check(lib.f2c_hybrid_spmm_csr(_ptr(sq_data), _DT[sq_data.dtype], _ptr(sq_codebooks), sq_codebooks.shape[0],
+                                      target_bits, column_slice, sq_data.shape[1], _ptr(vq_data), _DT[vq_data.dtype],
+                                      _ptr(vq_codebooks), n_cb, K, cs, _ptr(slot), _ptr(indptr), _ptr(indices),
+                                      _DT[indptr.dtype], _ptr(out), n_dst, feat_dim, _REDUCE[reduce], ep, _stream(vq_data)))
+    return out
+
+
+# ------------------------------------------------------------------ dropout
+def dropout_inplace(output, p, is_training, seed=None, offset=0, scale=False):
+    """src/fusion_dropout.cu:21-29: zero with probability p when training, survivors unchanged
+    (``scale=True`` multiplies them by 1/(1-p)); returns its argument.  ``seed=None`` draws a seed from
+    torch's generator (the reference seeds from the wall clock)."""
+    _chk(output, "output", (torch.float32,))
+    if seed is None:
+        seed = int(torch.randint(0, 2**62, (1,)).item())
+    with _on(output):
+        check(lib.f2c_dropout(_ptr(output), output.numel(), float(p), int(bool(is_training)), seed & 0xFFFFFFFFFFFFFFFF,
+                              int(offset), int(bool(scale)), _stream(output)))
+    return output
+
+
+# ------------------------------------------------------------------ k-means
+def pairwise_distance(x, y, metric):
+    """src/kmeans.cu:102-118.  x [n,d], y [k,d] fp32 -> [n,k] squared-L2 or cosine distance."""
+    _chk(x, "x", (torch.float32,))
+    _chk(y, "y", (torch.float32,))
+    if x.dim() != 2 or y.dim() != 2 or x.shape[1] != y.shape[1]:
+        raise RuntimeError("x must be [n, d] and y [k, d]")
+    dist = torch.empty((x.shape[0], y.shape[0]), dtype=torch.float32, device=x.device)
+    with _on(x):
+        check(lib.f2c_pairwise_distance(_ptr(x), _ptr(y), _ptr(dist), x.shape[0], y.shape[0], x.shape[1], _metric(metric),
+                                        _stream(x)))
+    return dist
+
+
+def kmeans_assign(x, centers, metric):
+    """labels[i] = first argmin_c dist(x_i, centers_c), int64 (src/kmeans.cu:77-98)."""
+    _chk(x, "data", (torch.float32,))
+    _chk(centers, "centers", (torch.float32,))
+    if x.dim() != 2 or centers.dim() != 2 or x.shape[1] != centers.shape[1]:
+        raise RuntimeError("data must be [n, d] and centers [k, d]")
+    n, d = x.shape
+    k = centers.shape[0]
+    labels = torch.empty((n,), dtype=torch.int64, device=x.device)
+    ws_bytes = lib.f2c_kmeans_assign_workspace(n, k, d)
+    ws = torch.empty((ws_bytes,), dtype=torch.uint8, device=x.device) if ws_bytes > 0 else None
+    with _on(x):
+        check(lib.f2c_kmeans_assign(_ptr(x), _ptr(centers), _ptr(labels), n, k, d, _metric(metric), _ptr(ws) if ws is not None else 0,
+                                    _stream(x)))
+    return labels
+
+
+class KMeans:
+    """src/pybind.cu:29-47 / src/kmeans.cu:13-100.  ``KMeans(n_cluster, feat_dim, metric, ...)`` or
+    ``KMeans(centers, metric, ...)``; the second form aliases ``centers`` (src/kmeans.cu:55) and
+    ``get_centers()`` returns that alias (:100)."""
+
+    _DEFAULTS = dict(max_iter=300, tol=1e-4, n_init=1, oversampling_factor=2.0, batch_samples=1 << 15,
+                     batch_centroids=0, inertia_check=False)
+
+    def __init__(self, *args, **kw):
+        from_centers = (len(args) > 0 and isinstance(args[0], torch.Tensor)) or "centers" in kw
+        names = (["centers", "metric"] if from_centers else ["n_cluster", "feat_dim", "metric"]) + list(self._DEFAULTS)
+        if len(args) > len(names):
+            raise TypeError("KMeans(): too many positional arguments")
+        params = dict(self._DEFAULTS)
+        params.update(zip(names, args))
+        for name, v in kw.items():
+            if name not in names or name in names[:len(args)]:
+                raise TypeError(f"KMeans(): unexpected or repeated argument '{name}'")
+            params[name] = v
+        missing = [n for n in names if n not in params]
+        if missing:
+            raise TypeError(f"KMeans(): missing arguments {missing}")
+        self.metric = params["metric"]
+        self.max_iter, self.tol, self.n_init = int(params["max_iter"]), float(params["tol"]), int(params["n_init"])
+        if from_centers:
+            c = params["centers"]
+            if not c.is_cuda:
+                raise RuntimeError("centers must be a CUDA tensor")
+            self.cluster_centers = c
+            self.init = "array"
+        else:
+            self.cluster_centers = torch.zeros((int(params["n_cluster"]), int(params["feat_dim"])), dtype=torch.float32,
+                                               device="cuda")
+            # src/kmeans.cu:16-22: cosine -> random initial centres, otherwise k-means++
+            self.init = "random" if self.metric == "cosine" else "kmeans++"
+        self.num_clusters = self.cluster_centers.shape[0]
+
+    def fit(self, data):
+        from .kmeans_fit import lloyd_fit
+        if not data.is_cuda:
+            raise RuntimeError("x must be a CUDA tensor")
+        centers = lloyd_fit(data.float().contiguous(), self.num_clusters, self.metric, self.init,
+                            self.cluster_centers if self.init == "array" else None, self.max_iter, self.tol, self.n_init)
+        self.cluster_centers.copy_(centers)
+
+    def predict(self, data, normalize_weights=True):
+        if not data.is_cuda:
+            raise RuntimeError("x must be a CUDA tensor")
+        return kmeans_assign(data.contiguous(), self.cluster_centers.contiguous(), self.metric)
+
+    def get_centers(self):
+        return self.cluster_centers
+
+
+def set_tuning(key, value):
+    """Experiment knob of the fused SQ kernel: key in {"vec", "inflight", "lut", "ctas_per_sm"}."""
+    check(lib.f2c_set_tuning({"vec": 0, "inflight": 1, "lut": 2, "ctas_per_sm": 3}[key], int(value)))
+
+
+# ------------------------------------------------------------------ neighbour sampling
+def csr_sampling(indptr, indices, seeds, num_pick, replace=False, rng_seed=0, rng_offset=0):
+    """The reference's ``ShmTensorLib.csr_sampling(indptr, indices, seeds, num_pick, replace)`` (call sites
+    examples/dataloader.py:174-175,287-288): uniform sampling of at most ``num_pick`` in-neighbours per seed
+    without replacement.  Returns ``(sub_indptr, sub_indices)``, a CSC over the seeds with global ids."""
+    if replace:
+        raise RuntimeError("csr_sampling: only replace=False is implemented (the reference never passes True)")
+    _chk(indptr, "indptr", (torch.int32, torch.int64))
+    _chk(indices, "indices", (indptr.dtype,))
+    _chk(seeds, "seeds", (indptr.dtype,))
+    n = seeds.numel()
+    deg = torch.empty((n,), dtype=indptr.dtype, device=indptr.device)
+    st = _stream(indptr)
+    with _on(indptr):
+        check(lib.f2c_sample_degrees(_ptr(indptr), _ptr(seeds), _ptr(deg), _DT[indptr.dtype], n, int(num_pick), st))
+        sub_indptr = torch.zeros((n + 1,), dtype=indptr.dtype, device=indptr.device)
+        torch.cumsum(deg, 0, out=sub_indptr[1:])
+        nnz = int(sub_indptr[-1].item()) if n > 0 else 0
+        sub_indices = torch.empty((nnz,), dtype=indptr.dtype, device=indptr.device)
+        check(lib.f2c_sample_neighbors(_ptr(indptr), _ptr(indices), _ptr(seeds), _ptr(sub_indptr), _ptr(sub_indices),
+                                       _DT[indptr.dtype], n, int(num_pick), int(rng_seed) & 0xFFFFFFFFFFFFFFFF,
+                                       int(rng_offset), st))
+    return sub_indptr, sub_indices

@@ -1,0 +1,170 @@
+/* f2cgt_b200 - C ABI of the B200 (sm_100a) implementation of F2CGT's compressed-feature hot path.
+ *
+ * This is the drop-in boundary: one `extern "C"` entry point per operator that the reference
+ * (gpzlx1/F2CGT) exposes through its pybind11 module `F2CGTLib` (src/pybind.cu:7-47), plus the
+ * operators its callers need that it does not bind.  The Python module `F2CGTLib` shipped with this
+ * library is a thin ctypes shim over these functions.
+ *
+ * Conventions (all entry points):
+ *   - every pointer is a DEVICE pointer unless the parameter name ends in `_host`;
+ *   - tensors are dense row-major ("contiguous" in torch terms); sizes are in elements;
+ *   - the library allocates nothing that outlives a call and never synchronises the device; work
+ *     is queued on `stream` (a cudaStream_t passed as void*; NULL = the legacy default stream,
+ *     which is what the reference launches on, e.g. src/fusion_spmm.cu:261);
+ *   - the return value is a status (F2C_OK = 0); on failure `f2c_last_error()` returns a message
+ *     for the calling thread.  The reference aborts the process on a bad dtype
+ *     (src/common.h:29,51,64,80,102) and checks nothing else; this library validates and returns;
+ *   - index tensors (`indptr`, `indices`) share one dtype, int32 or int64 (the reference also
+ *     instantiates int8/uint8/int16 indices, src/common.h:39-57, which no caller uses);
+ *   - code tensors are uint8 / int8 / int16 (src/common.h:68-82).  Packed widths (1, 2, 4 bits)
+ *     are raw bytes whatever the dtype says (src/sq_quantization.cu:131-132).
+ */
+#ifndef F2CGT_B200_H_
+#define F2CGT_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum {
+  F2C_U8 = 0, F2C_I8 = 1, F2C_I16 = 2, F2C_I32 = 3, F2C_I64 = 4, F2C_F16 = 5, F2C_F32 = 6, F2C_F64 = 7
+} f2c_dtype;
+
+typedef enum { F2C_MEAN = 0, F2C_SUM = 1 } f2c_reduce;   /* the reference only has mean */
+typedef enum { F2C_L2 = 0, F2C_COSINE = 1 } f2c_metric;  /* src/kmeans.cu:16-22,107-112 */
+
+typedef enum {
+  F2C_OK = 0,
+  F2C_ERR_INVALID = 1,      /* bad argument (null pointer, negative size, inconsistent shapes) */
+  F2C_ERR_UNSUPPORTED = 2,  /* dtype / bit width / size outside what the library implements */
+  F2C_ERR_CUDA = 3,         /* a CUDA runtime call or launch failed */
+  F2C_ERR_LIMIT = 4         /* a stated size limit of the entry point was exceeded */
+} f2c_status;
+
+/* Optional epilogue fused into the aggregation kernels: dropout on the aggregated output.
+ * Equivalent to calling f2c_dropout on the output with the same arguments.  NULL = no epilogue. */
+typedef struct {
+  float p;          /* drop probability */
+  int training;     /* 0 = identity */
+  int scale;        /* 0 = survivors unchanged (reference, src/fusion_dropout.cu:16); 1 = times 1/(1-p) */
+  uint64_t seed;    /* Philox key */
+  uint64_t offset;  /* Philox stream offset (counter words 2,3) */
+} f2c_epilogue;
+
+const char* f2c_last_error(void);
+int f2c_version(void);
+
+/* packbits(unpack, target_bits)  -  src/packbits.cu:44-64 (kernel :6-42).
+ * unpack [rows, unpack_dim] u8 -> pack [rows, ceil(unpack_dim*bits/8)] u8; bits in {1,2,4}. */
+int f2c_packbits(const uint8_t* unpack, uint8_t* pack, int64_t rows, int64_t unpack_dim, int bits,
+                 void* stream);
+
+/* unpackbits(pack, target_bits, unpack_dim)  -  src/packbits.cu:97-114 (kernel :66-95). */
+int f2c_unpackbits(const uint8_t* pack, uint8_t* unpack, int64_t rows, int64_t pack_dim, int64_t unpack_dim,
+                   int bits, void* stream);
+
+/* sq_compress(src, codebooks, target_bits, column_slice)  -  src/sq_quantization.cu:65-83 (kernel
+ * :5-63).  src [rows, feat_dim] f32 -> dst [rows, feat_dim] f32 holding integer-valued codes;
+ * codebooks [n_codebooks, 5] f32 rows [fmin,fmax,emin,emax,mean]; bits in {1,2,4,8,16}. */
+int f2c_sq_compress(const float* src, float* dst, const float* codebooks, int64_t n_codebooks, int64_t rows,
+                    int64_t feat_dim, int bits, int64_t column_slice, void* stream);
+
+/* sq_decompress(compress_data, codebooks, target_bits, column_slice, feat_dim)  -
+ * src/sq_quantization.cu:158-182 (kernel :85-156).  codes [rows, src_dim] -> out [rows, feat_dim] f32. */
+int f2c_sq_decompress(const void* codes, int code_dtype, const float* codebooks, int64_t n_codebooks,
+                      float* out, int64_t rows, int64_t src_dim, int64_t feat_dim, int bits,
+                      int64_t column_slice, void* stream);
+
+/* vq_decompress(index_tensor, codebooks, feat_dim)  -  src/vq_quantization.cu:35-60 (kernel :5-33).
+ * codes [rows, n_codebooks]; codebooks [n_codebooks, length, column_slice] f32 or f16 -> out f32. */
+int f2c_vq_decompress(const void* codes, int code_dtype, const void* codebooks, int codebook_dtype,
+                      float* out, int64_t rows, int64_t n_codebooks, int64_t length, int64_t column_slice,
+                      int64_t feat_dim, void* stream);
+
+/* spmm_csr(feat, indptr, indices)  -  src/fusion_spmm.cu:45-70 (kernel :13-43).  Mean (or sum) of
+ * neighbour rows over a CSC block.  feat [n_src, feat_dim] f32/f16/f64 -> out [n_dst, feat_dim], same dtype. */
+int f2c_spmm_csr(const void* feat, int feat_dtype, const void* indptr, const void* indices, int index_dtype,
+                 void* out, int64_t n_dst, int64_t feat_dim, int reduce, void* stream);
+
+/* sq_decompress_spmm_csr(compress_feat, codebooks, indptr, indices, target_bit, column_slice, feat_dim)
+ *  -  src/fusion_spmm.cu:240-272 (kernel :143-238).  out [n_dst, feat_dim] f32; the decoded rows are
+ * never written to memory.  n_src = number of rows of `codes` (used only by f2c_check_csc). */
+int f2c_sq_spmm_csr(const void* codes, int code_dtype, const float* codebooks, int64_t n_codebooks,
+                    const void* indptr, const void* indices, int index_dtype, float* out, int64_t n_dst,
+                    int64_t src_dim, int64_t feat_dim, int bits, int64_t column_slice, int reduce,
+                    const f2c_epilogue* epilogue, void* stream);
+
+/* vq_decompress_spmm_csr(compress_feat, codebooks, indptr, indices, feat_dim)  -
+ * src/fusion_spmm.cu:107-141 (kernel :72-105).  codebooks f32 only (as in the reference, :124-134). */
+int f2c_vq_spmm_csr(const void* codes, int code_dtype, const float* codebooks, const void* indptr,
+                    const void* indices, int index_dtype, float* out, int64_t n_dst, int64_t n_codebooks,
+                    int64_t length, int64_t column_slice, int64_t feat_dim, int reduce,
+                    const f2c_epilogue* epilogue, void* stream);
+
+/* fusion_decompress(sq_data, sq_codebooks, bits, column_slice, vq_data, vq_codebooks, feat_dim)  -
+ * the operator tests/test_fusion_decompress.py:40-42 calls and defines as
+ * cat(sq_decompress(sq_data), vq_decompress(vq_data)); the reference's src/ no longer has it.
+ * out [sq_rows + vq_rows, feat_dim] f32, one launch. */
+int f2c_hybrid_decompress(const void* sq_codes, int sq_dtype, const float* sq_codebooks, int64_t sq_n_codebooks,
+                          int bits, int64_t sq_column_slice, int64_t sq_rows, int64_t sq_src_dim,
+                          const void* vq_codes, int vq_dtype, const float* vq_codebooks, int64_t vq_rows,
+                          int64_t vq_n_codebooks, int64_t length, int64_t vq_column_slice, float* out,
+                          int64_t feat_dim, void* stream);
+
+/* Two-level aggregation in ONE launch (no counterpart kernel in the reference, which aggregates the
+ * level-2 table only: examples/conv.py:56-66, examples/compress.py:58-61).  Source row s is decoded
+ * from row slot[s] of the SQ table when slot[s] >= 0 and from row s of the VQ table otherwise;
+ * value = reference decode of that codec, aggregation = reference mean (src/fusion_spmm.cu:24-42). */
+int f2c_hybrid_spmm_csr(const void* sq_codes, int sq_dtype, const float* sq_codebooks, int64_t sq_n_codebooks,
+                        int bits, int64_t sq_column_slice, int64_t sq_src_dim, const void* vq_codes,
+                        int vq_dtype, const float* vq_codebooks, int64_t vq_n_codebooks, int64_t length,
+                        int64_t vq_column_slice, const int32_t* slot, const void* indptr, const void* indices,
+                        int index_dtype, float* out, int64_t n_dst, int64_t feat_dim, int reduce,
+                        const f2c_epilogue* epilogue, void* stream);
+
+/* dropout_inplace(output, p, is_training)  -  src/fusion_dropout.cu:21-29 (kernel :6-19), which the
+ * reference defines but never binds.  Counter-based (Philox4x32-10) instead of a time-seeded
+ * per-thread XORWOW state, so a (seed, offset) pair reproduces the mask. */
+int f2c_dropout(float* x, int64_t numel, float p, int training, uint64_t seed, uint64_t offset, int scale,
+                void* stream);
+
+/* pairwise_distance(x, y, metric)  -  src/kmeans.cu:102-118 (RAFT call :114-116).
+ * x [n, d], y [k, d] f32 -> dist [n, k] f32: squared L2 or cosine distance (1 - cos). */
+int f2c_pairwise_distance(const float* x, const float* y, float* dist, int64_t n, int64_t k, int64_t d,
+                          int metric, void* stream);
+
+/* KMeans.predict(data)  -  src/kmeans.cu:77-98 (RAFT kmeans_predict :93-95).  labels[i] = first
+ * argmin over centres of the metric above; labels are int64 as in the reference (:79-81).
+ * workspace: NULL, or a device buffer of f2c_kmeans_assign_workspace(n, k, d) bytes. */
+int64_t f2c_kmeans_assign_workspace(int64_t n, int64_t k, int64_t d);
+int f2c_kmeans_assign(const float* x, const float* centers, int64_t* labels, int64_t n, int64_t k, int64_t d,
+                      int metric, void* workspace, void* stream);
+
+/* Debug helper (no counterpart: the reference never checks that indices < compress_feat.size(0)).
+ * Writes 0 to *flag_device if indptr is non-decreasing from 0.. and every index is in [0, n_src),
+ * else a non-zero code.  Asynchronous; the caller reads the flag. */
+/* Experiment knobs of the fused SQ kernel (no counterpart in the reference).  key 0: bytes per lane per
+ * row load (4/8/16), 1: row loads in flight (4/8), 2: table decode on/off, 3: CTAs per SM.
+ * value 0 (key 2: -1) restores the built-in choice. */
+int f2c_set_tuning(int key, int value);
+
+int f2c_check_csc(const void* indptr, const void* indices, int index_dtype, int64_t n_dst, int64_t n_src,
+                  int32_t* flag_device, void* stream);
+
+/* csr_sampling(indptr, indices, seeds, num_pick, replace=False) of the reference's absent ShmTensor
+ * submodule (call sites examples/dataloader.py:174-175,287-288): uniform neighbour sampling without
+ * replacement.  Step 1 writes out_deg[i] = min(in_degree(seeds[i]), num_pick); the caller builds
+ * out_indptr as the exclusive prefix sum of out_deg; step 2 writes the sampled GLOBAL neighbour ids of
+ * seed i at out_indices[out_indptr[i] ...].  All id tensors share index_dtype.  num_pick <= 64. */
+int f2c_sample_degrees(const void* indptr, const void* seeds, void* out_deg, int index_dtype, int64_t n_seeds,
+                       int num_pick, void* stream);
+int f2c_sample_neighbors(const void* indptr, const void* indices, const void* seeds, const void* out_indptr,
+                         void* out_indices, int index_dtype, int64_t n_seeds, int num_pick, uint64_t rng_seed,
+                         uint64_t rng_offset, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* F2CGT_B200_H_ */

@@ -1,0 +1,243 @@
+"""GPU parity: the aggregation kernels (plain, fused SQ, fused VQ, two-level) against the oracle, the
+reference-kernel fixtures and the reference's own property fused == decode-then-aggregate."""
+import numpy as np
+import pytest
+
+from helpers import AGG_ATOL, AGG_RTOL, SQ_MAX_ULP, random_csc, sq_table, ulp_diff
+
+pytestmark = pytest.mark.gpu
+torch = pytest.importorskip("torch")
+
+
+def dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def host(t):
+    torch.cuda.synchronize()
+    return t.cpu().numpy()
+
+
+def close_to_oracle(got, want64):
+    """The tolerance named for aggregated outputs (fp32, any summation order)."""
+    return np.allclose(got, want64, rtol=AGG_RTOL, atol=AGG_ATOL)
+
+
+@pytest.mark.parametrize("dtype", [np.float32, np.float64, np.float16])
+@pytest.mark.parametrize("idx", [np.int64, np.int32])
+@pytest.mark.parametrize("D", [1, 100, 128, 260])
+def test_spmm_csr_bit_exact(capi, oracle, dtype, idx, D):
+    rng = np.random.default_rng(D)
+    feat = rng.standard_normal((70, D)).astype(dtype)
+    indptr, indices = random_csc(rng, 45, 70, max_deg=40, dtype=idx)
+    for reduce in ("mean", "sum"):
+        got = host(capi.spmm_csr(dev(feat), dev(indptr), dev(indices), reduce=reduce))
+        want = oracle.spmm_csr(feat, indptr, indices, reduce)
+        assert got.dtype == dtype and np.array_equal(got, want)
+
+
+def test_spmm_golden_and_toy(capi, golden):
+    feat, indptr, indices = dev(golden["spmm_feat"]), dev(golden["csc_indptr"]), dev(golden["csc_indices"])
+    assert np.array_equal(host(capi.spmm_csr(feat, indptr, indices)), golden["spmm_f32"])
+    assert np.array_equal(host(capi.spmm_csr(feat, indptr.int(), indices.int())), golden["spmm_f32_i32"])
+    if "spmm_f64" in golden:
+        assert np.array_equal(host(capi.spmm_csr(feat.double(), indptr, indices)), golden["spmm_f64"])
+    if "spmm_f16" in golden:
+        assert np.array_equal(host(capi.spmm_csr(feat.half(), indptr, indices)), golden["spmm_f16"])
+
+
+SQ_SHAPES = [  # (D, column_slice): vector paths, ragged widths, several codebook rows, per-column rows
+    (128, 128), (128, 32), (128, 16), (100, 100), (110, 56), (256, 256), (256, 64), (64, 64), (32, 8), (128, 8), (520, 520)]
+
+
+@pytest.mark.parametrize("bits", [1, 2, 4, 8, 16])
+@pytest.mark.parametrize("D,cs", SQ_SHAPES)
+def test_fused_sq_equals_unfused_and_oracle(capi, oracle, bits, D, cs):
+    rng = np.random.default_rng(bits * 1000 + D + cs)
+    n_src, n_dst = 300, 157
+    _, cb, stored = sq_table(oracle, rng, n_src, D, bits, cs)
+    for idx in (np.int64, np.int32):
+        indptr, indices = random_csc(rng, n_dst, n_src, max_deg=20, dtype=idx)
+        t_codes, t_cb, t_ip, t_ix = dev(stored), dev(cb), dev(indptr), dev(indices)
+        for reduce in ("mean", "sum"):
+            fused = capi.sq_decompress_spmm_csr(t_codes, t_cb, t_ip, t_ix, bits, cs, D, reduce=reduce)
+            unfused = capi.spmm_csr(capi.sq_decompress(t_codes, t_cb, bits, cs, D), t_ip, t_ix, reduce=reduce)
+            # the reference's own test: torch.equal (tests/test_fusion_decompress_spmm.py:120)
+            assert torch.equal(fused, unfused), (bits, D, cs, idx, reduce)
+            want = oracle.sq_decompress_spmm_csr(stored, cb, indptr, indices, bits, cs, D, reduce, acc64=True)
+            assert close_to_oracle(host(fused), want)
+    # production tables are int8 views of packed bytes
+    if bits < 8:
+        again = capi.sq_decompress_spmm_csr(t_codes.view(torch.int8), t_cb, t_ip, t_ix, bits, cs, D, reduce="sum")
+        assert torch.equal(again, fused)
+
+
+@pytest.mark.parametrize("bits", [2, 4, 8])
+def test_fused_sq_every_tuning_variant_is_bit_identical(capi, oracle, bits):
+    rng = np.random.default_rng(bits)
+    _, cb, stored = sq_table(oracle, rng, 400, 128, bits, 64)
+    indptr, indices = random_csc(rng, 333, 400, max_deg=25)
+    args = (dev(stored), dev(cb), dev(indptr), dev(indices), bits, 64, 128)
+    from f2cgt_b200 import ops
+    base = capi.sq_decompress_spmm_csr(*args)
+    try:
+        for vec in (4, 8, 16):
+            for inflight in (4, 8):
+                for lut in (0, 1):
+                    ops.set_tuning("vec", vec), ops.set_tuning("inflight", inflight), ops.set_tuning("lut", lut)
+                    assert torch.equal(capi.sq_decompress_spmm_csr(*args), base), (vec, inflight, lut)
+    finally:
+        ops.set_tuning("vec", 0), ops.set_tuning("inflight", 0), ops.set_tuning("lut", -1)
+
+
+def test_fused_sq_golden_reference_kernels(capi, golden):
+    ip, ix = dev(golden["csc_indptr"]), dev(golden["csc_indices"])
+    toy_ip = torch.tensor([0, 1, 3, 6], dtype=torch.int64, device="cuda")
+    toy_ix = torch.tensor([0, 1, 1, 2, 2, 0], dtype=torch.int64, device="cuda")
+    for bits in (1, 2, 4, 8, 16):
+        got = host(capi.sq_decompress_spmm_csr(dev(golden[f"sq_stored_b{bits}"]), dev(golden["sq_cb"]), ip, ix, bits, 100, 100))
+        assert np.array_equal(got.view(np.uint32), golden[f"sq_spmm_b{bits}"].view(np.uint32)), bits
+        got = host(capi.sq_decompress_spmm_csr(dev(golden[f"sq_stored_b{bits}"]), dev(golden["sq_cb"]), toy_ip, toy_ix, bits, 100, 100))
+        assert np.array_equal(got.view(np.uint32), golden[f"sq_spmm_toy_b{bits}"].view(np.uint32)), bits
+        got = host(capi.sq_decompress_spmm_csr(dev(golden[f"sq2_stored_b{bits}"]), dev(golden["sq2_cb"]), ip, ix, bits, 64, 128))
+        assert np.array_equal(got.view(np.uint32), golden[f"sq2_spmm_b{bits}"].view(np.uint32)), bits
+
+
+VQ_SHAPES = [  # (n_cb, K, cs, D)
+    (16, 256, 8, 128), (4, 256, 32, 128), (4, 256, 64, 256), (2, 256, 60, 110), (3, 100, 5, 13), (1, 16, 128, 128),
+    (2, 1000, 64, 128), (8, 256, 64, 512)]
+
+
+@pytest.mark.parametrize("code_dtype", [np.uint8, np.int16])
+@pytest.mark.parametrize("n_cb,K,cs,D", VQ_SHAPES)
+def test_fused_vq_equals_unfused_and_oracle(capi, oracle, code_dtype, n_cb, K, cs, D):
+    if code_dtype == np.uint8 and K > 256:
+        pytest.skip("uint8 codes address at most 256 centroids")
+    rng = np.random.default_rng(n_cb * 31 + cs)
+    n_src, n_dst = 300, 157
+    cbs = rng.standard_normal((n_cb, K, cs)).astype(np.float32)
+    codes = rng.integers(0, K, (n_src, n_cb)).astype(code_dtype)
+    for idx in (np.int64, np.int32):
+        indptr, indices = random_csc(rng, n_dst, n_src, max_deg=40, dtype=idx)
+        t = (dev(codes), dev(cbs), dev(indptr), dev(indices))
+        for reduce in ("mean", "sum"):
+            fused = capi.vq_decompress_spmm_csr(*t, D, reduce=reduce)
+            unfused = capi.spmm_csr(capi.vq_decompress(t[0], t[1], D), t[2], t[3], reduce=reduce)
+            assert torch.equal(fused, unfused), (n_cb, K, cs, D, idx, reduce)  # tests/test_fusion_decompress_spmm.py:33
+            assert np.array_equal(host(fused), oracle.vq_decompress_spmm_csr(codes, cbs, indptr, indices, D, reduce))
+
+
+def test_fused_vq_golden_reference_kernels(capi, golden):
+    ip, ix = dev(golden["csc_indptr"]), dev(golden["csc_indices"])
+    got = host(capi.vq_decompress_spmm_csr(dev(golden["vq_codes_u8"]), dev(golden["vq_cbs"]), ip, ix, 110))
+    assert np.array_equal(got, golden["vq_spmm_u8"])
+    got = host(capi.vq_decompress_spmm_csr(dev(golden["vq16_codes"]), dev(golden["vq16_cbs"]), ip, ix, 128))
+    assert np.array_equal(got, golden["vq16_spmm"])
+
+
+@pytest.mark.parametrize("bits", [1, 2, 4, 8, 16])
+@pytest.mark.parametrize("D,n_cb,cs", [(128, 4, 32), (256, 4, 64), (128, 16, 8)])
+def test_two_level_is_composition(capi, oracle, bits, D, n_cb, cs):
+    rng = np.random.default_rng(bits * 17 + D)
+    n_src, n_hot, n_dst = 500, 60, 211
+    _, cb, sq = sq_table(oracle, rng, n_hot, D, bits, D)
+    cbs = rng.standard_normal((n_cb, 256, cs)).astype(np.float32)
+    codes = rng.integers(0, 256, (n_src, n_cb)).astype(np.uint8)
+    slot = np.full(n_src, -1, np.int32)
+    hot = rng.choice(n_src, n_hot, replace=False)
+    slot[hot] = rng.permutation(n_hot).astype(np.int32)
+    for idx in (np.int64, np.int32):
+        indptr, indices = random_csc(rng, n_dst, n_src, max_deg=40, dtype=idx)
+        got = capi.two_level_decompress_spmm_csr(dev(sq), dev(cb), bits, D, dev(codes), dev(cbs), dev(slot), dev(indptr),
+                                                 dev(indices), D)
+        # composition on the GPU: decode all rows by their own codec, then the plain mean - must be bit-equal
+        full = capi.vq_decompress(dev(codes), dev(cbs), D)
+        full[dev(hot)] = capi.sq_decompress(dev(sq), dev(cb), bits, D, D)[dev(slot[hot].astype(np.int64))]
+        assert torch.equal(got, capi.spmm_csr(full, dev(indptr), dev(indices)))
+        want = oracle.two_level_decompress_spmm_csr(sq, cb, bits, D, codes, cbs, slot, indptr, indices, D, acc64=True)
+        assert close_to_oracle(host(got), want)
+    # all-cold and all-hot degenerate to the single-codec kernels
+    cold = capi.two_level_decompress_spmm_csr(dev(sq), dev(cb), bits, D, dev(codes), dev(cbs), dev(np.full(n_src, -1, np.int32)),
+                                              dev(indptr), dev(indices), D)
+    assert torch.equal(cold, capi.vq_decompress_spmm_csr(dev(codes), dev(cbs), dev(indptr), dev(indices), D))
+
+
+@pytest.mark.parametrize("kind", ["sq", "vq", "two_level"])
+def test_fused_dropout_equals_dropout_after(capi, oracle, kind):
+    rng = np.random.default_rng(99)
+    D, n_src, n_dst = 128, 300, 200
+    indptr, indices = random_csc(rng, n_dst, n_src)
+    ip, ix = dev(indptr), dev(indices)
+    drop = dict(p=0.5, seed=77, offset=5, training=True)
+    cbs = dev(rng.standard_normal((4, 256, 32)).astype(np.float32))
+    codes = dev(rng.integers(0, 256, (n_src, 4)).astype(np.uint8))
+    _, cb, sq = sq_table(oracle, rng, n_src, D, 4, 128)
+    if kind == "sq":
+        plain = capi.sq_decompress_spmm_csr(dev(sq), dev(cb), ip, ix, 4, 128, D)
+        fused = capi.sq_decompress_spmm_csr(dev(sq), dev(cb), ip, ix, 4, 128, D, dropout=drop)
+    elif kind == "vq":
+        plain = capi.vq_decompress_spmm_csr(codes, cbs, ip, ix, D)
+        fused = capi.vq_decompress_spmm_csr(codes, cbs, ip, ix, D, dropout=drop)
+    else:
+        slot = dev(np.where(rng.random(n_src) < 0.3, np.arange(n_src), -1).astype(np.int32))
+        plain = capi.two_level_decompress_spmm_csr(dev(sq), dev(cb), 4, 128, codes, cbs, slot, ip, ix, D)
+        fused = capi.two_level_decompress_spmm_csr(dev(sq), dev(cb), 4, 128, codes, cbs, slot, ip, ix, D, dropout=drop)
+    after = capi.dropout_inplace(plain.clone(), 0.5, True, seed=77, offset=5)
+    assert torch.equal(fused, after)
+    assert 0.4 < float((fused == 0).float().mean()) < 0.62
+    assert np.array_equal(host(after), oracle.dropout(host(plain), 0.5, True, 77, 5))
+
+
+def test_config1_sq8_block(capi, oracle):
+    """The CPU-runnable configuration: 100,000 x 128 N(0,1) features, 8-bit codes, 10,000 destination
+    rows with exactly 12 uniform neighbours, int64 CSC, seed 0."""
+    rng = np.random.default_rng(0)
+    x, cb, stored = sq_table(oracle, rng, 100_000, 128, 8, 128)
+    indptr = np.arange(0, 120_001, 12, dtype=np.int64)
+    indices = rng.integers(0, 100_000, 120_000).astype(np.int64)
+    got = host(capi.sq_decompress_spmm_csr(dev(stored), dev(cb), dev(indptr), dev(indices), 8, 128, 128))
+    want = oracle.sq_decompress_spmm_csr(stored, cb, indptr, indices, 8, 128, 128, acc64=True)
+    assert got.shape == (10_000, 128) and close_to_oracle(got, want)
+    # per-column codebooks (column_slice = 1)
+    cb1 = oracle.sq_codebooks(x[:20000], 1)
+    st1 = oracle.sq_codes_to_storage(oracle.sq_compress(x[:20000], cb1, 8, 1), 8)
+    ix1 = indices[:24000] % 20000
+    got1 = host(capi.sq_decompress_spmm_csr(dev(st1), dev(cb1), dev(indptr[:2001]), dev(ix1), 8, 1, 128))
+    assert close_to_oracle(got1, oracle.sq_decompress_spmm_csr(st1, cb1, indptr[:2001], ix1, 8, 1, 128, acc64=True))
+
+
+def test_empty_and_degenerate_blocks(capi):
+    cb = torch.tensor([[0.01, 3.0, -6.6, 1.6, 0.8]], device="cuda")
+    codes = torch.zeros((5, 64), dtype=torch.uint8, device="cuda")
+    # no destination rows
+    out = capi.sq_decompress_spmm_csr(codes, cb, torch.zeros(1, dtype=torch.int64, device="cuda"),
+                                      torch.zeros(0, dtype=torch.int64, device="cuda"), 4, 128, 128)
+    assert out.shape == (0, 128)
+    # destination rows without any edge -> zeros
+    out = capi.sq_decompress_spmm_csr(codes, cb, torch.zeros(8, dtype=torch.int64, device="cuda"),
+                                      torch.zeros(0, dtype=torch.int64, device="cuda"), 4, 128, 128)
+    assert out.shape == (7, 128) and float(out.abs().max()) == 0.0
+    cbs = torch.randn(4, 256, 32, device="cuda")
+    out = capi.vq_decompress_spmm_csr(torch.zeros((5, 4), dtype=torch.uint8, device="cuda"), cbs,
+                                      torch.zeros(8, dtype=torch.int32, device="cuda"),
+                                      torch.zeros(0, dtype=torch.int32, device="cuda"), 128)
+    assert out.shape == (7, 128) and float(out.abs().max()) == 0.0
+    with pytest.raises(RuntimeError):  # mixed index dtypes
+        capi.vq_decompress_spmm_csr(torch.zeros((5, 4), dtype=torch.uint8, device="cuda"), cbs,
+                                    torch.zeros(8, dtype=torch.int32, device="cuda"),
+                                    torch.zeros(0, dtype=torch.int64, device="cuda"), 128)
+
+
+def test_runs_on_the_callers_stream(capi):
+    # the reference launches on the legacy stream; this library must honour torch's current stream
+    s = torch.cuda.Stream()
+    cbs = torch.randn(4, 256, 32, device="cuda")
+    codes = torch.randint(0, 256, (1000, 4), dtype=torch.uint8, device="cuda")
+    ip = torch.arange(0, 1201, 12, dtype=torch.int64, device="cuda")
+    ix = torch.randint(0, 1000, (1200,), dtype=torch.int64, device="cuda")
+    want = capi.vq_decompress_spmm_csr(codes, cbs, ip, ix, 128)
+    torch.cuda.synchronize()
+    with torch.cuda.stream(s):
+        got = capi.vq_decompress_spmm_csr(codes, cbs, ip, ix, 128)
+    s.synchronize()
+    assert torch.equal(got, want)

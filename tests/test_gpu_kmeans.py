@@ -1,0 +1,81 @@
+"""GPU parity: pairwise distance and k-means assignment against the oracle (the reference's torch
+restatement, examples/my_kmeans.py:43-64,116-125, evaluated in double)."""
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+torch = pytest.importorskip("torch")
+
+
+def dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def labels_match(oracle, x, c, metric, got):
+    """Identical assignments, ignoring ties: where the label differs from the oracle's, the chosen
+    centre must be as close as the best one up to fp32 rounding of the distance."""
+    want, best, second = oracle.kmeans_assign(x, c, metric, with_margin=True)
+    diff = np.nonzero(got != want)[0]
+    if diff.size == 0:
+        return True
+    d = oracle.pairwise_distance(x[diff], c, metric).astype(np.float64)
+    chosen = d[np.arange(diff.size), got[diff]]
+    scale = np.maximum(np.abs(best[diff]), 1e-30) if metric != "cosine" else 1.0
+    ok = np.abs(chosen - best[diff]) <= 4e-6 * scale + 1e-7
+    return bool(ok.all()) and diff.size <= max(3, x.shape[0] // 2000)
+
+
+@pytest.mark.parametrize("metric", ["l2", "cosine"])
+@pytest.mark.parametrize("n,k,d", [(1000, 256, 8), (777, 256, 32), (513, 256, 64), (300, 17, 5), (64, 300, 100), (50, 40, 200), (1, 1, 1)])
+def test_pairwise_distance(capi, oracle, metric, n, k, d):
+    rng = np.random.default_rng(n + k + d)
+    x = rng.standard_normal((n, d)).astype(np.float32)
+    c = rng.standard_normal((k, d)).astype(np.float32)
+    got = capi.pairwise_distance(dev(x), dev(c), metric).cpu().numpy()
+    want = oracle.pairwise_distance(x, c, metric)
+    assert got.shape == (n, k)
+    assert np.allclose(got, want, rtol=2e-5, atol=2e-6)
+
+
+@pytest.mark.parametrize("metric", ["l2", "cosine"])
+@pytest.mark.parametrize("n,k,d", [(20000, 256, 8), (9999, 256, 32), (5000, 256, 64), (3000, 17, 5), (700, 300, 100), (300, 40, 200)])
+def test_kmeans_assign_identical_up_to_ties(capi, oracle, metric, n, k, d):
+    rng = np.random.default_rng(n + k + d + 1)
+    x = rng.standard_normal((n, d)).astype(np.float32)
+    c = rng.standard_normal((k, d)).astype(np.float32)
+    km = capi.KMeans(dev(c), metric)
+    got = km.predict(dev(x)).cpu().numpy()
+    assert got.dtype == np.int64 and got.shape == (n,)
+    assert labels_match(oracle, x, c, metric, got)
+    assert km.get_centers().data_ptr() == km.cluster_centers.data_ptr()
+
+
+def test_kmeans_exact_ties_take_first_centre(capi):
+    c = torch.randn(8, 16, device="cuda")
+    c2 = torch.cat([c, c])  # every centre duplicated: the first copy must win
+    x = torch.randn(500, 16, device="cuda")
+    for metric in ("l2", "cosine"):
+        lab = capi.KMeans(c2, metric).predict(x)
+        assert int(lab.max()) < 8
+
+
+def test_kmeans_zero_vectors_and_fit(capi):
+    x = torch.randn(4000, 8, device="cuda")
+    x[:5] = 0
+    c = torch.randn(16, 8, device="cuda")
+    d = capi.pairwise_distance(x, c, "cosine")
+    assert torch.all(d[:5] == 1.0)  # NaN distances count as 1 (examples/my_kmeans.py:92-94)
+    torch.manual_seed(0)
+    for metric in ("l2", "cosine"):
+        km = capi.KMeans(16, 8, metric, max_iter=30)
+        km.fit(x)
+        centers = km.get_centers()
+        assert centers.shape == (16, 8) and bool(torch.isfinite(centers).all())
+        lab = km.predict(x)
+        # a fit must beat random centres on its own objective
+        def inertia(cc, ll):
+            if metric == "cosine":
+                return float((1 - torch.nn.functional.cosine_similarity(x[5:], cc[ll[5:]], dim=1)).sum())
+            return float(((x - cc[ll]) ** 2).sum())
+        rnd = x[torch.randperm(4000, device="cuda")[:16]].contiguous()
+        assert inertia(centers, lab) < inertia(rnd, capi.KMeans(rnd, metric).predict(x))
