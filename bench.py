@@ -155,6 +155,9 @@ def run_ours(args):
     for s in range(args.steps):
         ip, ix = blocks[s % len(blocks)]
         evs = [torch.cuda.Event(enable_timing=True) for _ in range(len(BITS) + 1)]
+        # park the GPU for ~0.1 ms so that the host has queued the step's launches before the first event
+        # fires: the events then bracket device time only, not the Python launch path
+        torch.cuda._sleep(250_000)
         evs[0].record()
         for j, bits in enumerate(BITS):
             codes, cb = tables[bits]

@@ -86,6 +86,31 @@ __device__ __forceinline__ float sq_scale(float emin, float emax) {
   return (emax - emin) / drange;
 }
 
+// a / b with the IEEE round-to-nearest result of the division operator, given rcp = 1.0f / b computed
+// once per destination row: two Newton corrections through exact FMA residuals (Markstein) replace the
+// ~15-instruction division sequence per element.  Values outside the exponent range where the
+// residuals are exact (and inf/nan) take the ordinary division.
+__device__ __forceinline__ float div_exact(float a, float b, float rcp) {
+  float q = a * rcp;
+  float r = fmaf(-q, b, a);
+  q = fmaf(r, rcp, q);
+  r = fmaf(-q, b, a);
+  q = fmaf(r, rcp, q);
+  const float aa = fabsf(a);
+  if (!(aa < 1e30f) || (aa < 1e-30f && aa != 0.0f) || b > 1048576.0f) q = a / b;
+  return q;
+}
+
+// The same quotient without the range check, for callers that know |a| is 0 or well inside the normal range
+// and b is a small integer.
+__device__ __forceinline__ float div_exact_fast(float a, float b, float rcp) {
+  float q = a * rcp;
+  float r = fmaf(-q, b, a);
+  q = fmaf(r, rcp, q);
+  r = fmaf(-q, b, a);
+  return fmaf(r, rcp, q);
+}
+
 // Philox4x32-10 (Salmon et al., SC'11).  One call yields four 32-bit words for counter ctr.
 struct Philox {
   uint32_t k0, k1, o0, o1;

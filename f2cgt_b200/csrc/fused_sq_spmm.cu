@@ -32,7 +32,7 @@ int validate_sq(const char* op, int code_dtype, int64_t n_codebooks, int64_t src
                 int64_t column_slice);
 
 // tuning knobs (0 = heuristic); set through f2c_set_tuning for experiments
-int g_tune_vec = 0, g_tune_u = 0, g_tune_lut = -1, g_tune_ctas_per_sm = 0;
+int g_tune_vec = 0, g_tune_u = 0, g_tune_lut = -1, g_tune_ctas_per_sm = 0, g_tune_ablate = 0, g_tune_layout = 0;
 
 template <int VEC> struct VecLoad;
 template <> struct VecLoad<4> {
@@ -51,13 +51,6 @@ template <> struct VecLoad<16> {
 enum { DEC_ARITH = 0, DEC_LUT = 1 };
 enum { CODE_U8 = 0, CODE_I8 = 1, CODE_I16 = 2 };
 
-// Number of table copies for a given code width: one per shared-memory bank group of the lookup.
-template <int BITS> struct LutGeom {
-  static constexpr int FLOATS = 8 / BITS;             // floats returned per byte lookup: 1, 2, 4
-  static constexpr int COPIES = 32 / FLOATS;          // 32, 16, 8
-  static constexpr int BYTES = 256 * COPIES * FLOATS * 4;  // 32 KB
-};
-
 struct SqParams {
   const uint8_t* codes;
   const float* codebooks;
@@ -73,13 +66,114 @@ struct SqParams {
   int code_kind;
   int reduce;
   int vec_store;
+  int staged;        // 1: rows leave through the shared-memory staging area (feat_dim % 4 == 0)
+  int stage_offset;  // byte offset of that area in dynamic shared memory
+  int ablate;  // experiment mask: 1 skip accumulate, 2 skip epilogue, 4 skip table build, 8 skip row loads
   DropoutArgs drop;
 };
 
+// Decode table geometry.  Every width <= 8 bits is decoded a whole code byte at a time: entry `byte`
+// is a 256-byte slab holding the 8/BITS floats the byte encodes, replicated once per shared-memory
+// bank group (so lookups of a warp never collide), which makes the table 64 KB.  Because the slab
+// stride is 256 bytes, the byte offset of a lookup is (byte << 8) | lane_offset and is formed by ONE
+// byte-permute of the data word - no shift/mask/add chain per code.
+template <int BITS> struct Lut {
+  static constexpr int B = (BITS == 1 || BITS == 2 || BITS == 4) ? BITS : 8;
+  static constexpr int FLOATS = 8 / B;                    // floats per byte: 8, 4, 2, 1
+  static constexpr int COPY_BYTES = FLOATS >= 4 ? 16 : FLOATS * 4;  // one vector read per copy (two for 1-bit)
+  static constexpr int HALVES = FLOATS == 8 ? 2 : 1;      // 1-bit: floats 0-3 and 4-7 live 128 bytes apart
+  static constexpr int COPIES = 256 / (COPY_BYTES * HALVES) > 32 ? 32 : 256 / (COPY_BYTES * HALVES);  // 8, 16, 32, 32
+  static constexpr int NCODE = 1 << B;
+  static constexpr int TABLE_BYTES = 256 * 256;
+  __device__ static __forceinline__ uint32_t lane_offset(int lane) { return (uint32_t)(lane & (COPIES - 1)) * COPY_BYTES; }
+  // byte offset of float f of (byte, copy)
+  __device__ static __forceinline__ uint32_t offset(int byte, int copy, int f) {
+    return (uint32_t)byte * 256u + (uint32_t)(f / 4) * (HALVES == 2 ? 128u : 0u) + (uint32_t)copy * COPY_BYTES + (uint32_t)(f % 4) * 4u;
+  }
+};
+
+// Two independent fp32 additions in one issue slot (sm_100 packed add; each half rounds to nearest
+// exactly like a scalar add, so results do not change).
+__device__ __forceinline__ void add2(float& a0, float& a1, float b0, float b1) {
+  asm("{\n\t.reg .b64 ra, rb;\n\tmov.b64 ra, {%0, %1};\n\tmov.b64 rb, {%2, %3};\n\tadd.rn.f32x2 ra, ra, rb;\n\tmov.b64 {%0, %1}, ra;\n\t}"
+      : "+f"(a0), "+f"(a1) : "f"(b0), "f"(b1));
+}
+
+// Shared-memory reads by 32-bit shared-window address (keeps the address arithmetic to one add).
+__device__ __forceinline__ float lds_f32(uint32_t a) { float v; asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(a)); return v; }
+__device__ __forceinline__ float2 lds_f32x2(uint32_t a) {
+  float2 v; asm volatile("ld.shared.v2.f32 {%0, %1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(a)); return v;
+}
+__device__ __forceinline__ float4 lds_f32x4(uint32_t a) {
+  float4 v; asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(a)); return v;
+}
+
+// Add the decoded elements of one lane's share of a neighbour row to its accumulators.
+// `table` is the shared-window address of the decode table (DEC_LUT).
+template <int BITS, int VEC, int DEC>
+__device__ __forceinline__ void sq_accumulate(float (&acc)[BITS == 16 ? VEC / 2 : VEC * 8 / BITS], const VecLoad<VEC>& data,
+                                              uint32_t table, uint32_t lane_off, int code_kind, float scale,
+                                              float emin, float mean) {
+  constexpr int NW = VEC / 4;
+#pragma unroll
+  for (int w = 0; w < NW; ++w) {
+    const uint32_t word = data.w[w];
+    if (DEC == DEC_LUT) {
+      using L = Lut<BITS>;
+#pragma unroll
+      for (int b = 0; b < 4; ++b) {
+        // result bytes: [lane_off.b0, word.b_b, lane_off.b2, lane_off.b3]  ==  (byte << 8) | lane_off
+        const uint32_t e = table + __byte_perm(word, lane_off, 0x7604u | (uint32_t)(b << 4));
+        if (L::FLOATS == 1) {
+          acc[w * 4 + b] += lds_f32(e);
+        } else if (L::FLOATS == 2) {
+          float2 v = lds_f32x2(e);
+          add2(acc[w * 8 + 2 * b], acc[w * 8 + 2 * b + 1], v.x, v.y);
+        } else {
+#pragma unroll
+          for (int h = 0; h < L::HALVES; ++h) {
+            float4 v = lds_f32x4(e + 128 * h);
+            const int o = (w * 4 + b) * L::FLOATS + 4 * h;
+            add2(acc[o], acc[o + 1], v.x, v.y);
+            add2(acc[o + 2], acc[o + 3], v.z, v.w);
+          }
+        }
+      }
+    } else if (BITS == 1) {
+      const uint32_t negmean = __float_as_uint(-mean);
+#pragma unroll
+      for (int i = 0; i < 32; ++i) acc[w * 32 + i] += __uint_as_float(negmean ^ ((word << (31 - i)) & 0x80000000u));
+    } else if (BITS == 16) {
+      acc[w * 2 + 0] += sq_decode<BITS>((float)(int16_t)(word & 0xFFFFu), scale, emin, mean);
+      acc[w * 2 + 1] += sq_decode<BITS>((float)(int16_t)(word >> 16), scale, emin, mean);
+    } else if (BITS == 8) {
+#pragma unroll
+      for (int b = 0; b < 4; ++b) {
+        uint32_t byte = (word >> (8 * b)) & 0xFFu;
+        float c = code_kind == CODE_I8 ? (float)(int8_t)byte : (float)byte;
+        acc[w * 4 + b] += sq_decode<BITS>(c, scale, emin, mean);
+      }
+    } else {  // 2- or 4-bit arithmetic decode
+      constexpr int B = (BITS == 2 || BITS == 4) ? BITS : 4;
+      constexpr int PER_WORD = 32 / B;
+#pragma unroll
+      for (int i = 0; i < PER_WORD; ++i)
+        acc[w * PER_WORD + i] += sq_decode<BITS>((float)((word >> (B * i)) & ((1u << B) - 1u)), scale, emin, mean);
+    }
+  }
+}
+
+}  // namespace f2c
+#include "fused_sq_rowwarp.cuh"
+namespace f2c {
+
+// The kernel is software pipelined over the destination rows a lane group visits: while the rows of
+// destination row i are in flight, the neighbour ids of row i+1 and the indptr pair of row i+2 are
+// already being fetched, so a row costs one memory round trip instead of three dependent ones.
+// U = neighbours held in registers per row (rows with more take extra rounds of U).
 template <int BITS, int VEC, int U, typename IdxT, int DEC>
-__global__ void __launch_bounds__(256) sq_spmm_kernel(const SqParams p) {
+__global__ void __launch_bounds__(256, 2) sq_spmm_kernel(const SqParams p) {
   constexpr int EPL = BITS == 16 ? VEC / 2 : VEC * 8 / BITS;  // output columns per lane
-  constexpr int NW = VEC / 4;                                  // 32-bit words per lane per row
   extern __shared__ __align__(16) unsigned char smem_raw[];
 
   const int lane = threadIdx.x & 31;
@@ -98,134 +192,186 @@ __global__ void __launch_bounds__(256) sq_spmm_kernel(const SqParams p) {
   const float emax = __ldg(p.codebooks + cb_row * kCodebookDim + 3);
   const float mean = __ldg(p.codebooks + cb_row * kCodebookDim + 4);
   const float scale = sq_scale<BITS>(emin, emax);
-  (void)scale; (void)mean;
 
+  uint32_t lane_off = 0;
   if (DEC == DEC_LUT) {
-    // table[byte][copy][FLOATS]; copy c serves lanes with lane % COPIES == c, whose lane_g is c % G
-    constexpr int FLOATS = LutGeom<(BITS == 2 || BITS == 4 || BITS == 8) ? BITS : 8>::FLOATS;
-    constexpr int COPIES = 32 / FLOATS;
-    constexpr int B = (BITS == 2 || BITS == 4) ? BITS : 8;
-    float* lut = reinterpret_cast<float*>(smem_raw);
-    for (int i = threadIdx.x; i < 256 * COPIES * FLOATS; i += blockDim.x) {
-      int f = i % FLOATS, copy = (i / FLOATS) % COPIES, byte = i / (FLOATS * COPIES);
-      int row = ((copy & (G - 1)) * EPL) / p.column_slice;
+    // Copy c of a slab serves the lanes with lane % COPIES == c, whose lane_g is c % G.
+    // Phase 1 decodes each code value once per distinct codebook row (2^B * min(G, COPIES) exp2f in all);
+    // phase 2 assembles the byte-indexed, bank-replicated table from those values.
+    using L = Lut<BITS>;
+    float* base = reinterpret_cast<float*>(smem_raw + L::TABLE_BYTES);  // [n_rows][NCODE]
+    const int n_rows = G < L::COPIES ? G : L::COPIES;
+    for (int i = threadIdx.x; i < n_rows * L::NCODE; i += blockDim.x) {
+      int code = i & (L::NCODE - 1), g = i / L::NCODE;
+      int row = (g * EPL) / p.column_slice;
       if (row >= p.n_cb) row = p.n_cb - 1;
       float e0 = __ldg(p.codebooks + row * kCodebookDim + 2), e1 = __ldg(p.codebooks + row * kCodebookDim + 3);
       float m = __ldg(p.codebooks + row * kCodebookDim + 4);
-      float c;
-      if (B == 8) c = p.code_kind == CODE_I8 ? (float)(int8_t)byte : (float)byte;
-      else c = (float)((byte >> (B * f)) & ((1 << B) - 1));
-      lut[i] = sq_decode<BITS>(c, sq_scale<BITS>(e0, e1), e0, m);
+      float c = (L::B == 8 && p.code_kind == CODE_I8) ? (float)(int8_t)code : (float)code;
+      base[i] = sq_decode<BITS>(c, sq_scale<BITS>(e0, e1), e0, m);
     }
     __syncthreads();
+    // one 16-byte store per step: slab `byte`, bytes [16j, 16j+16)
+    constexpr int SPAN = L::HALVES == 2 ? 128 : 256;
+    for (int i = threadIdx.x; i < 256 * 16; i += blockDim.x) {
+      const int byte = i >> 4, j = i & 15;
+      float v[4];
+#pragma unroll
+      for (int t = 0; t < 4; ++t) {
+        const int o = 16 * j + 4 * t;                 // byte offset inside the slab
+        const int h = L::HALVES == 2 ? o / 128 : 0;
+        const int oo = o % SPAN;
+        const int copy = oo / L::COPY_BYTES;
+        const int f = (oo % L::COPY_BYTES) / 4 + 4 * h;
+        const int g = copy & (n_rows - 1);
+        v[t] = copy < L::COPIES ? base[g * L::NCODE + ((byte >> (L::B * f)) & (L::NCODE - 1))] : 0.0f;
+      }
+      *reinterpret_cast<float4*>(smem_raw + i * 16) = make_float4(v[0], v[1], v[2], v[3]);
+    }
+    __syncthreads();
+    lane_off = L::lane_offset(lane);
   }
+  if (DEC == DEC_LUT) lane_off = Lut<BITS>::lane_offset(lane);
+  const uint32_t table = (uint32_t)__cvta_generic_to_shared(smem_raw);
+
+  // Sums of decoded values are either 0 or, in magnitude, between 2^(emin-24) and deg * 2^emax (1 bit: multiples
+  // of ~mean); when that interval is well inside the normal range for every lane of the warp, the mean can use
+  // the division without the per-element range check.
+  const bool div_safe = __all_sync(0xffffffffu, BITS == 1 ? (mean > 1e-20f && mean < 1e20f) : (emin > -80.0f && emax < 80.0f));
 
   const IdxT* __restrict__ indptr = reinterpret_cast<const IdxT*>(p.indptr);
   const IdxT* __restrict__ indices = reinterpret_cast<const IdxT*>(p.indices);
   const int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-  const int64_t n_warps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+  const int64_t stride = (((int64_t)gridDim.x * blockDim.x) >> 5) * rows_per_warp;
   const uint8_t* __restrict__ my_codes = p.codes + byte0;
 
-  for (int64_t row_base = warp * rows_per_warp; row_base < p.n_dst; row_base += n_warps * rows_per_warp) {
-    const int64_t d = row_base + sub;
-    const bool valid = d < p.n_dst && lane_active;
-    int64_t begin = 0, end = 0;
-    if (valid) { begin = (int64_t)indptr[d]; end = (int64_t)indptr[d + 1]; }
-    float acc[EPL];
+  // ---- three-deep software pipeline over the rows d, d+stride, d+2*stride, ... of this lane group:
+  //   while row i is decoded, the code rows of row i+1, the neighbour ids of row i+2 and the indptr pair
+  //   of row i+3 are in flight.  Two register sets (P, P^1) alternate through a 2x unrolled loop so
+  //   that no load result has to be moved - a move would wait for the load and serialise the chain.
+  int64_t d = warp * rows_per_warp + sub;
+  int64_t begA = 0, begB = 0, begC = 0;  // first edge of rows i, i+1, i+2
+  int degA = 0, degB = 0, degC = 0;      // their degrees
+  if (d < p.n_dst && lane_active) { begA = (int64_t)indptr[d]; degA = (int)((int64_t)indptr[d + 1] - begA); }
+  if (d + stride < p.n_dst && lane_active) { begB = (int64_t)indptr[d + stride]; degB = (int)((int64_t)indptr[d + stride + 1] - begB); }
+  if (d + 2 * stride < p.n_dst && lane_active) { begC = (int64_t)indptr[d + 2 * stride]; degC = (int)((int64_t)indptr[d + 2 * stride + 1] - begC); }
+  uint32_t nidx[2][U];
+  VecLoad<VEC> data[2][U];
 #pragma unroll
-    for (int e = 0; e < EPL; ++e) acc[e] = 0.0f;
+  for (int u = 0; u < U; ++u) nidx[0][u] = u < degA ? (uint32_t)indices[begA + u] : 0u;
+#pragma unroll
+  for (int u = 0; u < U; ++u) nidx[1][u] = u < degB ? (uint32_t)indices[begB + u] : 0u;
+#pragma unroll
+  for (int u = 0; u < U; ++u)
+    if (u < degA) data[0][u].load(my_codes + (int64_t)nidx[0][u] * p.row_bytes);
 
-    for (int64_t k = begin; k < end; k += U) {
-      VecLoad<VEC> data[U];
+  for (int64_t row_base = warp * rows_per_warp; row_base < p.n_dst;) {
 #pragma unroll
-      for (int u = 0; u < U; ++u) {
-        if (k + u < end) {
-          int64_t src = (int64_t)indices[k + u];
-          data[u].load(my_codes + src * p.row_bytes);
+    for (int P = 0; P < 2; ++P) {
+      if (row_base < p.n_dst) {  // warp uniform
+        // (1) code rows of the next destination row -> data[P^1]
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+          if (u < degB) data[P ^ 1][u].load(my_codes + (int64_t)nidx[P ^ 1][u] * p.row_bytes);
+        // (2) neighbour ids of the row after it -> nidx[P] (its previous content was consumed one stage ago)
+#pragma unroll
+        for (int u = 0; u < U; ++u) nidx[P][u] = u < degC ? (uint32_t)indices[begC + u] : 0u;
+        // (3) indptr pair three rows ahead
+        int64_t begD = 0;
+        int degD = 0;
+        if (d + 3 * stride < p.n_dst && lane_active) {
+          begD = (int64_t)indptr[d + 3 * stride];
+          degD = (int)((int64_t)indptr[d + 3 * stride + 1] - begD);
         }
-      }
+
+        // (4) decode + accumulate the current row from data[P]
+        float acc[EPL];
 #pragma unroll
-      for (int u = 0; u < U; ++u) {
-        if (k + u < end) {
+        for (int e = 0; e < EPL; ++e) acc[e] = 0.0f;
+        {
 #pragma unroll
-          for (int w = 0; w < NW; ++w) {
-            const uint32_t word = data[u].w[w];
-            if (BITS == 1) {
-              const uint32_t negmean = __float_as_uint(-mean);
+          for (int u = 0; u < U; ++u)
+            if (u < degA) sq_accumulate<BITS, VEC, DEC>(acc, data[P][u], table, lane_off, p.code_kind, scale, emin, mean);
+        }
+        // destination rows with more than U neighbours: further rounds of four, not pipelined
+        for (int k = U; k < degA; k += 4) {
+          VecLoad<VEC> extra[4];
 #pragma unroll
-              for (int i = 0; i < 32; ++i)
-                acc[w * 32 + i] += __uint_as_float(negmean ^ ((word << (31 - i)) & 0x80000000u));
-            } else if (BITS == 16) {
-              acc[w * 2 + 0] += sq_decode<BITS>((float)(int16_t)(word & 0xFFFFu), scale, emin, mean);
-              acc[w * 2 + 1] += sq_decode<BITS>((float)(int16_t)(word >> 16), scale, emin, mean);
-            } else if (DEC == DEC_LUT && BITS == 8) {
-              const float* lut = reinterpret_cast<const float*>(smem_raw) + lane;
+          for (int u = 0; u < 4; ++u)
+            if (k + u < degA) extra[u].load(my_codes + (int64_t)indices[begA + k + u] * p.row_bytes);
 #pragma unroll
-              for (int b = 0; b < 4; ++b) acc[w * 4 + b] += lut[((word >> (8 * b)) & 0xFFu) * 32];
-            } else if (DEC == DEC_LUT && BITS == 4) {
-              const float2* lut = reinterpret_cast<const float2*>(smem_raw) + (lane & 15);
+          for (int u = 0; u < 4; ++u)
+            if (k + u < degA) sq_accumulate<BITS, VEC, DEC>(acc, extra[u], table, lane_off, p.code_kind, scale, emin, mean);
+        }
+
+        // (5) mean / dropout / store
+        {
+          const bool have_row = d < p.n_dst && lane_active;
+          if (p.staged) {
+            // Each lane holds EPL consecutive columns, so direct stores would scatter 16-byte pieces over
+            // 32 different lines per instruction.  Stage the warp's raw sums in shared memory (chunk index
+            // XOR-swizzled so that neither side has bank conflicts), then read them back row by row, apply
+            // the mean / dropout to the one float4 each lane holds, and write whole 512-byte runs.
+            constexpr int Q = EPL / 4;                                    // chunks (float4) per lane
+            constexpr int LQ = Q >= 8 ? 3 : Q == 4 ? 2 : Q == 2 ? 1 : 0;  // low chunk-index bits that only depend on q
+            const int NC = p.feat_dim >> 2;                               // chunks per output row
+            const int NCP = Q << p.logG;                                  // row stride of the staging area (>= NC)
+            float4* stage = reinterpret_cast<float4*>(smem_raw + p.stage_offset) + (threadIdx.x >> 5) * (32 * Q);
+            // chunk c of a row is kept at c ^ m, m = the lane bits that the low bits of c do not already spread
+            // over the banks; m only touches the q part of the index, so a lane stays inside its own Q chunks
+            if (have_row) {
+              const int m = ((lane & 7) >> (3 - LQ)) & ((1 << LQ) - 1);
 #pragma unroll
-              for (int b = 0; b < 4; ++b) {
-                float2 v = lut[((word >> (8 * b)) & 0xFFu) * 16];
-                acc[w * 8 + 2 * b] += v.x;
-                acc[w * 8 + 2 * b + 1] += v.y;
+              for (int q = 0; q < Q; ++q) {
+                const int c4 = lane_g * Q + q;
+                if (c4 < NC) stage[sub * NCP + (c4 ^ m)] = make_float4(acc[4 * q], acc[4 * q + 1], acc[4 * q + 2], acc[4 * q + 3]);
               }
-            } else if (DEC == DEC_LUT && BITS == 2) {
-              const float4* lut = reinterpret_cast<const float4*>(smem_raw) + (lane & 7);
-#pragma unroll
-              for (int b = 0; b < 4; ++b) {
-                float4 v = lut[((word >> (8 * b)) & 0xFFu) * 8];
-                acc[w * 16 + 4 * b] += v.x;
-                acc[w * 16 + 4 * b + 1] += v.y;
-                acc[w * 16 + 4 * b + 2] += v.z;
-                acc[w * 16 + 4 * b + 3] += v.w;
+            }
+            // reciprocal of the row's degree, once per lane group (0 marks "do not divide")
+            float my_rcp = 0.0f;
+            if (p.reduce == F2C_MEAN && degA > 1) my_rcp = 1.0f / (float)degA;
+            __syncwarp();
+            for (int row = 0; row < rows_per_warp; ++row) {
+              const int64_t dr = row_base + row;
+              if (dr >= p.n_dst) break;
+              const float rcp = __shfl_sync(0xffffffffu, my_rcp, row << p.logG);
+              const float deg = (float)__shfl_sync(0xffffffffu, degA, row << p.logG);
+              for (int c = lane; c < NC; c += 32) {
+                const int writer = (row << p.logG) + c / Q;  // lane that produced chunk c
+                const int m = ((writer & 7) >> (3 - LQ)) & ((1 << LQ) - 1);
+                float4 v = stage[row * NCP + (c ^ m)];
+                if (rcp != 0.0f) {
+                  if (div_safe) {
+                    v.x = div_exact_fast(v.x, deg, rcp); v.y = div_exact_fast(v.y, deg, rcp);
+                    v.z = div_exact_fast(v.z, deg, rcp); v.w = div_exact_fast(v.w, deg, rcp);
+                  } else {
+                    v.x = div_exact(v.x, deg, rcp); v.y = div_exact(v.y, deg, rcp);
+                    v.z = div_exact(v.z, deg, rcp); v.w = div_exact(v.w, deg, rcp);
+                  }
+                }
+                if (p.drop.enabled) v = dropout_apply4(v, (uint64_t)(dr * p.feat_dim + 4 * c), p.drop);
+                stg_cs_f4(p.out + dr * p.feat_dim + 4 * c, v);
               }
-            } else if (BITS == 8) {
+            }
+            __syncwarp();
+          } else if (have_row) {
+            float* orow = p.out + d * p.feat_dim;
+            const float deg = degA == 0 ? 1.0f : (float)degA;
 #pragma unroll
-              for (int b = 0; b < 4; ++b) {
-                uint32_t byte = (word >> (8 * b)) & 0xFFu;
-                float c = p.code_kind == CODE_I8 ? (float)(int8_t)byte : (float)byte;
-                acc[w * 4 + b] += sq_decode<BITS>(c, scale, emin, mean);
+            for (int e = 0; e < EPL; ++e) {
+              int col = c0 + e;
+              if (col < p.feat_dim) {
+                float v = p.reduce == F2C_MEAN ? acc[e] / deg : acc[e];
+                if (p.drop.enabled) v = dropout_apply1(v, (uint64_t)(d * p.feat_dim + col), p.drop);
+                orow[col] = v;
               }
-            } else {  // 2- or 4-bit arithmetic decode
-              constexpr int B = (BITS == 2 || BITS == 4) ? BITS : 4;
-              constexpr int PER_WORD = 32 / B;
-#pragma unroll
-              for (int i = 0; i < PER_WORD; ++i)
-                acc[w * PER_WORD + i] += sq_decode<BITS>((float)((word >> (B * i)) & ((1u << B) - 1u)), scale, emin, mean);
             }
           }
         }
-      }
-    }
-
-    if (valid) {
-      const float deg = end - begin == 0 ? 1.0f : (float)(end - begin);
-      float* orow = p.out + d * p.feat_dim;
-      if (p.reduce == F2C_MEAN) {
-#pragma unroll
-        for (int e = 0; e < EPL; ++e) acc[e] = acc[e] / deg;
-      }
-      if (p.vec_store) {
-#pragma unroll
-        for (int q = 0; q < EPL / 4; ++q) {
-          int col = c0 + 4 * q;
-          if (col < p.feat_dim) {  // feat_dim % 4 == 0 here
-            float4 v = make_float4(acc[4 * q], acc[4 * q + 1], acc[4 * q + 2], acc[4 * q + 3]);
-            if (p.drop.enabled) v = dropout_apply4(v, (uint64_t)(d * p.feat_dim + col), p.drop);
-            stg_cs_f4(orow + col, v);
-          }
-        }
-      } else {
-#pragma unroll
-        for (int e = 0; e < EPL; ++e) {
-          int col = c0 + e;
-          if (col < p.feat_dim) {
-            float v = acc[e];
-            if (p.drop.enabled) v = dropout_apply1(v, (uint64_t)(d * p.feat_dim + col), p.drop);
-            orow[col] = v;
-          }
-        }
+        // rotate the (already resident) scalars; the register sets swap through P
+        begA = begB; degA = degB; begB = begC; degB = degC; begC = begD; degC = degD;
+        d += stride;
+        row_base += stride;
       }
     }
   }
@@ -287,11 +433,40 @@ __global__ void __launch_bounds__(256) sq_spmm_generic_kernel(const void* __rest
 static int ilog2(int v) { int l = 0; while ((1 << l) < v) ++l; return l; }
 
 template <int BITS, int VEC, int U, typename IdxT, int DEC>
-static int launch_fast(const SqParams& p, cudaStream_t st) {
+static int launch_fast(SqParams p, cudaStream_t st) {
   auto kern = sq_spmm_kernel<BITS, VEC, U, IdxT, DEC>;
-  size_t smem = DEC == DEC_LUT ? 32768 : 0;  // below the 48 KB that needs no opt-in
+  // table (64 KB) + the decoded code values of each distinct codebook row
+  size_t smem = 0;
+  if (DEC == DEC_LUT) {
+    constexpr int B = (BITS == 1 || BITS == 2 || BITS == 4) ? BITS : 8;
+    constexpr int COPIES = B == 1 ? 8 : B == 2 ? 16 : 32;
+    int n_rows = (1 << p.logG) < COPIES ? (1 << p.logG) : COPIES;
+    smem = 65536 + (size_t)n_rows * (1 << B) * sizeof(float);
+  }
+  // staging area for coalesced output: 8 warps x rows per warp x feat_dim floats
+  p.staged = 0;
+  p.stage_offset = (int)smem;
+  constexpr int EPL = BITS == 16 ? VEC / 2 : VEC * 8 / BITS;
+  size_t stage_bytes = (size_t)8 * 32 * EPL * sizeof(float);  // 8 warps x 32 lanes x EPL floats
+  if (p.vec_store && EPL >= 4 && stage_bytes <= 64 * 1024) {
+    p.staged = 1;
+    smem += stage_bytes;
+  }
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 65536 + 32 * 256 * 4 + 65536);
+    if (e != cudaSuccess) return set_error(F2C_ERR_CUDA, "sq_decompress_spmm_csr: %s", cudaGetErrorString(e));
+  }
   int rows_per_cta = 8 * (32 >> p.logG);
-  int ctas_per_sm = g_tune_ctas_per_sm > 0 ? g_tune_ctas_per_sm : 4;
+  // persistent grid: exactly as many CTAs as the device keeps resident (queried once per variant)
+  static int resident = 0;
+  static size_t resident_smem = ~(size_t)0;
+  if (resident == 0 || resident_smem != smem) {
+    int n = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kern, 256, smem) != cudaSuccess || n < 1) n = 1;
+    resident = n;
+    resident_smem = smem;
+  }
+  int ctas_per_sm = g_tune_ctas_per_sm > 0 ? g_tune_ctas_per_sm : resident;
   int64_t grid = ceil_div(p.n_dst, rows_per_cta);
   if (grid > (int64_t)kSmCount * ctas_per_sm) grid = (int64_t)kSmCount * ctas_per_sm;
   kern<<<(unsigned)grid, 256, smem, st>>>(p);
@@ -300,15 +475,16 @@ static int launch_fast(const SqParams& p, cudaStream_t st) {
 
 template <int BITS, int VEC, typename IdxT, int DEC>
 static int pick_u(const SqParams& p, cudaStream_t st) {
-  int u = g_tune_u > 0 ? g_tune_u : 4;
-  if (u >= 8) return launch_fast<BITS, VEC, 8, IdxT, DEC>(p, st);
-  return launch_fast<BITS, VEC, 4, IdxT, DEC>(p, st);
+  int u = g_tune_u > 0 ? g_tune_u : 12;
+  if (u >= 16) return launch_fast<BITS, VEC, 16, IdxT, DEC>(p, st);
+  if (u >= 12) return launch_fast<BITS, VEC, 12, IdxT, DEC>(p, st);
+  return launch_fast<BITS, VEC, 8, IdxT, DEC>(p, st);
 }
 
 template <int BITS, typename IdxT>
 static int dispatch_fast(const SqParams& p, int vec, bool lut, cudaStream_t st) {
-  constexpr int VMAX = BITS == 1 ? 4 : BITS == 2 ? 8 : 16;  // keeps EPL <= 32 accumulators
-  constexpr bool CAN_LUT = BITS == 2 || BITS == 4 || BITS == 8;
+  constexpr int VMAX = BITS == 1 ? 4 : 8;  // two register sets of U rows: at most two words per row, EPL <= 32
+  constexpr bool CAN_LUT = BITS <= 8;
   if (vec > VMAX) vec = VMAX;
   if constexpr (CAN_LUT) if (lut) {
     if (vec == 16) return pick_u<BITS, VMAX >= 16 ? 16 : VMAX, IdxT, DEC_LUT>(p, st);
@@ -322,19 +498,39 @@ static int dispatch_fast(const SqParams& p, int vec, bool lut, cudaStream_t st) 
 
 template <int BITS, typename IdxT>
 static int launch_sq_spmm(const void* codes, int code_dtype, const float* codebooks, int64_t n_cb, const void* indptr,
-                          const void* indices, float* out, int64_t n_dst, int64_t src_dim, int64_t D, int64_t cs, int reduce,
+                          const void* indices, float* out, int64_t n_dst, int64_t n_src, int64_t src_dim, int64_t D, int64_t cs, int reduce,
                           const DropoutArgs& drop, cudaStream_t st) {
   if (n_dst == 0 || D == 0) return F2C_OK;
   const int code_bytes = dtype_size(code_dtype);
   const int64_t row_bytes = src_dim * code_bytes;
+  const bool natural = BITS < 8 || (BITS == 8 && code_bytes == 1) || (BITS == 16 && code_bytes == 2);
+  // ---- one warp per destination row (default): needs float4-aligned output columns ----
+  {
+    const int load_align = BITS == 16 ? 8 : BITS == 8 ? 4 : BITS == 4 ? 2 : 1;
+    bool ok = natural && n_src < (1ll << 32) && D % 4 == 0 && aligned(out, 16) && aligned(codes, load_align) &&
+              row_bytes % load_align == 0 && (n_cb == 1 || cs % 4 == 0) && g_tune_layout == 2;
+    if (ok) {
+      SqParams p;
+      p.codes = (const uint8_t*)codes; p.codebooks = codebooks; p.indptr = indptr; p.indices = indices; p.out = out;
+      p.n_dst = n_dst; p.row_bytes = row_bytes; p.feat_dim = (int)D; p.column_slice = (int)cs; p.n_cb = (int)n_cb;
+      p.logG = 5; p.code_kind = code_dtype == F2C_I8 ? CODE_I8 : code_dtype == F2C_U8 ? CODE_U8 : CODE_I16;
+      p.reduce = reduce; p.vec_store = 1; p.staged = 0; p.stage_offset = 0; p.drop = drop; p.ablate = g_tune_ablate;
+      // one table per CTA: every lane that shares a table copy must share a codebook row
+      bool lut = BITS <= 8 && g_tune_lut != 0 && (n_cb == 1 || (BITS >= 4 && D <= 128));
+      bool handled = false;
+      int rc = launch_rowwarp<BITS, IdxT>(p, lut, st, &handled);
+      if (handled) return rc;
+    }
+  }
   // ---- can the vector kernel serve this shape? ----
-  constexpr int VMAX = BITS == 1 ? 4 : BITS == 2 ? 8 : 16;
+  constexpr int VMAX = BITS == 1 ? 4 : 8;
   int vec = 0;
   for (int v = VMAX; v >= 4; v >>= 1)
     if (row_bytes % v == 0 && aligned(codes, v) && row_bytes <= 32 * v) { vec = v; break; }
   if (g_tune_vec > 0 && vec > g_tune_vec && row_bytes <= 32 * g_tune_vec) vec = g_tune_vec;
   bool natural_dtype = BITS < 8 || (BITS == 8 && code_bytes == 1) || (BITS == 16 && code_bytes == 2);
-  bool fast = vec != 0 && natural_dtype;
+  // the vector kernel keeps neighbour ids in 32-bit registers
+  bool fast = vec != 0 && natural_dtype && n_src < (1ll << 32);
   int epl = 0, G = 0;
   if (fast) {
     epl = BITS == 16 ? vec / 2 : vec * 8 / BITS;
@@ -347,9 +543,9 @@ static int launch_sq_spmm(const void* codes, int code_dtype, const float* codebo
     p.codes = (const uint8_t*)codes; p.codebooks = codebooks; p.indptr = indptr; p.indices = indices; p.out = out;
     p.n_dst = n_dst; p.row_bytes = row_bytes; p.feat_dim = (int)D; p.column_slice = (int)cs; p.n_cb = (int)n_cb;
     p.logG = ilog2(G); p.code_kind = code_dtype == F2C_I8 ? CODE_I8 : code_dtype == F2C_U8 ? CODE_U8 : CODE_I16;
-    p.reduce = reduce; p.vec_store = D % 4 == 0 && aligned(out, 16); p.drop = drop;
+    p.reduce = reduce; p.vec_store = D % 4 == 0 && aligned(out, 16); p.drop = drop; p.ablate = g_tune_ablate;
     // table copies are shared by lanes l and l + COPIES: they must own the same columns
-    int copies = BITS == 8 ? 32 : BITS == 4 ? 16 : 8;
+    int copies = BITS >= 4 ? 32 : BITS == 2 ? 16 : 8;
     bool lut = (n_cb == 1 || copies % G == 0) && g_tune_lut != 0;
     return dispatch_fast<BITS, IdxT>(p, vec, lut, st);
   }
@@ -370,10 +566,10 @@ using namespace f2c;
 
 extern "C" int f2c_sq_spmm_csr(const void* codes, int code_dtype, const float* codebooks, int64_t n_codebooks,
                                const void* indptr, const void* indices, int index_dtype, float* out, int64_t n_dst,
-                               int64_t src_dim, int64_t feat_dim, int bits, int64_t column_slice, int reduce,
+                               int64_t n_src, int64_t src_dim, int64_t feat_dim, int bits, int64_t column_slice, int reduce,
                                const f2c_epilogue* epilogue, void* stream) {
   const char* op = "sq_decompress_spmm_csr";
-  F2C_REQUIRE(n_dst >= 0, F2C_ERR_INVALID, "%s: negative size", op);
+  F2C_REQUIRE(n_dst >= 0 && n_src >= 0, F2C_ERR_INVALID, "%s: negative size", op);
   int rc = validate_sq(op, code_dtype, n_codebooks, src_dim, feat_dim, bits, column_slice);
   if (rc) return rc;
   F2C_REQUIRE(is_index_dtype(index_dtype), F2C_ERR_UNSUPPORTED, "%s: indptr/indices must be int32 or int64", op);
@@ -388,9 +584,9 @@ extern "C" int f2c_sq_spmm_csr(const void* codes, int code_dtype, const float* c
 #define F2C_SQ(B)                                                                                                   \
   return index_dtype == F2C_I32                                                                                     \
              ? launch_sq_spmm<B, int32_t>(codes, code_dtype, codebooks, n_codebooks, indptr, indices, out, n_dst,   \
-                                          src_dim, feat_dim, column_slice, reduce, drop, st)                       \
+                                          n_src, src_dim, feat_dim, column_slice, reduce, drop, st)                       \
              : launch_sq_spmm<B, int64_t>(codes, code_dtype, codebooks, n_codebooks, indptr, indices, out, n_dst,   \
-                                          src_dim, feat_dim, column_slice, reduce, drop, st)
+                                          n_src, src_dim, feat_dim, column_slice, reduce, drop, st)
   switch (bits) {
     case 1: F2C_SQ(1);
     case 2: F2C_SQ(2);
@@ -410,6 +606,8 @@ extern "C" int f2c_set_tuning(int key, int value) {
     case 1: g_tune_u = value; break;
     case 2: g_tune_lut = value; break;
     case 3: g_tune_ctas_per_sm = value; break;
+    case 4: g_tune_ablate = value; break;
+    case 5: g_tune_layout = value; break;
     default: return set_error(F2C_ERR_INVALID, "set_tuning: unknown key %d", key);
   }
   return F2C_OK;

@@ -178,8 +178,8 @@ def sq_decompress_spmm_csr(compress_feat, codebooks, indptr, indices, target_bit
     ep = _epilogue(dropout)
     with _on(compress_feat):
         check(lib.f2c_sq_spmm_csr(_ptr(compress_feat), _DT[compress_feat.dtype], _ptr(codebooks), codebooks.shape[0],
-                                  _ptr(indptr), _ptr(indices), _DT[indptr.dtype], _ptr(out), n_dst, compress_feat.shape[1],
-                                  feat_dim, target_bit, column_slice, _REDUCE[reduce], ep, _stream(compress_feat)))
+                                  _ptr(indptr), _ptr(indices), _DT[indptr.dtype], _ptr(out), n_dst, compress_feat.shape[0],
+                                  compress_feat.shape[1], feat_dim, target_bit, column_slice, _REDUCE[reduce], ep, _stream(compress_feat)))
     return out
 
 
@@ -339,7 +339,7 @@ class KMeans:
 
 def set_tuning(key, value):
     """Experiment knob of the fused SQ kernel: key in {"vec", "inflight", "lut", "ctas_per_sm"}."""
-    check(lib.f2c_set_tuning({"vec": 0, "inflight": 1, "lut": 2, "ctas_per_sm": 3}[key], int(value)))
+    check(lib.f2c_set_tuning({"vec": 0, "inflight": 1, "lut": 2, "ctas_per_sm": 3, "ablate": 4, "layout": 5}[key], int(value)))
 
 
 # ------------------------------------------------------------------ neighbour sampling

@@ -90,10 +90,11 @@ int f2c_spmm_csr(const void* feat, int feat_dtype, const void* indptr, const voi
 
 /* sq_decompress_spmm_csr(compress_feat, codebooks, indptr, indices, target_bit, column_slice, feat_dim)
  *  -  src/fusion_spmm.cu:240-272 (kernel :143-238).  out [n_dst, feat_dim] f32; the decoded rows are
- * never written to memory.  n_src = number of rows of `codes` (used only by f2c_check_csc). */
+ * never written to memory.  n_src = number of rows of `codes` (compress_feat.size(0)); every index
+ * must be below it (f2c_check_csc verifies that on request). */
 int f2c_sq_spmm_csr(const void* codes, int code_dtype, const float* codebooks, int64_t n_codebooks,
                     const void* indptr, const void* indices, int index_dtype, float* out, int64_t n_dst,
-                    int64_t src_dim, int64_t feat_dim, int bits, int64_t column_slice, int reduce,
+                    int64_t n_src, int64_t src_dim, int64_t feat_dim, int bits, int64_t column_slice, int reduce,
                     const f2c_epilogue* epilogue, void* stream);
 
 /* vq_decompress_spmm_csr(compress_feat, codebooks, indptr, indices, feat_dim)  -

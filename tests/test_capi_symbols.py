@@ -41,7 +41,7 @@ def test_argument_validation_needs_no_gpu():
     assert rc == 2  # packed codes cannot be an int16 tensor
     rc = lib.f2c_sq_decompress(None, _lib.U8, None, 1, None, 4, 16, 128, 4, 128, None)
     assert rc == 1 and b"exceeds" in lib.f2c_last_error()  # 16 bytes hold 32 4-bit elements, not 128
-    rc = lib.f2c_sq_spmm_csr(None, _lib.U8, None, 5, None, None, _lib.I64, None, 4, 64, 128, 4, 31, 0, None, None)
+    rc = lib.f2c_sq_spmm_csr(None, _lib.U8, None, 5, None, None, _lib.I64, None, 4, 9, 64, 128, 4, 31, 0, None, None)
     assert rc == 1 and b"column_slice" in lib.f2c_last_error()
     rc = lib.f2c_vq_spmm_csr(None, _lib.U8, None, None, None, _lib.I16, None, 4, 4, 256, 32, 128, 0, None, None)
     assert rc == 2  # int16 indices
@@ -50,7 +50,7 @@ def test_argument_validation_needs_no_gpu():
     assert lib.f2c_kmeans_assign(None, None, None, 10, 0, 8, 0, None, None) == 1
     # zero-sized work is a no-op, not an error
     assert lib.f2c_packbits(None, None, 0, 8, 4, None) == 0
-    assert lib.f2c_sq_spmm_csr(None, _lib.U8, None, 1, None, None, _lib.I64, None, 0, 64, 128, 4, 128, 0, None, None) == 0
+    assert lib.f2c_sq_spmm_csr(None, _lib.U8, None, 1, None, None, _lib.I64, None, 0, 9, 64, 128, 4, 128, 0, None, None) == 0
 
 
 def test_python_surface_matches_reference_module():

@@ -53,12 +53,13 @@ def test_sq_compress_matches_oracle(capi, oracle, bits, D, cs):
     want = oracle.sq_compress(x, cb, bits, cs)
     bad = got != want
     if bad.any():
-        # log2f differs by an ulp between libdevice and libm; only elements sitting on a
-        # quantisation boundary may land in the neighbouring bucket
+        # log2f differs by an ulp between libdevice and libm; only elements sitting on a quantisation
+        # boundary may land in the neighbouring bucket.  The 0.5 % of elements clamped to fmin sit exactly
+        # on the lowest boundary (log2f(fmin) - emin is 0 or -1 ulp), so up to ~1 % may differ.
         pre = oracle.sq_compress_prefloor(x, cb, bits, cs)
-        assert np.all(np.abs(pre[bad] - np.round(pre[bad])) < 1e-3)
+        assert np.all(np.abs(pre[bad] - np.round(pre[bad])) < max(1e-3, 2.0 ** (bits - 1) * 2e-6))
         assert np.all(np.abs(got[bad] - want[bad]) == 1)
-        assert bad.mean() < 1e-3
+        assert bad.mean() < 0.015
 
 
 @pytest.mark.parametrize("bits", [1, 2, 4, 8, 16])
