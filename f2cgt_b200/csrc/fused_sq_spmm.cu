@@ -4,26 +4,34 @@
 //   out[d, :] = (sum_{k in N(d), CSC order} decode(codes[indices[k], :])) / max(deg(d), 1)
 //
 // The decoded fp32 rows never exist in memory: a neighbour's compressed row (16..256 B) is fetched
-// with one 128-bit (or 64/32-bit) read-only load per lane, decoded in registers and added to fp32
-// register accumulators in CSC order, which makes the result equal to decode-then-aggregate bit for
-// bit and independent of launch geometry.
+// with one 32/64-bit read-only load per lane, decoded and added to fp32 accumulators in registers,
+// in CSC order, which makes the result equal to decode-then-aggregate bit for bit and independent of
+// launch geometry.
 //
-// Layout of work.  A destination row is owned by a group of G = row_bytes / VEC consecutive lanes
-// (G a power of two, so a warp serves 32/G rows at once); lane g of the group owns bytes
-// [g*VEC, (g+1)*VEC) of every neighbour row and the EPL = VEC*8/bits output columns they encode.
-// Per step the group issues U independent row loads before it decodes any of them, so
-// threads * U * VEC bytes are in flight per SM - what an HBM-latency-bound gather needs.
+// What bounds it.  Per edge the kernel moves only row_bytes + 8 bytes but must produce feat_dim fp32
+// values, so on B200 it is bound by instruction issue and by latency (a sampled block offers ~10^5
+// independent rows, each a chain indptr -> indices -> code rows), not by HBM.  The design therefore
+// minimises instructions per decoded element and keeps three destination rows per lane group in
+// flight:
 //
-// Decode.  One MUFU.EX2 per element would cap the kernel below the HBM roofline for narrow codes, so
-// 2/4/8-bit codes are decoded through a shared-memory table built at kernel start WITH THE SAME
-// EXPRESSION as the element-wise decode (hence the same bits): the table is indexed by a whole code
-// byte and returns the 4 / 2 / 1 floats the byte encodes, and it is replicated once per bank group
-// (8 / 16 / 32 copies, 32 KB in all) so that a warp's lookups never collide.  1-bit codes are +-mean:
-// the sign bit is injected into the constant with two integer ops.  16-bit codes (and tables that
-// would need more than one codebook row per lane) use the arithmetic decode.
+//  * Work layout.  A destination row is owned by a group of G = row_bytes / VEC consecutive lanes
+//    (G a power of two; a warp serves 32/G rows at once); lane g owns bytes [g*VEC, (g+1)*VEC) of
+//    every neighbour row and the EPL = VEC*8/bits output columns they encode.
+//  * Decode.  Every width <= 8 bits is decoded a whole code byte at a time through a shared-memory
+//    table built at kernel start WITH THE SAME EXPRESSION as the element-wise decode (hence the same
+//    bits): slab `byte` (256 bytes) holds the 8/bits floats the byte encodes, replicated once per
+//    bank group so lookups never collide.  With a 256-byte slab stride the lookup offset
+//    (byte << 8) | lane_offset is ONE byte-permute of the data word; the lookup is one LDS.64/.128,
+//    and the adds are packed two-per-instruction (add.f32x2).  16-bit codes use the arithmetic decode.
+//  * Pipeline.  While row i is decoded, the code rows of row i+1, the neighbour ids of row i+2 and
+//    the indptr pair of row i+3 are in flight; two register sets alternate through a 2x unrolled loop
+//    so that no load result is ever moved (a move would wait for the load and serialise the chain).
+//  * Output.  A lane holds EPL consecutive columns, so direct stores would scatter 16-byte pieces
+//    over 32 lines per instruction; the warp's sums are staged in shared memory (XOR-swizzled, no
+//    bank conflicts either way), read back row by row, divided by the degree with two FMA
+//    corrections that reproduce the IEEE quotient, and written as whole 512-byte runs.
 //
-// Grid: persistent, a multiple of the SM count; each CTA builds its table once and walks row tiles
-// with a grid stride.
+// Grid: persistent, exactly the resident CTA count; each CTA builds its table once.
 #include "common.cuh"
 
 namespace f2c {
@@ -31,8 +39,8 @@ namespace f2c {
 int validate_sq(const char* op, int code_dtype, int64_t n_codebooks, int64_t src_dim, int64_t feat_dim, int bits,
                 int64_t column_slice);
 
-// tuning knobs (0 = heuristic); set through f2c_set_tuning for experiments
-int g_tune_vec = 0, g_tune_u = 0, g_tune_lut = -1, g_tune_ctas_per_sm = 0, g_tune_ablate = 0, g_tune_layout = 0;
+// experiment knobs (0 = built-in choice), set through f2c_set_tuning
+int g_tune_vec = 0, g_tune_u = 0, g_tune_lut = -1, g_tune_ctas_per_sm = 0;
 
 template <int VEC> struct VecLoad;
 template <> struct VecLoad<4> {
@@ -42,10 +50,6 @@ template <> struct VecLoad<4> {
 template <> struct VecLoad<8> {
   uint32_t w[2];
   __device__ __forceinline__ void load(const void* p) { uint2 v = ldg_nc_u64(p); w[0] = v.x; w[1] = v.y; }
-};
-template <> struct VecLoad<16> {
-  uint32_t w[4];
-  __device__ __forceinline__ void load(const void* p) { uint4 v = ldg_nc_u128(p); w[0] = v.x; w[1] = v.y; w[2] = v.z; w[3] = v.w; }
 };
 
 enum { DEC_ARITH = 0, DEC_LUT = 1 };
@@ -58,62 +62,81 @@ struct SqParams {
   const void* indices;
   float* out;
   int64_t n_dst;
-  int64_t row_bytes;
+  uint32_t row_bytes;
   int feat_dim;
   int column_slice;
   int n_cb;
   int logG;
   int code_kind;
   int reduce;
-  int vec_store;
   int staged;        // 1: rows leave through the shared-memory staging area (feat_dim % 4 == 0)
   int stage_offset;  // byte offset of that area in dynamic shared memory
-  int ablate;  // experiment mask: 1 skip accumulate, 2 skip epilogue, 4 skip table build, 8 skip row loads
   DropoutArgs drop;
 };
 
-// Decode table geometry.  Every width <= 8 bits is decoded a whole code byte at a time: entry `byte`
-// is a 256-byte slab holding the 8/BITS floats the byte encodes, replicated once per shared-memory
-// bank group (so lookups of a warp never collide), which makes the table 64 KB.  Because the slab
-// stride is 256 bytes, the byte offset of a lookup is (byte << 8) | lane_offset and is formed by ONE
-// byte-permute of the data word - no shift/mask/add chain per code.
+// Decode table geometry: 256 slabs of 256 bytes (64 KB).  A slab holds COPIES copies of the FLOATS
+// floats its byte encodes; one copy is one vector read (1-bit codes: two 16-byte halves kept 128 bytes
+// apart so that eight lanes reading a half touch eight different bank groups).
 template <int BITS> struct Lut {
   static constexpr int B = (BITS == 1 || BITS == 2 || BITS == 4) ? BITS : 8;
-  static constexpr int FLOATS = 8 / B;                    // floats per byte: 8, 4, 2, 1
-  static constexpr int COPY_BYTES = FLOATS >= 4 ? 16 : FLOATS * 4;  // one vector read per copy (two for 1-bit)
-  static constexpr int HALVES = FLOATS == 8 ? 2 : 1;      // 1-bit: floats 0-3 and 4-7 live 128 bytes apart
+  static constexpr int FLOATS = 8 / B;                              // 8, 4, 2, 1
+  static constexpr int COPY_BYTES = FLOATS >= 4 ? 16 : FLOATS * 4;
+  static constexpr int HALVES = FLOATS == 8 ? 2 : 1;
   static constexpr int COPIES = 256 / (COPY_BYTES * HALVES) > 32 ? 32 : 256 / (COPY_BYTES * HALVES);  // 8, 16, 32, 32
   static constexpr int NCODE = 1 << B;
   static constexpr int TABLE_BYTES = 256 * 256;
   __device__ static __forceinline__ uint32_t lane_offset(int lane) { return (uint32_t)(lane & (COPIES - 1)) * COPY_BYTES; }
-  // byte offset of float f of (byte, copy)
-  __device__ static __forceinline__ uint32_t offset(int byte, int copy, int f) {
-    return (uint32_t)byte * 256u + (uint32_t)(f / 4) * (HALVES == 2 ? 128u : 0u) + (uint32_t)copy * COPY_BYTES + (uint32_t)(f % 4) * 4u;
-  }
 };
 
-// Two independent fp32 additions in one issue slot (sm_100 packed add; each half rounds to nearest
-// exactly like a scalar add, so results do not change).
-__device__ __forceinline__ void add2(float& a0, float& a1, float b0, float b1) {
-  asm("{\n\t.reg .b64 ra, rb;\n\tmov.b64 ra, {%0, %1};\n\tmov.b64 rb, {%2, %3};\n\tadd.rn.f32x2 ra, ra, rb;\n\tmov.b64 {%0, %1}, ra;\n\t}"
-      : "+f"(a0), "+f"(a1) : "f"(b0), "f"(b1));
-}
+// Accumulators: fp32 pairs packed in 64-bit registers where the decode delivers pairs (table decode of
+// 1/2/4-bit codes), so that every add is one add.f32x2 on operands that are already pairs; scalar
+// fp32 registers otherwise.  Each half rounds to nearest exactly like a scalar add.
+template <int EPL, bool PACKED> struct Acc;
+template <int EPL> struct Acc<EPL, true> {
+  unsigned long long v[EPL / 2];
+  __device__ __forceinline__ void clear() {
+#pragma unroll
+    for (int i = 0; i < EPL / 2; ++i) v[i] = 0ull;
+  }
+  __device__ __forceinline__ void add_pair(int i, unsigned long long x) { asm("add.rn.f32x2 %0, %0, %1;" : "+l"(v[i]) : "l"(x)); }
+  __device__ __forceinline__ void add_one(int, float) {}
+  __device__ __forceinline__ float4 chunk(int q) const {
+    return make_float4(__uint_as_float((uint32_t)v[2 * q]), __uint_as_float((uint32_t)(v[2 * q] >> 32)),
+                       __uint_as_float((uint32_t)v[2 * q + 1]), __uint_as_float((uint32_t)(v[2 * q + 1] >> 32)));
+  }
+  __device__ __forceinline__ float get(int e) const { return __uint_as_float((uint32_t)(v[e >> 1] >> (32 * (e & 1)))); }
+};
+template <int EPL> struct Acc<EPL, false> {
+  float v[EPL];
+  __device__ __forceinline__ void clear() {
+#pragma unroll
+    for (int i = 0; i < EPL; ++i) v[i] = 0.0f;
+  }
+  __device__ __forceinline__ void add_pair(int, unsigned long long) {}
+  __device__ __forceinline__ void add_one(int i, float x) { v[i] += x; }
+  __device__ __forceinline__ float4 chunk(int q) const { return make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]); }
+  __device__ __forceinline__ float get(int e) const { return v[e]; }
+};
 
-// Shared-memory reads by 32-bit shared-window address (keeps the address arithmetic to one add).
-__device__ __forceinline__ float lds_f32(uint32_t a) { float v; asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(a)); return v; }
-__device__ __forceinline__ float2 lds_f32x2(uint32_t a) {
-  float2 v; asm volatile("ld.shared.v2.f32 {%0, %1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(a)); return v;
+__device__ __forceinline__ unsigned long long lds_b64(uint32_t a) {
+  unsigned long long v;
+  asm volatile("ld.shared.b64 %0, [%1];" : "=l"(v) : "r"(a));
+  return v;
 }
-__device__ __forceinline__ float4 lds_f32x4(uint32_t a) {
-  float4 v; asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(a)); return v;
+__device__ __forceinline__ void lds_b64x2(uint32_t a, unsigned long long& x, unsigned long long& y) {
+  asm volatile("ld.shared.v2.b64 {%0, %1}, [%2];" : "=l"(x), "=l"(y) : "r"(a));
+}
+__device__ __forceinline__ float lds_f32(uint32_t a) {
+  float v;
+  asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(a));
+  return v;
 }
 
 // Add the decoded elements of one lane's share of a neighbour row to its accumulators.
-// `table` is the shared-window address of the decode table (DEC_LUT).
-template <int BITS, int VEC, int DEC>
-__device__ __forceinline__ void sq_accumulate(float (&acc)[BITS == 16 ? VEC / 2 : VEC * 8 / BITS], const VecLoad<VEC>& data,
-                                              uint32_t table, uint32_t lane_off, int code_kind, float scale,
-                                              float emin, float mean) {
+// `table` = shared-window address of the decode table; lane_off = this lane's copy offset in a slab.
+template <int BITS, int VEC, int DEC, typename AccT>
+__device__ __forceinline__ void sq_accumulate(AccT& acc, const VecLoad<VEC>& data, uint32_t table, uint32_t lane_off, int code_kind,
+                                              float scale, float emin, float mean) {
   constexpr int NW = VEC / 4;
 #pragma unroll
   for (int w = 0; w < NW; ++w) {
@@ -122,58 +145,48 @@ __device__ __forceinline__ void sq_accumulate(float (&acc)[BITS == 16 ? VEC / 2 
       using L = Lut<BITS>;
 #pragma unroll
       for (int b = 0; b < 4; ++b) {
-        // result bytes: [lane_off.b0, word.b_b, lane_off.b2, lane_off.b3]  ==  (byte << 8) | lane_off
+        // result bytes [lane_off.b0, word.b_b, lane_off.b2, lane_off.b3]  ==  (byte << 8) | lane_off
         const uint32_t e = table + __byte_perm(word, lane_off, 0x7604u | (uint32_t)(b << 4));
+        const int k = w * 4 + b;  // byte number inside the lane's slice
         if (L::FLOATS == 1) {
-          acc[w * 4 + b] += lds_f32(e);
+          acc.add_one(k, lds_f32(e));
         } else if (L::FLOATS == 2) {
-          float2 v = lds_f32x2(e);
-          add2(acc[w * 8 + 2 * b], acc[w * 8 + 2 * b + 1], v.x, v.y);
+          acc.add_pair(k, lds_b64(e));
         } else {
 #pragma unroll
           for (int h = 0; h < L::HALVES; ++h) {
-            float4 v = lds_f32x4(e + 128 * h);
-            const int o = (w * 4 + b) * L::FLOATS + 4 * h;
-            add2(acc[o], acc[o + 1], v.x, v.y);
-            add2(acc[o + 2], acc[o + 3], v.z, v.w);
+            unsigned long long x, y;
+            lds_b64x2(e + 128 * h, x, y);
+            acc.add_pair((k * L::HALVES + h) * 2, x);
+            acc.add_pair((k * L::HALVES + h) * 2 + 1, y);
           }
         }
       }
-    } else if (BITS == 1) {
-      const uint32_t negmean = __float_as_uint(-mean);
-#pragma unroll
-      for (int i = 0; i < 32; ++i) acc[w * 32 + i] += __uint_as_float(negmean ^ ((word << (31 - i)) & 0x80000000u));
     } else if (BITS == 16) {
-      acc[w * 2 + 0] += sq_decode<BITS>((float)(int16_t)(word & 0xFFFFu), scale, emin, mean);
-      acc[w * 2 + 1] += sq_decode<BITS>((float)(int16_t)(word >> 16), scale, emin, mean);
+      acc.add_one(w * 2 + 0, sq_decode<BITS>((float)(int16_t)(word & 0xFFFFu), scale, emin, mean));
+      acc.add_one(w * 2 + 1, sq_decode<BITS>((float)(int16_t)(word >> 16), scale, emin, mean));
     } else if (BITS == 8) {
 #pragma unroll
       for (int b = 0; b < 4; ++b) {
         uint32_t byte = (word >> (8 * b)) & 0xFFu;
         float c = code_kind == CODE_I8 ? (float)(int8_t)byte : (float)byte;
-        acc[w * 4 + b] += sq_decode<BITS>(c, scale, emin, mean);
+        acc.add_one(w * 4 + b, sq_decode<BITS>(c, scale, emin, mean));
       }
-    } else {  // 2- or 4-bit arithmetic decode
-      constexpr int B = (BITS == 2 || BITS == 4) ? BITS : 4;
+    } else {  // 1-, 2- or 4-bit arithmetic decode
+      constexpr int B = (BITS == 1 || BITS == 2 || BITS == 4) ? BITS : 4;
       constexpr int PER_WORD = 32 / B;
 #pragma unroll
       for (int i = 0; i < PER_WORD; ++i)
-        acc[w * PER_WORD + i] += sq_decode<BITS>((float)((word >> (B * i)) & ((1u << B) - 1u)), scale, emin, mean);
+        acc.add_one(w * PER_WORD + i, sq_decode<BITS>((float)((word >> (B * i)) & ((1u << B) - 1u)), scale, emin, mean));
     }
   }
 }
 
-}  // namespace f2c
-#include "fused_sq_rowwarp.cuh"
-namespace f2c {
-
-// The kernel is software pipelined over the destination rows a lane group visits: while the rows of
-// destination row i are in flight, the neighbour ids of row i+1 and the indptr pair of row i+2 are
-// already being fetched, so a row costs one memory round trip instead of three dependent ones.
-// U = neighbours held in registers per row (rows with more take extra rounds of U).
+// U = neighbours held in registers per destination row (rows with more take extra, unpipelined rounds).
 template <int BITS, int VEC, int U, typename IdxT, int DEC>
 __global__ void __launch_bounds__(256, 2) sq_spmm_kernel(const SqParams p) {
   constexpr int EPL = BITS == 16 ? VEC / 2 : VEC * 8 / BITS;  // output columns per lane
+  constexpr bool PACKED = DEC == DEC_LUT && BITS <= 4;
   extern __shared__ __align__(16) unsigned char smem_raw[];
 
   const int lane = threadIdx.x & 31;
@@ -181,7 +194,7 @@ __global__ void __launch_bounds__(256, 2) sq_spmm_kernel(const SqParams p) {
   const int lane_g = lane & (G - 1);
   const int sub = lane >> p.logG;
   const int rows_per_warp = 32 >> p.logG;
-  const int byte0 = lane_g * VEC;
+  const uint32_t byte0 = (uint32_t)lane_g * VEC;
   const bool lane_active = byte0 < p.row_bytes;
   const int c0 = lane_g * EPL;
 
@@ -197,9 +210,9 @@ __global__ void __launch_bounds__(256, 2) sq_spmm_kernel(const SqParams p) {
   if (DEC == DEC_LUT) {
     // Copy c of a slab serves the lanes with lane % COPIES == c, whose lane_g is c % G.
     // Phase 1 decodes each code value once per distinct codebook row (2^B * min(G, COPIES) exp2f in all);
-    // phase 2 assembles the byte-indexed, bank-replicated table from those values.
+    // phase 2 assembles the byte-indexed, bank-replicated table from those values, 16 bytes per store.
     using L = Lut<BITS>;
-    float* base = reinterpret_cast<float*>(smem_raw + L::TABLE_BYTES);  // [n_rows][NCODE]
+    float* base = reinterpret_cast<float*>(smem_raw + L::TABLE_BYTES + 256);  // [n_rows][NCODE], after the zero slab
     const int n_rows = G < L::COPIES ? G : L::COPIES;
     for (int i = threadIdx.x; i < n_rows * L::NCODE; i += blockDim.x) {
       int code = i & (L::NCODE - 1), g = i / L::NCODE;
@@ -211,14 +224,13 @@ __global__ void __launch_bounds__(256, 2) sq_spmm_kernel(const SqParams p) {
       base[i] = sq_decode<BITS>(c, sq_scale<BITS>(e0, e1), e0, m);
     }
     __syncthreads();
-    // one 16-byte store per step: slab `byte`, bytes [16j, 16j+16)
     constexpr int SPAN = L::HALVES == 2 ? 128 : 256;
     for (int i = threadIdx.x; i < 256 * 16; i += blockDim.x) {
       const int byte = i >> 4, j = i & 15;
       float v[4];
 #pragma unroll
       for (int t = 0; t < 4; ++t) {
-        const int o = 16 * j + 4 * t;                 // byte offset inside the slab
+        const int o = 16 * j + 4 * t;  // byte offset inside the slab
         const int h = L::HALVES == 2 ? o / 128 : 0;
         const int oo = o % SPAN;
         const int copy = oo / L::COPY_BYTES;
@@ -228,14 +240,15 @@ __global__ void __launch_bounds__(256, 2) sq_spmm_kernel(const SqParams p) {
       }
       *reinterpret_cast<float4*>(smem_raw + i * 16) = make_float4(v[0], v[1], v[2], v[3]);
     }
+    // zero slab used by neighbour slots beyond a row's degree (its address is lane_off + TABLE_BYTES with byte 0)
+    for (int i = threadIdx.x; i < 64; i += blockDim.x) reinterpret_cast<float*>(smem_raw + L::TABLE_BYTES)[i] = 0.0f;
     __syncthreads();
     lane_off = L::lane_offset(lane);
   }
-  if (DEC == DEC_LUT) lane_off = Lut<BITS>::lane_offset(lane);
   const uint32_t table = (uint32_t)__cvta_generic_to_shared(smem_raw);
 
-  // Sums of decoded values are either 0 or, in magnitude, between 2^(emin-24) and deg * 2^emax (1 bit: multiples
-  // of ~mean); when that interval is well inside the normal range for every lane of the warp, the mean can use
+  // Sums of decoded values are 0 or, in magnitude, between 2^(emin-24) and deg * 2^emax (1 bit: multiples of
+  // ~mean); when that interval is well inside the normal range for every lane of the warp, the mean can use
   // the division without the per-element range check.
   const bool div_safe = __all_sync(0xffffffffu, BITS == 1 ? (mean > 1e-20f && mean < 1e20f) : (emin > -80.0f && emax < 80.0f));
 
@@ -245,133 +258,150 @@ __global__ void __launch_bounds__(256, 2) sq_spmm_kernel(const SqParams p) {
   const int64_t stride = (((int64_t)gridDim.x * blockDim.x) >> 5) * rows_per_warp;
   const uint8_t* __restrict__ my_codes = p.codes + byte0;
 
-  // ---- three-deep software pipeline over the rows d, d+stride, d+2*stride, ... of this lane group:
-  //   while row i is decoded, the code rows of row i+1, the neighbour ids of row i+2 and the indptr pair
-  //   of row i+3 are in flight.  Two register sets (P, P^1) alternate through a 2x unrolled loop so
-  //   that no load result has to be moved - a move would wait for the load and serialise the chain.
-  int64_t d = warp * rows_per_warp + sub;
-  int64_t begA = 0, begB = 0, begC = 0;  // first edge of rows i, i+1, i+2
-  int degA = 0, degB = 0, degC = 0;      // their degrees
-  if (d < p.n_dst && lane_active) { begA = (int64_t)indptr[d]; degA = (int)((int64_t)indptr[d + 1] - begA); }
-  if (d + stride < p.n_dst && lane_active) { begB = (int64_t)indptr[d + stride]; degB = (int)((int64_t)indptr[d + stride + 1] - begB); }
-  if (d + 2 * stride < p.n_dst && lane_active) { begC = (int64_t)indptr[d + 2 * stride]; degC = (int)((int64_t)indptr[d + 2 * stride + 1] - begC); }
-  uint32_t nidx[2][U];
+  // ---- three-deep software pipeline over the rows d, d+stride, d+2*stride, ... of this lane group.
+  // Rows are counted in 32 bits (the host checks n_dst < 2^31).
+  const int n_dst = (int)p.n_dst;
+  const int istride = (int)stride;
+  int d = (int)(warp * rows_per_warp) + sub;
+  const IdxT* idsA = indices;  // first neighbour id of rows i, i+1, i+2
+  const IdxT* idsB = indices;
+  const IdxT* idsC = indices;
+  int degA = 0, degB = 0, degC = 0;
+  if (d < n_dst && lane_active) { int64_t b = (int64_t)indptr[d]; degA = (int)((int64_t)indptr[d + 1] - b); idsA = indices + b; }
+  if (d + istride < n_dst && lane_active) {
+    int64_t b = (int64_t)indptr[d + istride]; degB = (int)((int64_t)indptr[d + istride + 1] - b); idsB = indices + b;
+  }
+  if (d + 2 * istride < n_dst && lane_active) {
+    int64_t b = (int64_t)indptr[d + 2 * istride]; degC = (int)((int64_t)indptr[d + 2 * istride + 1] - b); idsC = indices + b;
+  }
+  // One set of id registers is enough: a stage first issues the row loads that consume them, then
+  // overwrites them with the ids of the row after (the hardware scoreboard orders the two).
+  uint32_t nidx[U];
   VecLoad<VEC> data[2][U];
 #pragma unroll
-  for (int u = 0; u < U; ++u) nidx[0][u] = u < degA ? (uint32_t)indices[begA + u] : 0u;
+  for (int u = 0; u < U; ++u) nidx[u] = u < degA ? (uint32_t)idsA[u] : 0u;
 #pragma unroll
-  for (int u = 0; u < U; ++u) nidx[1][u] = u < degB ? (uint32_t)indices[begB + u] : 0u;
+  for (int u = 0; u < U; ++u) {
 #pragma unroll
-  for (int u = 0; u < U; ++u)
-    if (u < degA) data[0][u].load(my_codes + (int64_t)nidx[0][u] * p.row_bytes);
+    for (int w = 0; w < VEC / 4; ++w) data[0][u].w[w] = 0u;
+    if (u < degA) data[0][u].load(my_codes + (uint64_t)nidx[u] * p.row_bytes);
+  }
+#pragma unroll
+  for (int u = 0; u < U; ++u) nidx[u] = u < degB ? (uint32_t)idsB[u] : 0u;
+  // Neighbour slots beyond a row's degree read slab 0 of a zero-filled copy of the table geometry
+  // (their data word is kept 0), so the decode loop needs no divergent branch: adding +0 changes nothing.
+  const uint32_t lane_off_zero = lane_off + Lut<BITS>::TABLE_BYTES;
 
-  for (int64_t row_base = warp * rows_per_warp; row_base < p.n_dst;) {
+  for (int row_base = (int)(warp * rows_per_warp); row_base < n_dst;) {
 #pragma unroll
     for (int P = 0; P < 2; ++P) {
-      if (row_base < p.n_dst) {  // warp uniform
+      if (row_base < n_dst) {  // warp uniform
         // (1) code rows of the next destination row -> data[P^1]
 #pragma unroll
-        for (int u = 0; u < U; ++u)
-          if (u < degB) data[P ^ 1][u].load(my_codes + (int64_t)nidx[P ^ 1][u] * p.row_bytes);
-        // (2) neighbour ids of the row after it -> nidx[P] (its previous content was consumed one stage ago)
+        for (int u = 0; u < U; ++u) {
 #pragma unroll
-        for (int u = 0; u < U; ++u) nidx[P][u] = u < degC ? (uint32_t)indices[begC + u] : 0u;
+          for (int w = 0; w < VEC / 4; ++w) data[P ^ 1][u].w[w] = 0u;
+          if (u < degB) data[P ^ 1][u].load(my_codes + (uint64_t)nidx[u] * p.row_bytes);
+        }
+        // (2) neighbour ids of the row after it
+#pragma unroll
+        for (int u = 0; u < U; ++u) nidx[u] = u < degC ? (uint32_t)idsC[u] : 0u;
         // (3) indptr pair three rows ahead
-        int64_t begD = 0;
+        const IdxT* idsD = indices;
         int degD = 0;
-        if (d + 3 * stride < p.n_dst && lane_active) {
-          begD = (int64_t)indptr[d + 3 * stride];
-          degD = (int)((int64_t)indptr[d + 3 * stride + 1] - begD);
+        if (d + 3 * istride < n_dst && lane_active) {
+          int64_t b = (int64_t)indptr[d + 3 * istride];
+          degD = (int)((int64_t)indptr[d + 3 * istride + 1] - b);
+          idsD = indices + b;
         }
 
         // (4) decode + accumulate the current row from data[P]
-        float acc[EPL];
+        Acc<EPL, PACKED> acc;
+        acc.clear();
+        const int umax = __reduce_max_sync(0xffffffffu, degA < U ? degA : U);  // slots any row of the warp uses
 #pragma unroll
-        for (int e = 0; e < EPL; ++e) acc[e] = 0.0f;
-        {
-#pragma unroll
-          for (int u = 0; u < U; ++u)
-            if (u < degA) sq_accumulate<BITS, VEC, DEC>(acc, data[P][u], table, lane_off, p.code_kind, scale, emin, mean);
+        for (int u = 0; u < U; ++u) {
+          if (u < umax) {  // warp uniform
+            if (DEC == DEC_LUT) {
+              sq_accumulate<BITS, VEC, DEC>(acc, data[P][u], table, u < degA ? lane_off : lane_off_zero, p.code_kind, scale, emin, mean);
+            } else if (u < degA) {
+              sq_accumulate<BITS, VEC, DEC>(acc, data[P][u], table, lane_off, p.code_kind, scale, emin, mean);
+            }
+          }
         }
         // destination rows with more than U neighbours: further rounds of four, not pipelined
         for (int k = U; k < degA; k += 4) {
           VecLoad<VEC> extra[4];
 #pragma unroll
           for (int u = 0; u < 4; ++u)
-            if (k + u < degA) extra[u].load(my_codes + (int64_t)indices[begA + k + u] * p.row_bytes);
+            if (k + u < degA) extra[u].load(my_codes + (uint64_t)(uint32_t)idsA[k + u] * p.row_bytes);
 #pragma unroll
           for (int u = 0; u < 4; ++u)
             if (k + u < degA) sq_accumulate<BITS, VEC, DEC>(acc, extra[u], table, lane_off, p.code_kind, scale, emin, mean);
         }
 
         // (5) mean / dropout / store
-        {
-          const bool have_row = d < p.n_dst && lane_active;
-          if (p.staged) {
-            // Each lane holds EPL consecutive columns, so direct stores would scatter 16-byte pieces over
-            // 32 different lines per instruction.  Stage the warp's raw sums in shared memory (chunk index
-            // XOR-swizzled so that neither side has bank conflicts), then read them back row by row, apply
-            // the mean / dropout to the one float4 each lane holds, and write whole 512-byte runs.
-            constexpr int Q = EPL / 4;                                    // chunks (float4) per lane
-            constexpr int LQ = Q >= 8 ? 3 : Q == 4 ? 2 : Q == 2 ? 1 : 0;  // low chunk-index bits that only depend on q
-            const int NC = p.feat_dim >> 2;                               // chunks per output row
-            const int NCP = Q << p.logG;                                  // row stride of the staging area (>= NC)
-            float4* stage = reinterpret_cast<float4*>(smem_raw + p.stage_offset) + (threadIdx.x >> 5) * (32 * Q);
-            // chunk c of a row is kept at c ^ m, m = the lane bits that the low bits of c do not already spread
-            // over the banks; m only touches the q part of the index, so a lane stays inside its own Q chunks
-            if (have_row) {
-              const int m = ((lane & 7) >> (3 - LQ)) & ((1 << LQ) - 1);
+        const bool have_row = d < n_dst && lane_active;
+        if (p.staged) {
+          constexpr int Q = EPL / 4;                                    // chunks (float4) per lane
+          constexpr int LQ = Q >= 8 ? 3 : Q == 4 ? 2 : Q == 2 ? 1 : 0;  // low chunk-index bits that only depend on q
+          const int NC = p.feat_dim >> 2;                               // chunks per output row
+          const int NCP = Q << p.logG;                                  // row stride of the staging area (>= NC)
+          float4* stage = reinterpret_cast<float4*>(smem_raw + p.stage_offset) + (threadIdx.x >> 5) * (32 * Q);
+          // chunk c of a row is kept at c ^ m, m = the lane bits that the low bits of c do not already spread
+          // over the banks; m only touches the q part of the index, so a lane stays inside its own Q chunks
+          if (have_row) {
+            const int m = ((lane & 7) >> (3 - LQ)) & ((1 << LQ) - 1);
 #pragma unroll
-              for (int q = 0; q < Q; ++q) {
-                const int c4 = lane_g * Q + q;
-                if (c4 < NC) stage[sub * NCP + (c4 ^ m)] = make_float4(acc[4 * q], acc[4 * q + 1], acc[4 * q + 2], acc[4 * q + 3]);
-              }
+            for (int q = 0; q < Q; ++q) {
+              const int c4 = lane_g * Q + q;
+              if (c4 < NC) stage[sub * NCP + (c4 ^ m)] = acc.chunk(q);
             }
-            // reciprocal of the row's degree, once per lane group (0 marks "do not divide")
-            float my_rcp = 0.0f;
-            if (p.reduce == F2C_MEAN && degA > 1) my_rcp = 1.0f / (float)degA;
-            __syncwarp();
-            for (int row = 0; row < rows_per_warp; ++row) {
-              const int64_t dr = row_base + row;
-              if (dr >= p.n_dst) break;
-              const float rcp = __shfl_sync(0xffffffffu, my_rcp, row << p.logG);
-              const float deg = (float)__shfl_sync(0xffffffffu, degA, row << p.logG);
-              for (int c = lane; c < NC; c += 32) {
-                const int writer = (row << p.logG) + c / Q;  // lane that produced chunk c
-                const int m = ((writer & 7) >> (3 - LQ)) & ((1 << LQ) - 1);
-                float4 v = stage[row * NCP + (c ^ m)];
-                if (rcp != 0.0f) {
-                  if (div_safe) {
-                    v.x = div_exact_fast(v.x, deg, rcp); v.y = div_exact_fast(v.y, deg, rcp);
-                    v.z = div_exact_fast(v.z, deg, rcp); v.w = div_exact_fast(v.w, deg, rcp);
-                  } else {
-                    v.x = div_exact(v.x, deg, rcp); v.y = div_exact(v.y, deg, rcp);
-                    v.z = div_exact(v.z, deg, rcp); v.w = div_exact(v.w, deg, rcp);
-                  }
+          }
+          // reciprocal of the row's degree, once per lane group (0 marks "do not divide")
+          float my_rcp = 0.0f;
+          if (p.reduce == F2C_MEAN && degA > 1) my_rcp = 1.0f / (float)degA;
+          __syncwarp();
+          for (int row = 0; row < rows_per_warp; ++row) {
+            const int64_t dr = row_base + row;
+            if (dr >= n_dst) break;
+            const float rcp = __shfl_sync(0xffffffffu, my_rcp, row << p.logG);
+            const float deg = (float)__shfl_sync(0xffffffffu, degA, row << p.logG);
+            for (int c = lane; c < NC; c += 32) {
+              const int writer = (row << p.logG) + c / Q;  // lane that produced chunk c
+              const int m = ((writer & 7) >> (3 - LQ)) & ((1 << LQ) - 1);
+              float4 v = stage[row * NCP + (c ^ m)];
+              if (rcp != 0.0f) {
+                if (div_safe) {
+                  v.x = div_exact_fast(v.x, deg, rcp); v.y = div_exact_fast(v.y, deg, rcp);
+                  v.z = div_exact_fast(v.z, deg, rcp); v.w = div_exact_fast(v.w, deg, rcp);
+                } else {
+                  v.x = div_exact(v.x, deg, rcp); v.y = div_exact(v.y, deg, rcp);
+                  v.z = div_exact(v.z, deg, rcp); v.w = div_exact(v.w, deg, rcp);
                 }
-                if (p.drop.enabled) v = dropout_apply4(v, (uint64_t)(dr * p.feat_dim + 4 * c), p.drop);
-                stg_cs_f4(p.out + dr * p.feat_dim + 4 * c, v);
               }
+              if (p.drop.enabled) v = dropout_apply4(v, (uint64_t)(dr * p.feat_dim + 4 * c), p.drop);
+              stg_cs_f4(p.out + dr * p.feat_dim + 4 * c, v);
             }
-            __syncwarp();
-          } else if (have_row) {
-            float* orow = p.out + d * p.feat_dim;
-            const float deg = degA == 0 ? 1.0f : (float)degA;
+          }
+          __syncwarp();
+        } else if (have_row) {
+          float* orow = p.out + (int64_t)d * p.feat_dim;
+          const float deg = degA == 0 ? 1.0f : (float)degA;
 #pragma unroll
-            for (int e = 0; e < EPL; ++e) {
-              int col = c0 + e;
-              if (col < p.feat_dim) {
-                float v = p.reduce == F2C_MEAN ? acc[e] / deg : acc[e];
-                if (p.drop.enabled) v = dropout_apply1(v, (uint64_t)(d * p.feat_dim + col), p.drop);
-                orow[col] = v;
-              }
+          for (int e = 0; e < EPL; ++e) {
+            int col = c0 + e;
+            if (col < p.feat_dim) {
+              float v = p.reduce == F2C_MEAN ? acc.get(e) / deg : acc.get(e);
+              if (p.drop.enabled) v = dropout_apply1(v, (uint64_t)((int64_t)d * p.feat_dim + col), p.drop);
+              orow[col] = v;
             }
           }
         }
         // rotate the (already resident) scalars; the register sets swap through P
-        begA = begB; degA = degB; begB = begC; degB = degC; begC = begD; degC = degD;
-        d += stride;
-        row_base += stride;
+        idsA = idsB; degA = degB; idsB = idsC; degB = degC; idsC = idsD; degC = degD;
+        d += istride;
+        row_base += istride;
       }
     }
   }
@@ -433,31 +463,28 @@ __global__ void __launch_bounds__(256) sq_spmm_generic_kernel(const void* __rest
 static int ilog2(int v) { int l = 0; while ((1 << l) < v) ++l; return l; }
 
 template <int BITS, int VEC, int U, typename IdxT, int DEC>
-static int launch_fast(SqParams p, cudaStream_t st) {
+static int launch_fast(SqParams p, bool vec_store, cudaStream_t st) {
   auto kern = sq_spmm_kernel<BITS, VEC, U, IdxT, DEC>;
-  // table (64 KB) + the decoded code values of each distinct codebook row
+  constexpr int EPL = BITS == 16 ? VEC / 2 : VEC * 8 / BITS;
+  // decode table (64 KB) + the decoded code values of each distinct codebook row
   size_t smem = 0;
   if (DEC == DEC_LUT) {
-    constexpr int B = (BITS == 1 || BITS == 2 || BITS == 4) ? BITS : 8;
-    constexpr int COPIES = B == 1 ? 8 : B == 2 ? 16 : 32;
-    int n_rows = (1 << p.logG) < COPIES ? (1 << p.logG) : COPIES;
-    smem = 65536 + (size_t)n_rows * (1 << B) * sizeof(float);
+    using L = Lut<BITS>;
+    int n_rows = (1 << p.logG) < L::COPIES ? (1 << p.logG) : L::COPIES;
+    smem = L::TABLE_BYTES + 256 + (size_t)n_rows * L::NCODE * sizeof(float);
   }
-  // staging area for coalesced output: 8 warps x rows per warp x feat_dim floats
+  // staging area for coalesced output: 8 warps x 32 lanes x EPL floats
   p.staged = 0;
   p.stage_offset = (int)smem;
-  constexpr int EPL = BITS == 16 ? VEC / 2 : VEC * 8 / BITS;
-  size_t stage_bytes = (size_t)8 * 32 * EPL * sizeof(float);  // 8 warps x 32 lanes x EPL floats
-  if (p.vec_store && EPL >= 4 && stage_bytes <= 64 * 1024) {
+  if (vec_store && EPL >= 4) {
     p.staged = 1;
-    smem += stage_bytes;
+    smem += (size_t)8 * 32 * EPL * sizeof(float);
   }
   if (smem > 48 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 65536 + 32 * 256 * 4 + 65536);
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 65536 + 256 + 32 * 256 * 4 + 32768);
     if (e != cudaSuccess) return set_error(F2C_ERR_CUDA, "sq_decompress_spmm_csr: %s", cudaGetErrorString(e));
   }
-  int rows_per_cta = 8 * (32 >> p.logG);
-  // persistent grid: exactly as many CTAs as the device keeps resident (queried once per variant)
+  // persistent grid: exactly as many CTAs as the device keeps resident (queried when the footprint changes)
   static int resident = 0;
   static size_t resident_smem = ~(size_t)0;
   if (resident == 0 || resident_smem != smem) {
@@ -467,6 +494,7 @@ static int launch_fast(SqParams p, cudaStream_t st) {
     resident_smem = smem;
   }
   int ctas_per_sm = g_tune_ctas_per_sm > 0 ? g_tune_ctas_per_sm : resident;
+  int rows_per_cta = 8 * (32 >> p.logG);
   int64_t grid = ceil_div(p.n_dst, rows_per_cta);
   if (grid > (int64_t)kSmCount * ctas_per_sm) grid = (int64_t)kSmCount * ctas_per_sm;
   kern<<<(unsigned)grid, 256, smem, st>>>(p);
@@ -474,80 +502,57 @@ static int launch_fast(SqParams p, cudaStream_t st) {
 }
 
 template <int BITS, int VEC, typename IdxT, int DEC>
-static int pick_u(const SqParams& p, cudaStream_t st) {
+static int pick_u(const SqParams& p, bool vec_store, cudaStream_t st) {
   int u = g_tune_u > 0 ? g_tune_u : 12;
-  if (u >= 16) return launch_fast<BITS, VEC, 16, IdxT, DEC>(p, st);
-  if (u >= 12) return launch_fast<BITS, VEC, 12, IdxT, DEC>(p, st);
-  return launch_fast<BITS, VEC, 8, IdxT, DEC>(p, st);
+  if (u >= 16) return launch_fast<BITS, VEC, 16, IdxT, DEC>(p, vec_store, st);
+  if (u >= 12) return launch_fast<BITS, VEC, 12, IdxT, DEC>(p, vec_store, st);
+  return launch_fast<BITS, VEC, 8, IdxT, DEC>(p, vec_store, st);
 }
 
 template <int BITS, typename IdxT>
-static int dispatch_fast(const SqParams& p, int vec, bool lut, cudaStream_t st) {
-  constexpr int VMAX = BITS == 1 ? 4 : 8;  // two register sets of U rows: at most two words per row, EPL <= 32
+static int dispatch_fast(const SqParams& p, int vec, bool lut, bool vec_store, cudaStream_t st) {
   constexpr bool CAN_LUT = BITS <= 8;
-  if (vec > VMAX) vec = VMAX;
+  constexpr bool CAN_8 = BITS != 1;  // 1-bit: 4 bytes per lane already are 32 columns
   if constexpr (CAN_LUT) if (lut) {
-    if (vec == 16) return pick_u<BITS, VMAX >= 16 ? 16 : VMAX, IdxT, DEC_LUT>(p, st);
-    if (vec == 8) return pick_u<BITS, VMAX >= 8 ? 8 : VMAX, IdxT, DEC_LUT>(p, st);
-    return pick_u<BITS, 4, IdxT, DEC_LUT>(p, st);
+    if constexpr (CAN_8) if (vec == 8) return pick_u<BITS, 8, IdxT, DEC_LUT>(p, vec_store, st);
+    return pick_u<BITS, 4, IdxT, DEC_LUT>(p, vec_store, st);
   }
-  if (vec == 16) return pick_u<BITS, VMAX >= 16 ? 16 : VMAX, IdxT, DEC_ARITH>(p, st);
-  if (vec == 8) return pick_u<BITS, VMAX >= 8 ? 8 : VMAX, IdxT, DEC_ARITH>(p, st);
-  return pick_u<BITS, 4, IdxT, DEC_ARITH>(p, st);
+  if constexpr (CAN_8) if (vec == 8) return pick_u<BITS, 8, IdxT, DEC_ARITH>(p, vec_store, st);
+  return pick_u<BITS, 4, IdxT, DEC_ARITH>(p, vec_store, st);
 }
 
 template <int BITS, typename IdxT>
 static int launch_sq_spmm(const void* codes, int code_dtype, const float* codebooks, int64_t n_cb, const void* indptr,
-                          const void* indices, float* out, int64_t n_dst, int64_t n_src, int64_t src_dim, int64_t D, int64_t cs, int reduce,
-                          const DropoutArgs& drop, cudaStream_t st) {
+                          const void* indices, float* out, int64_t n_dst, int64_t n_src, int64_t src_dim, int64_t D, int64_t cs,
+                          int reduce, const DropoutArgs& drop, cudaStream_t st) {
   if (n_dst == 0 || D == 0) return F2C_OK;
   const int code_bytes = dtype_size(code_dtype);
   const int64_t row_bytes = src_dim * code_bytes;
-  const bool natural = BITS < 8 || (BITS == 8 && code_bytes == 1) || (BITS == 16 && code_bytes == 2);
-  // ---- one warp per destination row (default): needs float4-aligned output columns ----
-  {
-    const int load_align = BITS == 16 ? 8 : BITS == 8 ? 4 : BITS == 4 ? 2 : 1;
-    bool ok = natural && n_src < (1ll << 32) && D % 4 == 0 && aligned(out, 16) && aligned(codes, load_align) &&
-              row_bytes % load_align == 0 && (n_cb == 1 || cs % 4 == 0) && g_tune_layout == 2;
-    if (ok) {
-      SqParams p;
-      p.codes = (const uint8_t*)codes; p.codebooks = codebooks; p.indptr = indptr; p.indices = indices; p.out = out;
-      p.n_dst = n_dst; p.row_bytes = row_bytes; p.feat_dim = (int)D; p.column_slice = (int)cs; p.n_cb = (int)n_cb;
-      p.logG = 5; p.code_kind = code_dtype == F2C_I8 ? CODE_I8 : code_dtype == F2C_U8 ? CODE_U8 : CODE_I16;
-      p.reduce = reduce; p.vec_store = 1; p.staged = 0; p.stage_offset = 0; p.drop = drop; p.ablate = g_tune_ablate;
-      // one table per CTA: every lane that shares a table copy must share a codebook row
-      bool lut = BITS <= 8 && g_tune_lut != 0 && (n_cb == 1 || (BITS >= 4 && D <= 128));
-      bool handled = false;
-      int rc = launch_rowwarp<BITS, IdxT>(p, lut, st, &handled);
-      if (handled) return rc;
-    }
-  }
   // ---- can the vector kernel serve this shape? ----
-  constexpr int VMAX = BITS == 1 ? 4 : 8;
+  constexpr int VMAX = BITS == 1 ? 4 : 8;  // two register sets of U rows: at most two words per row, EPL <= 32
   int vec = 0;
   for (int v = VMAX; v >= 4; v >>= 1)
     if (row_bytes % v == 0 && aligned(codes, v) && row_bytes <= 32 * v) { vec = v; break; }
   if (g_tune_vec > 0 && vec > g_tune_vec && row_bytes <= 32 * g_tune_vec) vec = g_tune_vec;
-  bool natural_dtype = BITS < 8 || (BITS == 8 && code_bytes == 1) || (BITS == 16 && code_bytes == 2);
+  const bool natural_dtype = BITS < 8 || (BITS == 8 && code_bytes == 1) || (BITS == 16 && code_bytes == 2);
   // the vector kernel keeps neighbour ids in 32-bit registers
-  bool fast = vec != 0 && natural_dtype && n_src < (1ll << 32);
+  bool fast = vec != 0 && natural_dtype && n_src < (1ll << 32) && n_dst < (1ll << 30);
   int epl = 0, G = 0;
   if (fast) {
     epl = BITS == 16 ? vec / 2 : vec * 8 / BITS;
     G = 1 << ilog2((int)ceil_div(row_bytes, vec));
-    // every lane's columns must share one codebook row
-    fast = n_cb == 1 || cs % epl == 0;
+    fast = n_cb == 1 || cs % epl == 0;  // every lane's columns must share one codebook row
   }
   if (fast) {
     SqParams p;
     p.codes = (const uint8_t*)codes; p.codebooks = codebooks; p.indptr = indptr; p.indices = indices; p.out = out;
-    p.n_dst = n_dst; p.row_bytes = row_bytes; p.feat_dim = (int)D; p.column_slice = (int)cs; p.n_cb = (int)n_cb;
+    p.n_dst = n_dst; p.row_bytes = (uint32_t)row_bytes; p.feat_dim = (int)D; p.column_slice = (int)cs; p.n_cb = (int)n_cb;
     p.logG = ilog2(G); p.code_kind = code_dtype == F2C_I8 ? CODE_I8 : code_dtype == F2C_U8 ? CODE_U8 : CODE_I16;
-    p.reduce = reduce; p.vec_store = D % 4 == 0 && aligned(out, 16); p.drop = drop; p.ablate = g_tune_ablate;
+    p.reduce = reduce; p.staged = 0; p.stage_offset = 0; p.drop = drop;
     // table copies are shared by lanes l and l + COPIES: they must own the same columns
     int copies = BITS >= 4 ? 32 : BITS == 2 ? 16 : 8;
     bool lut = (n_cb == 1 || copies % G == 0) && g_tune_lut != 0;
-    return dispatch_fast<BITS, IdxT>(p, vec, lut, st);
+    return dispatch_fast<BITS, IdxT>(p, vec, lut, D % 4 == 0 && aligned(out, 16), st);
   }
   int64_t blocks = ceil_div(n_dst, 8);
   if (blocks > kSmCount * 32) blocks = kSmCount * 32;
@@ -584,7 +589,7 @@ extern "C" int f2c_sq_spmm_csr(const void* codes, int code_dtype, const float* c
 #define F2C_SQ(B)                                                                                                   \
   return index_dtype == F2C_I32                                                                                     \
              ? launch_sq_spmm<B, int32_t>(codes, code_dtype, codebooks, n_codebooks, indptr, indices, out, n_dst,   \
-                                          n_src, src_dim, feat_dim, column_slice, reduce, drop, st)                       \
+                                          n_src, src_dim, feat_dim, column_slice, reduce, drop, st)                \
              : launch_sq_spmm<B, int64_t>(codes, code_dtype, codebooks, n_codebooks, indptr, indices, out, n_dst,   \
                                           n_src, src_dim, feat_dim, column_slice, reduce, drop, st)
   switch (bits) {
@@ -597,17 +602,15 @@ extern "C" int f2c_sq_spmm_csr(const void* codes, int code_dtype, const float* c
 #undef F2C_SQ
 }
 
-// Experiment knobs for the fused kernels (no counterpart in the reference).  key: 0 = bytes per lane
-// per row load, 1 = rows in flight, 2 = table decode on/off, 3 = CTAs per SM.  value 0 (or -1 for
-// key 2) restores the heuristic.
+// Experiment knobs of the fused SQ kernel (no counterpart in the reference).  key 0: bytes per lane per
+// row load (4/8), 1: neighbours held in registers per row (8/12/16), 2: table decode on/off, 3: CTAs per
+// SM.  value 0 (key 2: -1) restores the built-in choice.
 extern "C" int f2c_set_tuning(int key, int value) {
   switch (key) {
     case 0: g_tune_vec = value; break;
     case 1: g_tune_u = value; break;
     case 2: g_tune_lut = value; break;
     case 3: g_tune_ctas_per_sm = value; break;
-    case 4: g_tune_ablate = value; break;
-    case 5: g_tune_layout = value; break;
     default: return set_error(F2C_ERR_INVALID, "set_tuning: unknown key %d", key);
   }
   return F2C_OK;

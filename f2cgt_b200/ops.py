@@ -339,7 +339,7 @@ class KMeans:
 
 def set_tuning(key, value):
     """Experiment knob of the fused SQ kernel: key in {"vec", "inflight", "lut", "ctas_per_sm"}."""
-    check(lib.f2c_set_tuning({"vec": 0, "inflight": 1, "lut": 2, "ctas_per_sm": 3, "ablate": 4, "layout": 5}[key], int(value)))
+    check(lib.f2c_set_tuning({"vec": 0, "inflight": 1, "lut": 2, "ctas_per_sm": 3}[key], int(value)))
 
 
 # ------------------------------------------------------------------ neighbour sampling
