@@ -512,7 +512,7 @@ static int pick_u(const SqParams& p, bool vec_store, cudaStream_t st) {
 template <int BITS, typename IdxT>
 static int dispatch_fast(const SqParams& p, int vec, bool lut, bool vec_store, cudaStream_t st) {
   constexpr bool CAN_LUT = BITS <= 8;
-  constexpr bool CAN_8 = BITS != 1;  // 1-bit: 4 bytes per lane already are 32 columns
+  constexpr bool CAN_8 = BITS > 2;  // 1/2-bit: 4 bytes per lane already are 32 / 16 columns
   if constexpr (CAN_LUT) if (lut) {
     if constexpr (CAN_8) if (vec == 8) return pick_u<BITS, 8, IdxT, DEC_LUT>(p, vec_store, st);
     return pick_u<BITS, 4, IdxT, DEC_LUT>(p, vec_store, st);
@@ -529,7 +529,9 @@ static int launch_sq_spmm(const void* codes, int code_dtype, const float* codebo
   const int code_bytes = dtype_size(code_dtype);
   const int64_t row_bytes = src_dim * code_bytes;
   // ---- can the vector kernel serve this shape? ----
-  constexpr int VMAX = BITS == 1 ? 4 : 8;  // two register sets of U rows: at most two words per row, EPL <= 32
+  // bytes per lane per row: at most two words (two register sets of U rows are live) and at most 32 columns;
+  // measured on B200: 8 bytes for 4/8/16-bit codes, 4 bytes for 1/2-bit codes
+  constexpr int VMAX = BITS <= 2 ? 4 : 8;
   int vec = 0;
   for (int v = VMAX; v >= 4; v >>= 1)
     if (row_bytes % v == 0 && aligned(codes, v) && row_bytes <= 32 * v) { vec = v; break; }
