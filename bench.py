@@ -37,6 +37,9 @@ BITS = (1, 2, 4)
 COLUMN_SLICE = 128
 N_MINIBATCHES = 6
 METRIC = "fused_sq_decompress_spmm_sampled_edges_per_s"
+# dram__bytes_read.sum + dram__bytes_write.sum per launch on this block, from one ncu capture per width
+# (profiles/sq_spmm_bench_block.md); below the algorithmic bytes because the output is still dirty in L2 at kernel end
+NCU_DRAM_TRAFFIC_BYTES = {1: 34.9e6, 2: 43.1e6, 4: 48.5e6}
 
 
 def algorithmic_bytes(n_edges, n_dst, row_bytes, idx_bytes, feat_dim, codebook_bytes):
@@ -111,9 +114,79 @@ def build_workload(device, rank, world):
         seeds = torch.randperm(NUM_NODES, generator=g, device=device)[:BATCH]
         blk = synth.sample_blocks(indptr, indices, seeds, FAN_OUT, rng_seed=rank * 1000 + b)[0]
         blocks.append((blk["indptr"].contiguous(), blk["indices_global"].contiguous()))
+        if world > 1:  # what the sharded modes need: the block's distinct source rows and block-local ids
+            BLOCK_EXTRA.append((blk["src_nodes"].contiguous(), blk["indices_local"].contiguous()))
     del indptr, indices
     torch.cuda.empty_cache()
     return tables, blocks
+
+
+BLOCK_EXTRA = []
+
+
+def time_steps(step_fn, blocks, steps, warmup, flush, torch):
+    """Per-step CUDA events on the current stream; returns (list of step ms, edges done)."""
+    for w in range(warmup):
+        step_fn(w % len(blocks))
+        flush.sum()
+    torch.cuda.synchronize()
+    ms, edges = [], 0
+    for s in range(steps):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda._sleep(250_000)
+        a.record()
+        step_fn(s % len(blocks))
+        b.record()
+        flush.sum()
+        torch.cuda.synchronize()
+        ms.append(a.elapsed_time(b))
+        edges += blocks[s % len(blocks)][1].numel() * len(BITS)
+    return ms, edges
+
+
+def multi_gpu_modes(args, capi, tables, blocks, flush, device, rank, world, torch, dist):
+    """Row-sharded table at N > 1: NCCL all-to-all fetch (what the task statement describes) and direct peer loads."""
+    from f2cgt_b200 import ops, shard
+    out = {}
+    lo, hi = shard.shard_bounds(NUM_NODES, world, rank)
+    shards = {b: tables[b][0][lo:hi].contiguous() for b in BITS}
+    # --- peer loads: every rank maps the other shards (CUDA IPC) and the kernel reads remote rows itself
+    try:
+        peers = {b: shard.PeerTable(shards[b], NUM_NODES) for b in BITS}
+
+        def step_peer(i):
+            ip, ix = blocks[i]
+            for b in BITS:
+                ops.sq_decompress_spmm_csr_peer(peers[b], tables[b][1], ip, ix, b, COLUMN_SLICE, FEAT_DIM)
+        ms, edges = time_steps(step_peer, blocks, args.steps, args.warmup, flush, torch)
+        out["sharded_peer_loads"] = (sum(ms), edges)
+        # one-off check against the replicated table
+        ip, ix = blocks[0]
+        a = ops.sq_decompress_spmm_csr_peer(peers[4], tables[4][1], ip, ix, 4, COLUMN_SLICE, FEAT_DIM)
+        bref = capi.sq_decompress_spmm_csr(tables[4][0], tables[4][1], ip, ix, 4, COLUMN_SLICE, FEAT_DIM)
+        assert torch.equal(a, bref), "peer-load result differs from the replicated table"
+    except Exception as e:  # noqa: BLE001
+        out["sharded_peer_loads_error"] = repr(e)[:300]
+    # --- NCCL all-to-all: owners gather rows, rows are exchanged, the kernel runs on block-local rows
+    try:
+        st = {b: shard.ShardedTable(shards[b], NUM_NODES) for b in BITS}
+        plans = [st[BITS[0]].plan(src) for src, _ in BLOCK_EXTRA]  # id exchange happens when the block is sampled
+
+        def step_a2a(i):
+            ip, _ = blocks[i]
+            _, ix_local = BLOCK_EXTRA[i]
+            for b in BITS:
+                rows = st[b].fetch_rows(plans[i])
+                capi.sq_decompress_spmm_csr(rows, tables[b][1], ip, ix_local, b, COLUMN_SLICE, FEAT_DIM)
+        ms, edges = time_steps(step_a2a, blocks, args.steps, args.warmup, flush, torch)
+        out["sharded_nccl_all_to_all"] = (sum(ms), edges)
+        rows = st[4].fetch_rows(plans[0])
+        a = capi.sq_decompress_spmm_csr(rows, tables[4][1], blocks[0][0], BLOCK_EXTRA[0][1], 4, COLUMN_SLICE, FEAT_DIM)
+        bref = capi.sq_decompress_spmm_csr(tables[4][0], tables[4][1], blocks[0][0], blocks[0][1], 4, COLUMN_SLICE, FEAT_DIM)
+        assert torch.equal(a, bref), "all-to-all result differs from the replicated table"
+    except Exception as e:  # noqa: BLE001
+        out["sharded_nccl_all_to_all_error"] = repr(e)[:300]
+    return out
 
 
 def run_ours(args):
@@ -209,11 +282,24 @@ def run_ours(args):
 
     # ---- aggregate over ranks: max time, summed edges
     stats = torch.tensor([total_ms, e2e_s, float(edges_done), float(e2e_edges)], dtype=torch.float64, device=device)
+    modes = {}
     if world > 1:
         mx = stats.clone(); dist.all_reduce(mx, op=dist.ReduceOp.MAX)
         sm = stats.clone(); dist.all_reduce(sm, op=dist.ReduceOp.SUM)
         total_ms, e2e_s = float(mx[0]), float(mx[1])
         edges_all, e2e_edges_all = float(sm[2]), float(sm[3])
+        modes["replicated"] = edges_all / (total_ms * 1e-3)
+        raw = multi_gpu_modes(args, capi, tables, blocks, flush, device, rank, world, torch, dist)
+        for name in ("sharded_peer_loads", "sharded_nccl_all_to_all"):
+            ok = torch.tensor([1.0 if name in raw else 0.0], dtype=torch.float64, device=device)
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+            if float(ok[0]) == 1.0:
+                t = torch.tensor([raw[name][0]], dtype=torch.float64, device=device)
+                e = torch.tensor([float(raw[name][1])], dtype=torch.float64, device=device)
+                dist.all_reduce(t, op=dist.ReduceOp.MAX); dist.all_reduce(e, op=dist.ReduceOp.SUM)
+                modes[name] = float(e[0]) / (float(t[0]) * 1e-3)
+            elif rank == 0 and name + "_error" in raw:
+                modes[name + "_error"] = raw[name + "_error"]
     else:
         edges_all, e2e_edges_all = float(edges_done), float(e2e_edges)
 
@@ -238,14 +324,15 @@ def run_ours(args):
                        "edges_per_block": int(n_edges), "dst_rows_per_block": int(n_dst), "index_dtype": "int64",
                        "gather": "global ids into the HBM-resident table", "minibatches_rotated": len(blocks),
                        "l2": "256 MiB read sweep between steps (outside the step's event pair) evicts L2; tables 39/78/157 MB",
-                       "table": "replicated per GPU", "timing": "CUDA events on the launching stream, max over ranks"},
+                       "table": "replicated per GPU (157 MB at 4 bits); the row-sharded placements are timed beside it at N>1 "
+                                "and reported in table_placements_edges_per_s", "timing": "CUDA events on the launching stream, max over ranks"},
             "roofline": {"bound": "hbm", "kernel": "sq_spmm_kernel<4-bit>", "achieved": dom["gbs"], "peak": peak, "unit": "GB/s",
-                         "frac": dom["frac_of_peak"], "traffic": None, "peak_source": f"MEASURED_PEAKS.json hbm_gbs ({peak_kind})"},
+                         "frac": dom["frac_of_peak"], "traffic": NCU_DRAM_TRAFFIC_BYTES[4], "traffic_unit": "bytes/launch (ncu dram read+write, profiles/sq_spmm_bench_block.md)", "algorithmic_bytes": dom["algorithmic_bytes"], "peak_source": f"MEASURED_PEAKS.json hbm_gbs ({peak_kind})"},
             "variants": variants,
             "e2e": {"value": e2e_edges_all / e2e_s, "unit": "edges/s", "h2d_bytes_per_step": h2d // e2e_steps,
                     "d2h_bytes_per_step": d2h // e2e_steps, "steps": e2e_steps,
                     "what": "pinned-host CSC -> device, 3 fused launches via F2CGTLib, aggregated rows -> pinned host"},
-            "gpu_launches": args.steps * len(BITS),
+            "gpu_launches": args.steps * len(BITS), "table_placements_edges_per_s": modes,
             "clocks": clocks, "wall_s_timed_region": wall,
         }
         if world == 1 and not args.no_cpu_baseline:

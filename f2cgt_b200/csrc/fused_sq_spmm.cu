@@ -55,6 +55,12 @@ template <> struct VecLoad<8> {
 enum { DEC_ARITH = 0, DEC_LUT = 1 };
 enum { CODE_U8 = 0, CODE_I8 = 1, CODE_I16 = 2 };
 
+struct PeerInfo {
+  const void* shard[8];
+  int world;
+  int64_t rows_per_shard;
+};
+
 struct SqParams {
   const uint8_t* codes;
   const float* codebooks;
@@ -69,6 +75,10 @@ struct SqParams {
   int logG;
   int code_kind;
   int reduce;
+  // row-sharded table (PEER kernels): row r lives on shard r / rows_per_shard, all shards mapped into this process
+  const uint8_t* shard[8];
+  uint32_t rows_per_shard;
+  unsigned long long shard_magic;  // floor(2^64 / rows_per_shard) + 1: exact 32-bit division by one multiply-high
   int staged;        // 1: rows leave through the shared-memory staging area (feat_dim % 4 == 0)
   int stage_offset;  // byte offset of that area in dynamic shared memory
   DropoutArgs drop;
@@ -183,7 +193,9 @@ __device__ __forceinline__ void sq_accumulate(AccT& acc, const VecLoad<VEC>& dat
 }
 
 // U = neighbours held in registers per destination row (rows with more take extra, unpipelined rounds).
-template <int BITS, int VEC, int U, typename IdxT, int DEC>
+// PEER: the table is row-sharded over the GPUs of one NVSwitch box and every shard is mapped into this process;
+// a neighbour's row is read from its owner's HBM with an ordinary load over NVLink (no collective, no staging copy).
+template <int BITS, int VEC, int U, typename IdxT, int DEC, bool PEER = false>
 __global__ void __launch_bounds__(256, 2) sq_spmm_kernel(const SqParams p) {
   constexpr int EPL = BITS == 16 ? VEC / 2 : VEC * 8 / BITS;  // output columns per lane
   constexpr bool PACKED = DEC == DEC_LUT && BITS <= 4;
@@ -257,6 +269,13 @@ __global__ void __launch_bounds__(256, 2) sq_spmm_kernel(const SqParams p) {
   const int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int64_t stride = (((int64_t)gridDim.x * blockDim.x) >> 5) * rows_per_warp;
   const uint8_t* __restrict__ my_codes = p.codes + byte0;
+  // address of this lane's slice of source row `id`
+  auto row_ptr = [&](uint32_t id) -> const uint8_t* {
+    if (!PEER) return my_codes + (uint64_t)id * p.row_bytes;
+    const uint32_t owner = (uint32_t)__umul64hi((unsigned long long)id, p.shard_magic);
+    const uint32_t local = id - owner * p.rows_per_shard;
+    return p.shard[owner] + byte0 + (uint64_t)local * p.row_bytes;
+  };
 
   // ---- three-deep software pipeline over the rows d, d+stride, d+2*stride, ... of this lane group.
   // Rows are counted in 32 bits (the host checks n_dst < 2^31).
@@ -284,7 +303,7 @@ __global__ void __launch_bounds__(256, 2) sq_spmm_kernel(const SqParams p) {
   for (int u = 0; u < U; ++u) {
 #pragma unroll
     for (int w = 0; w < VEC / 4; ++w) data[0][u].w[w] = 0u;
-    if (u < degA) data[0][u].load(my_codes + (uint64_t)nidx[u] * p.row_bytes);
+    if (u < degA) data[0][u].load(row_ptr(nidx[u]));
   }
 #pragma unroll
   for (int u = 0; u < U; ++u) nidx[u] = u < degB ? (uint32_t)idsB[u] : 0u;
@@ -301,7 +320,7 @@ __global__ void __launch_bounds__(256, 2) sq_spmm_kernel(const SqParams p) {
         for (int u = 0; u < U; ++u) {
 #pragma unroll
           for (int w = 0; w < VEC / 4; ++w) data[P ^ 1][u].w[w] = 0u;
-          if (u < degB) data[P ^ 1][u].load(my_codes + (uint64_t)nidx[u] * p.row_bytes);
+          if (u < degB) data[P ^ 1][u].load(row_ptr(nidx[u]));
         }
         // (2) neighbour ids of the row after it
 #pragma unroll
@@ -334,7 +353,7 @@ __global__ void __launch_bounds__(256, 2) sq_spmm_kernel(const SqParams p) {
           VecLoad<VEC> extra[4];
 #pragma unroll
           for (int u = 0; u < 4; ++u)
-            if (k + u < degA) extra[u].load(my_codes + (uint64_t)(uint32_t)idsA[k + u] * p.row_bytes);
+            if (k + u < degA) extra[u].load(row_ptr((uint32_t)idsA[k + u]));
 #pragma unroll
           for (int u = 0; u < 4; ++u)
             if (k + u < degA) sq_accumulate<BITS, VEC, DEC>(acc, extra[u], table, lane_off, p.code_kind, scale, emin, mean);
@@ -462,9 +481,9 @@ __global__ void __launch_bounds__(256) sq_spmm_generic_kernel(const void* __rest
 
 static int ilog2(int v) { int l = 0; while ((1 << l) < v) ++l; return l; }
 
-template <int BITS, int VEC, int U, typename IdxT, int DEC>
+template <int BITS, int VEC, int U, typename IdxT, int DEC, bool PEER = false>
 static int launch_fast(SqParams p, bool vec_store, cudaStream_t st) {
-  auto kern = sq_spmm_kernel<BITS, VEC, U, IdxT, DEC>;
+  auto kern = sq_spmm_kernel<BITS, VEC, U, IdxT, DEC, PEER>;
   constexpr int EPL = BITS == 16 ? VEC / 2 : VEC * 8 / BITS;
   // decode table (64 KB) + the decoded code values of each distinct codebook row
   size_t smem = 0;
@@ -524,7 +543,7 @@ static int dispatch_fast(const SqParams& p, int vec, bool lut, bool vec_store, c
 template <int BITS, typename IdxT>
 static int launch_sq_spmm(const void* codes, int code_dtype, const float* codebooks, int64_t n_cb, const void* indptr,
                           const void* indices, float* out, int64_t n_dst, int64_t n_src, int64_t src_dim, int64_t D, int64_t cs,
-                          int reduce, const DropoutArgs& drop, cudaStream_t st) {
+                          int reduce, const DropoutArgs& drop, cudaStream_t st, const PeerInfo* peer = nullptr) {
   if (n_dst == 0 || D == 0) return F2C_OK;
   const int code_bytes = dtype_size(code_dtype);
   const int64_t row_bytes = src_dim * code_bytes;
@@ -554,8 +573,19 @@ static int launch_sq_spmm(const void* codes, int code_dtype, const float* codebo
     // table copies are shared by lanes l and l + COPIES: they must own the same columns
     int copies = BITS >= 4 ? 32 : BITS == 2 ? 16 : 8;
     bool lut = (n_cb == 1 || copies % G == 0) && g_tune_lut != 0;
+    if (peer != nullptr) {
+      for (int r = 0; r < 8; ++r) p.shard[r] = (const uint8_t*)peer->shard[r < peer->world ? r : 0];
+      p.rows_per_shard = (uint32_t)peer->rows_per_shard;
+      p.shard_magic = ~0ull / (unsigned long long)peer->rows_per_shard + 1ull;
+      constexpr int DEC = BITS <= 8 ? DEC_LUT : DEC_ARITH;
+      if (vec != VMAX || (BITS <= 8 && !lut))
+        return set_error(F2C_ERR_UNSUPPORTED, "sq_decompress_spmm_csr_peer: shape or codebook layout not served by the peer kernel");
+      return launch_fast<BITS, VMAX, 12, IdxT, DEC, true>(p, D % 4 == 0 && aligned(out, 16), st);
+    }
     return dispatch_fast<BITS, IdxT>(p, vec, lut, D % 4 == 0 && aligned(out, 16), st);
   }
+  if (peer != nullptr)
+    return set_error(F2C_ERR_UNSUPPORTED, "sq_decompress_spmm_csr_peer: shape not served by the peer kernel");
   int64_t blocks = ceil_div(n_dst, 8);
   if (blocks > kSmCount * 32) blocks = kSmCount * 32;
 #define F2C_GEN(T) sq_spmm_generic_kernel<BITS, T, IdxT><<<(unsigned)blocks, 256, 0, st>>>( \
@@ -602,6 +632,49 @@ extern "C" int f2c_sq_spmm_csr(const void* codes, int code_dtype, const float* c
     default: F2C_SQ(16);
   }
 #undef F2C_SQ
+}
+
+extern "C" int f2c_sq_spmm_csr_peer(const void* const* shard_ptrs_host, int world, int64_t rows_per_shard, int code_dtype,
+                                    const float* codebooks, int64_t n_codebooks, const void* indptr, const void* indices,
+                                    int index_dtype, float* out, int64_t n_dst, int64_t n_src, int64_t src_dim,
+                                    int64_t feat_dim, int bits, int64_t column_slice, int reduce,
+                                    const f2c_epilogue* epilogue, void* stream) {
+  const char* op = "sq_decompress_spmm_csr_peer";
+  F2C_REQUIRE(n_dst >= 0 && n_src >= 0, F2C_ERR_INVALID, "%s: negative size", op);
+  F2C_REQUIRE(world >= 1 && world <= 8, F2C_ERR_LIMIT, "%s: 1 to 8 shards (got %d)", op, world);
+  F2C_REQUIRE(rows_per_shard >= 2 && rows_per_shard < (1ll << 32) && rows_per_shard * world >= n_src, F2C_ERR_INVALID,
+              "%s: %d shards of %lld rows do not cover %lld rows", op, world, (long long)rows_per_shard, (long long)n_src);
+  F2C_REQUIRE(shard_ptrs_host != nullptr, F2C_ERR_INVALID, "%s: null pointer", op);
+  int rc = validate_sq(op, code_dtype, n_codebooks, src_dim, feat_dim, bits, column_slice);
+  if (rc) return rc;
+  F2C_REQUIRE(is_index_dtype(index_dtype), F2C_ERR_UNSUPPORTED, "%s: indptr/indices must be int32 or int64", op);
+  F2C_REQUIRE(reduce == F2C_MEAN || reduce == F2C_SUM, F2C_ERR_INVALID, "%s: reduce must be mean or sum", op);
+  F2C_REQUIRE(bits >= 8 || n_codebooks == 1 || column_slice % (8 / bits) == 0, F2C_ERR_INVALID,
+              "%s: column_slice (%lld) must be a multiple of %d for %d-bit codes", op, (long long)column_slice, 8 / bits, bits);
+  F2C_REQUIRE(n_dst * feat_dim == 0 || (indptr && out && codebooks), F2C_ERR_INVALID, "%s: null pointer", op);
+  PeerInfo peer{};
+  for (int r = 0; r < world; ++r) {
+    F2C_REQUIRE(shard_ptrs_host[r] != nullptr, F2C_ERR_INVALID, "%s: shard %d is null", op, r);
+    peer.shard[r] = shard_ptrs_host[r];
+  }
+  peer.world = world;
+  peer.rows_per_shard = rows_per_shard;
+  DropoutArgs drop = make_dropout(epilogue);
+  cudaStream_t st = (cudaStream_t)stream;
+#define F2C_SQP(B)                                                                                                       \
+  return index_dtype == F2C_I32                                                                                          \
+             ? launch_sq_spmm<B, int32_t>(peer.shard[0], code_dtype, codebooks, n_codebooks, indptr, indices, out, n_dst, \
+                                          n_src, src_dim, feat_dim, column_slice, reduce, drop, st, &peer)              \
+             : launch_sq_spmm<B, int64_t>(peer.shard[0], code_dtype, codebooks, n_codebooks, indptr, indices, out, n_dst, \
+                                          n_src, src_dim, feat_dim, column_slice, reduce, drop, st, &peer)
+  switch (bits) {
+    case 1: F2C_SQP(1);
+    case 2: F2C_SQP(2);
+    case 4: F2C_SQP(4);
+    case 8: F2C_SQP(8);
+    default: F2C_SQP(16);
+  }
+#undef F2C_SQP
 }
 
 // Experiment knobs of the fused SQ kernel (no counterpart in the reference).  key 0: bytes per lane per

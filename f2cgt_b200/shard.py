@@ -1,0 +1,134 @@
+"""Row-sharded compressed table on one NVSwitch box: rank r owns rows [r*rows_per_rank, (r+1)*rows_per_rank).
+
+Two ways to aggregate a block whose source rows live on other GPUs:
+
+* ``ShardedTable.fetch(ids)`` - the exchange the reference never needed (it keeps one pinned replica per machine,
+  examples/load_dataset.py:63-85): ids are bucketed by owner, exchanged, the owners gather their rows, and the rows
+  are exchanged back, all as point-to-point operations grouped into one NCCL all-to-all
+  (``dist.batch_isend_irecv``; the same code runs over gloo on CPU, which is how the tests cover it).
+  The fused kernel then runs on the fetched, block-local rows.
+* ``PeerTable`` - every rank maps the other ranks' shards through CUDA IPC and the fused kernel reads remote rows
+  itself with ordinary loads over NVLink (``f2c_sq_spmm_csr_peer``): no collective, no host synchronisation.
+
+Host logic only; all arithmetic is in the CUDA library.
+"""
+import torch
+import torch.distributed as dist
+
+
+def rows_per_rank(n_rows, world):
+    return (n_rows + world - 1) // world
+
+
+def shard_bounds(n_rows, world, rank):
+    rpr = rows_per_rank(n_rows, world)
+    return min(rank * rpr, n_rows), min((rank + 1) * rpr, n_rows)
+
+
+def bucket_by_owner(ids, rpr, world):
+    """Stable bucketing of global row ids by owning rank.
+
+    Returns (order, sorted_ids, counts): ids[order] == sorted_ids is grouped by owner, counts[r] ids go to rank r."""
+    owner = torch.div(ids, rpr, rounding_mode="floor")
+    order = torch.argsort(owner, stable=True)
+    counts = torch.bincount(owner, minlength=world)[:world]
+    return order, ids[order], counts
+
+
+def _exchange(send, send_counts, recv_counts, group):
+    """Variable-size all-to-all of the leading dimension as one group of point-to-point operations."""
+    world = dist.get_world_size(group)
+    rank = dist.get_rank(group)
+    recv = send.new_empty((int(sum(recv_counts)),) + tuple(send.shape[1:]))
+    s_off = [0]
+    r_off = [0]
+    for r in range(world):
+        s_off.append(s_off[-1] + int(send_counts[r]))
+        r_off.append(r_off[-1] + int(recv_counts[r]))
+    ops = []
+    for r in range(world):
+        if r == rank:
+            recv[r_off[r]:r_off[r + 1]].copy_(send[s_off[r]:s_off[r + 1]])
+            continue
+        if recv_counts[r] > 0:
+            ops.append(dist.P2POp(dist.irecv, recv[r_off[r]:r_off[r + 1]], dist.get_global_rank(group, r) if group else r, group))
+        if send_counts[r] > 0:
+            ops.append(dist.P2POp(dist.isend, send[s_off[r]:s_off[r + 1]].contiguous(), dist.get_global_rank(group, r) if group else r, group))
+    if ops:
+        for w in dist.batch_isend_irecv(ops):
+            w.wait()
+    return recv
+
+
+class ShardedTable:
+    """One rank's shard of a [n_rows, row_width] table plus the row fetch over the process group."""
+
+    def __init__(self, local_rows, n_rows, group=None):
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.n_rows = int(n_rows)
+        self.rpr = rows_per_rank(self.n_rows, self.world)
+        lo, hi = shard_bounds(self.n_rows, self.world, self.rank)
+        if local_rows.shape[0] != hi - lo:
+            raise ValueError(f"rank {self.rank} must hold rows [{lo}, {hi}) - got {local_rows.shape[0]} rows")
+        self.local = local_rows
+        self.lo = lo
+
+    def plan(self, ids):
+        """Everything about a fetch that depends only on the ids (can be computed when the block is sampled):
+        bucketing, the count exchange and the id exchange.  Returns a dict consumed by ``fetch_rows``."""
+        if ids.numel() and (int(ids.min()) < 0 or int(ids.max()) >= self.n_rows):
+            raise IndexError("row id outside the table")
+        order, sorted_ids, counts = bucket_by_owner(ids, self.rpr, self.world)
+        send_counts = counts.to("cpu").tolist()
+        all_counts = [None] * self.world
+        dist.all_gather_object(all_counts, send_counts, group=self.group)
+        recv_counts = [all_counts[r][self.rank] for r in range(self.world)]
+        wanted = _exchange(sorted_ids, send_counts, recv_counts, self.group)  # ids other ranks want from this shard
+        return dict(order=order, send_counts=send_counts, recv_counts=recv_counts, local_index=wanted - self.lo)
+
+    def fetch_rows(self, plan):
+        """Owner-side gather + row exchange; returns the rows in the order of the ids given to ``plan``."""
+        rows = self.local.index_select(0, plan["local_index"])
+        got = _exchange(rows, plan["recv_counts"], plan["send_counts"], self.group)
+        out = torch.empty_like(got)
+        out[plan["order"]] = got
+        return out
+
+    def fetch(self, ids):
+        return self.fetch_rows(self.plan(ids))
+
+
+class PeerTable:
+    """Shards of all ranks mapped into this process through CUDA IPC (plain peer mappings, no multicast).
+
+    ``ptrs`` is a device tensor of ``world`` uint64 base addresses, ``tensors`` keeps the mappings alive.  Every
+    rank must construct it collectively; the local shard must stay allocated as long as any peer uses it."""
+
+    def __init__(self, local_rows, n_rows, group=None):
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.n_rows = int(n_rows)
+        self.rpr = rows_per_rank(self.n_rows, self.world)
+        self.local = local_rows
+        storage = local_rows.untyped_storage()
+        handle = storage._share_cuda_()  # (device, ipc handle, size, offset, ref-counter handle, ...)
+        meta = (handle, tuple(local_rows.shape), local_rows.dtype, local_rows.storage_offset())
+        metas = [None] * self.world
+        dist.all_gather_object(metas, meta, group=self.group)
+        self.tensors = []
+        for r, (h, shape, dtype, offset) in enumerate(metas):
+            if r == self.rank:
+                self.tensors.append(local_rows)
+                continue
+            # h = (owner device, ipc handle, bytes, offset, ref-counter handle, ...): the mapping is opened on the
+            # owner's device ordinal (all GPUs of the box are visible to every rank)
+            st = torch.UntypedStorage._new_shared_cuda(*h)
+            t = torch.empty(0, dtype=dtype, device=torch.device("cuda", h[0])).set_(st, offset, shape)
+            # a first device-to-device copy makes torch enable peer access between the two devices
+            torch.empty(1, dtype=dtype, device=local_rows.device).copy_(t.reshape(-1)[:1])
+            self.tensors.append(t)
+        self.ptrs = torch.tensor([t.data_ptr() for t in self.tensors], dtype=torch.int64, device=local_rows.device)
+        dist.barrier(group=self.group)

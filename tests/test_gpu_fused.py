@@ -261,3 +261,26 @@ def test_runs_on_the_callers_stream(capi):
         got = capi.vq_decompress_spmm_csr(codes, cbs, ip, ix, 128)
     s.synchronize()
     assert torch.equal(got, want)
+
+
+@pytest.mark.parametrize("bits", [1, 2, 4, 8, 16])
+@pytest.mark.parametrize("world", [2, 3, 8])
+def test_peer_sharded_table_equals_whole_table(capi, oracle, bits, world):
+    """The row-sharded entry point with every shard on this GPU (the pointers could as well be peer mappings)."""
+    from f2cgt_b200 import ops, shard
+    rng = np.random.default_rng(bits + world)
+    n_src, n_dst, D = 1003, 400, 128
+    _, cb, stored = sq_table(oracle, rng, n_src, D, bits, 128)
+    indptr, indices = random_csc(rng, n_dst, n_src, max_deg=20)
+    table = dev(stored)
+    rpr = shard.rows_per_rank(n_src, world)
+
+    class FakePeers:  # what shard.PeerTable exposes
+        pass
+    pt = FakePeers()
+    pt.world, pt.rpr, pt.n_rows = world, rpr, n_src
+    pt.tensors = [table[r * rpr:(r + 1) * rpr].clone() if r * rpr < n_src else table[:1].clone() for r in range(world)]
+    pt.local = pt.tensors[0]
+    got = ops.sq_decompress_spmm_csr_peer(pt, dev(cb), dev(indptr), dev(indices), bits, 128, D)
+    want = capi.sq_decompress_spmm_csr(table, dev(cb), dev(indptr), dev(indices), bits, 128, D)
+    assert torch.equal(got, want)

@@ -1,0 +1,74 @@
+"""CPU, two gloo ranks: the row-sharded table fetch (bucketing, count / id / row exchange, un-sorting)."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from f2cgt_b200 import shard
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    return port
+
+
+def _worker(rank, world, port, n_rows, q):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        g = torch.Generator().manual_seed(0)
+        table = torch.randint(0, 256, (n_rows, 16), generator=g, dtype=torch.uint8)  # same on every rank
+        lo, hi = shard.shard_bounds(n_rows, world, rank)
+        st = shard.ShardedTable(table[lo:hi].clone(), n_rows)
+        g2 = torch.Generator().manual_seed(100 + rank)
+        for n_ids in (0, 1, 257, 5000):
+            ids = torch.randint(0, n_rows, (n_ids,), generator=g2)  # duplicates and any order
+            rows = st.fetch(ids)
+            assert rows.shape == (n_ids, 16) and torch.equal(rows, table[ids])
+        # every id on one remote rank, and an id outside the table
+        other = (rank + 1) % world
+        olo, ohi = shard.shard_bounds(n_rows, world, other)
+        ids = torch.arange(olo, ohi)
+        assert torch.equal(st.fetch(ids), table[ids])
+        try:
+            st.plan(torch.tensor([n_rows]))
+            ok = False
+        except IndexError:
+            ok = True
+        assert ok
+        q.put((rank, "ok"))
+    except Exception as e:  # noqa: BLE001
+        q.put((rank, repr(e)))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("n_rows", [1001, 64])
+def test_sharded_fetch_two_ranks(n_rows):
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, n_rows, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    results = [q.get(timeout=120) for _ in procs]
+    for p in procs:
+        p.join(timeout=60)
+    assert sorted(results) == [(0, "ok"), (1, "ok")], results
+
+
+def test_bucketing_is_stable_and_complete():
+    ids = torch.tensor([5, 900, 3, 450, 901, 4, 0])
+    order, sorted_ids, counts = shard.bucket_by_owner(ids, 300, 4)
+    assert counts.tolist() == [4, 1, 0, 2]
+    assert sorted_ids.tolist() == [5, 3, 4, 0, 450, 900, 901]  # grouped by owner, original order kept inside a group
+    assert torch.equal(ids[order], sorted_ids)
+    assert shard.shard_bounds(1001, 2, 0) == (0, 501) and shard.shard_bounds(1001, 2, 1) == (501, 1001)
+    assert shard.shard_bounds(10, 4, 3) == (9, 10)
