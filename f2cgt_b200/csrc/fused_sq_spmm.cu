@@ -41,6 +41,7 @@ int validate_sq(const char* op, int code_dtype, int64_t n_codebooks, int64_t src
 
 // experiment knobs (0 = built-in choice), set through f2c_set_tuning
 int g_tune_vec = 0, g_tune_u = 0, g_tune_lut = -1, g_tune_ctas_per_sm = 0;
+extern int g_kmeans_force_exact;
 
 template <int VEC> struct VecLoad;
 template <> struct VecLoad<4> {
@@ -686,6 +687,7 @@ extern "C" int f2c_set_tuning(int key, int value) {
     case 1: g_tune_u = value; break;
     case 2: g_tune_lut = value; break;
     case 3: g_tune_ctas_per_sm = value; break;
+    case 10: g_kmeans_force_exact = value; break;
     default: return set_error(F2C_ERR_INVALID, "set_tuning: unknown key %d", key);
   }
   return F2C_OK;

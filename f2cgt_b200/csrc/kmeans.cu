@@ -71,8 +71,14 @@ __global__ void __launch_bounds__(256) kmeans_warp_kernel(const float* __restric
 template <int DMAX, int METRIC>
 __global__ void __launch_bounds__(256) kmeans_thread_kernel(const float* __restrict__ x, const float* __restrict__ y,
                                                             int64_t* __restrict__ labels, const int32_t* __restrict__ subset,
-                                                            int64_t n, int k, int d, int kc) {
+                                                            const int32_t* __restrict__ count_dev, int64_t n, int k, int d, int kc) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
+  // count_dev != nullptr: the number of listed points is only known on the device; surplus blocks leave at once
+  if (count_dev != nullptr) {
+    const int64_t cnt = *count_dev;
+    if ((int64_t)blockIdx.x * blockDim.x >= cnt) return;
+    n = cnt < n ? cnt : n;
+  }
   float* yc_s = reinterpret_cast<float*>(smem_raw);  // [kc][DMAX]
   float* cc_s = yc_s + (size_t)kc * DMAX;            // [kc]
   const int64_t slot = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -128,7 +134,7 @@ __global__ void __launch_bounds__(256) kmeans_thread_kernel(const float* __restr
 
 template <int DMAX>
 static int launch_thread_assign(const float* x, const float* y, int64_t* labels, const int32_t* subset, int64_t n, int64_t k,
-                                int64_t d, int metric, cudaStream_t st) {
+                                int64_t d, int metric, cudaStream_t st, const int32_t* count_dev = nullptr) {
   int kc = (int)k;
   const size_t budget = 96 * 1024;
   while ((size_t)kc * (DMAX + 1) * sizeof(float) > budget) kc = (kc + 1) / 2;
@@ -138,11 +144,11 @@ static int launch_thread_assign(const float* x, const float* y, int64_t* labels,
   if (metric == F2C_COSINE) {
     auto kern = kmeans_thread_kernel<DMAX, F2C_COSINE>;
     e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e == cudaSuccess) kern<<<grid, 256, smem, st>>>(x, y, labels, subset, n, (int)k, (int)d, kc);
+    if (e == cudaSuccess) kern<<<grid, 256, smem, st>>>(x, y, labels, subset, count_dev, n, (int)k, (int)d, kc);
   } else {
     auto kern = kmeans_thread_kernel<DMAX, F2C_L2>;
     e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e == cudaSuccess) kern<<<grid, 256, smem, st>>>(x, y, labels, subset, n, (int)k, (int)d, kc);
+    if (e == cudaSuccess) kern<<<grid, 256, smem, st>>>(x, y, labels, subset, count_dev, n, (int)k, (int)d, kc);
   }
   if (e != cudaSuccess) return set_error(F2C_ERR_CUDA, "kmeans_assign: %s", cudaGetErrorString(e));
   return check_launch("kmeans_assign");
@@ -166,6 +172,24 @@ int kmeans_assign_exact(const float* x, const float* y, int64_t* labels, const i
     kmeans_warp_kernel<F2C_L2, false, true><<<(unsigned)blocks, 256, 0, st>>>(x, y, nullptr, labels, n, (int)k, (int)d);
   return check_launch("kmeans_assign");
 }
+
+// Exact assignment of the points listed in `list`; their number sits in device memory (*count_dev <= max_count).
+int kmeans_assign_exact_listed(const float* x, const float* y, int64_t* labels, const int32_t* list, const int32_t* count_dev,
+                               int64_t max_count, int64_t k, int64_t d, int metric, cudaStream_t st) {
+  if (max_count == 0) return F2C_OK;
+  if (d <= 8) return launch_thread_assign<8>(x, y, labels, list, max_count, k, d, metric, st, count_dev);
+  if (d <= 16) return launch_thread_assign<16>(x, y, labels, list, max_count, k, d, metric, st, count_dev);
+  if (d <= 32) return launch_thread_assign<32>(x, y, labels, list, max_count, k, d, metric, st, count_dev);
+  if (d <= 64) return launch_thread_assign<64>(x, y, labels, list, max_count, k, d, metric, st, count_dev);
+  if (d <= 128) return launch_thread_assign<128>(x, y, labels, list, max_count, k, d, metric, st, count_dev);
+  return set_error(F2C_ERR_UNSUPPORTED, "kmeans_assign: listed re-scoring needs d <= 128");
+}
+
+bool kmeans_tc_supported(int64_t n, int64_t k, int64_t d);
+int64_t kmeans_tc_workspace(int64_t n);
+int kmeans_assign_tc(const float* x, const float* y, int64_t* labels, int64_t n, int64_t k, int64_t d, int metric, void* workspace,
+                     cudaStream_t st);
+int g_kmeans_force_exact = 0;  // experiment / test switch (f2c_set_tuning key 10)
 
 static int validate_km(const char* op, int64_t n, int64_t k, int64_t d, int metric) {
   F2C_REQUIRE(n >= 0 && k >= 1 && d >= 1, F2C_ERR_INVALID, "%s: bad shape n=%lld k=%lld d=%lld", op, (long long)n, (long long)k,
@@ -196,16 +220,17 @@ extern "C" int f2c_pairwise_distance(const float* x, const float* y, float* dist
 }
 
 extern "C" int64_t f2c_kmeans_assign_workspace(int64_t n, int64_t k, int64_t d) {
-  (void)n; (void)k; (void)d;
-  return 0;
+  return kmeans_tc_supported(n, k, d) ? kmeans_tc_workspace(n) : 0;
 }
 
 extern "C" int f2c_kmeans_assign(const float* x, const float* centers, int64_t* labels, int64_t n, int64_t k, int64_t d,
                                  int metric, void* workspace, void* stream) {
-  (void)workspace;
   int rc = validate_km("kmeans_assign", n, k, d, metric);
   if (rc) return rc;
   if (n == 0) return F2C_OK;
   F2C_REQUIRE(x && centers && labels, F2C_ERR_INVALID, "kmeans_assign: null pointer");
+  // tensor-core path when a scratch buffer is supplied and the shape fits; the exact fp32 scorer otherwise
+  if (workspace != nullptr && kmeans_tc_supported(n, k, d) && !g_kmeans_force_exact && aligned(workspace, 16))
+    return kmeans_assign_tc(x, centers, labels, n, k, d, metric, workspace, (cudaStream_t)stream);
   return kmeans_assign_exact(x, centers, labels, nullptr, n, k, d, metric, (cudaStream_t)stream);
 }

@@ -298,6 +298,12 @@ def kmeans_assign(x, centers, metric):
     with _on(x):
         check(lib.f2c_kmeans_assign(_ptr(x), _ptr(centers), _ptr(labels), n, k, d, _metric(metric), _ptr(ws) if ws is not None else 0,
                                     _stream(x)))
+    if ws is not None:
+        # word 1 of the scratch header is set when the tensor-core kernel gave up on a bounded wait
+        head = ws[:8].view(torch.int32).cpu()
+        if int(head[1]) != 0:
+            raise RuntimeError("f2cgt_b200: kmeans_assign: tensor-core kernel reported a timed-out wait")
+        kmeans_assign.last_undecided = int(head[0])
     return labels
 
 
@@ -357,7 +363,7 @@ class KMeans:
 
 def set_tuning(key, value):
     """Experiment knob of the fused SQ kernel: key in {"vec", "inflight", "lut", "ctas_per_sm"}."""
-    check(lib.f2c_set_tuning({"vec": 0, "inflight": 1, "lut": 2, "ctas_per_sm": 3}[key], int(value)))
+    check(lib.f2c_set_tuning({"vec": 0, "inflight": 1, "lut": 2, "ctas_per_sm": 3, "kmeans_exact": 10}[key], int(value)))
 
 
 # ------------------------------------------------------------------ neighbour sampling

