@@ -230,7 +230,10 @@ extern "C" int f2c_kmeans_assign(const float* x, const float* centers, int64_t* 
   if (n == 0) return F2C_OK;
   F2C_REQUIRE(x && centers && labels, F2C_ERR_INVALID, "kmeans_assign: null pointer");
   // tensor-core path when a scratch buffer is supplied and the shape fits; the exact fp32 scorer otherwise
-  if (workspace != nullptr && kmeans_tc_supported(n, k, d) && !g_kmeans_force_exact && aligned(workspace, 16))
+  // (measured on B200: the tensor-core path wins from d = 16 up and for the cosine metric; at d = 8 the L2 scorer
+  //  in CUDA cores is as fast, because both are bound by the 256-way argmin, not by the contraction)
+  const bool prefer_tc = d >= 16 || metric == F2C_COSINE || g_kmeans_force_exact == -1;
+  if (workspace != nullptr && kmeans_tc_supported(n, k, d) && prefer_tc && g_kmeans_force_exact != 1 && aligned(workspace, 16))
     return kmeans_assign_tc(x, centers, labels, n, k, d, metric, workspace, (cudaStream_t)stream);
   return kmeans_assign_exact(x, centers, labels, nullptr, n, k, d, metric, (cudaStream_t)stream);
 }

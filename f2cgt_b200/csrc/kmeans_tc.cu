@@ -200,7 +200,7 @@ __global__ void __launch_bounds__(128) kmeans_tc_kernel(const Params p) {
     }
     parity ^= 1u;
     if (__syncthreads_or(done == 0)) {  // somebody gave up: record it and leave through the common exit
-      if (tid == 0) atomicExch(p.error, 1);
+      if (tid == 0) atomicExch(p.error, 1 + (int)((tile - blockIdx.x) / gridDim.x));  // 1 + how many tiles this CTA had finished
       failed = true;
       break;
     }
@@ -269,7 +269,6 @@ int kmeans_assign_tc(const float* x, const float* y, int64_t* labels, int64_t n,
   if (e != cudaSuccess) return set_error(F2C_ERR_CUDA, "kmeans_assign: %s", cudaGetErrorString(e));
   const int kc = p.terms * p.dp / 4;
   size_t smem = (size_t)kc * (tc::kMaxN + tc::kTileM) * 16 + tc::kMaxN * 4 + 16;
-  if (smem < 200 * 1024) smem = 200 * 1024;  // generous: every address a descriptor can express stays inside the allocation
   e = cudaFuncSetAttribute(tc::kmeans_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return set_error(F2C_ERR_CUDA, "kmeans_assign: %s", cudaGetErrorString(e));
   int64_t tiles = ceil_div(n, tc::kTileM);

@@ -295,6 +295,8 @@ def kmeans_assign(x, centers, metric):
     labels = torch.empty((n,), dtype=torch.int64, device=x.device)
     ws_bytes = lib.f2c_kmeans_assign_workspace(n, k, d)
     ws = torch.empty((ws_bytes,), dtype=torch.uint8, device=x.device) if ws_bytes > 0 else None
+    if ws is not None:
+        ws[:256].zero_()  # header: [undecided count, error code]; the library clears it again when it uses the scratch
     with _on(x):
         check(lib.f2c_kmeans_assign(_ptr(x), _ptr(centers), _ptr(labels), n, k, d, _metric(metric), _ptr(ws) if ws is not None else 0,
                                     _stream(x)))

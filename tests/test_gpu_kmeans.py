@@ -95,14 +95,16 @@ def test_tensor_core_assignment_equals_exact_fp32_kernel(capi, oracle, metric, n
     if k >= 8:
         c2[k // 2] = c2[1]         # an exact duplicate centre: the lower index must win
     for centers in (c, c2):
-        tc = capi.kmeans_assign(x, centers, metric)
-        undecided = ops.kmeans_assign.last_undecided
         try:
+            ops.set_tuning("kmeans_exact", -1)  # force the tensor-core path whatever the shape heuristic says
+            tc = capi.kmeans_assign(x, centers, metric)
+            undecided = ops.kmeans_assign.last_undecided
             ops.set_tuning("kmeans_exact", 1)
             exact = capi.kmeans_assign(x, centers, metric)
         finally:
             ops.set_tuning("kmeans_exact", 0)
         assert torch.equal(tc, exact), (metric, n, k, d, int((tc != exact).sum()))
         # the split product decides almost everything itself (plain TF32 for d > 32 defers more)
-        assert undecided <= (0.02 if d <= 32 else 0.6) * n + 8 + (n if centers is c2 else 0) * 0.05
+        # (a duplicated centre makes every point that prefers it an exact tie: about 1/k of the points)
+        assert undecided <= (0.02 if d <= 32 else 0.6) * n + 8 + (3.0 * n / k if centers is c2 else 0)
     assert labels_match(oracle, x.cpu().numpy(), c.cpu().numpy(), metric, tc.cpu().numpy()) or True
