@@ -56,6 +56,7 @@ SIGNATURES = {
     "f2c_pairwise_distance": [p, p, p, i64, i64, i64, ci, p],
     "f2c_kmeans_assign_workspace": [i64, i64, i64],
     "f2c_kmeans_assign": [p, p, p, i64, i64, i64, ci, p, p],
+    "f2c_kmeans_assign_static": [p, p, p, i64, i64, i64, ci, p],
     "f2c_check_csc": [p, p, ci, i64, i64, p, p],
     "f2c_set_tuning": [ci, ci],
     "f2c_sample_degrees": [p, p, p, ci, i64, ci, p],

@@ -20,6 +20,8 @@
 // the A tile and TMEM lane t in the epilogue; thread 0 issues the MMAs.  Centres are staged once per
 // persistent CTA.  Every wait on the MMA-completion mbarrier is bounded; on expiry the CTA records
 // an error code, frees its TMEM and returns.
+#include <mutex>
+
 #include "common.cuh"
 
 namespace f2c {
@@ -281,4 +283,61 @@ int kmeans_assign_tc(const float* x, const float* y, int64_t* labels, int64_t n,
   return kmeans_assign_exact_listed(x, y, labels, p.amb_list, p.amb_count, n, k, d, metric, st);
 }
 
+// ------------------------------------------------------------------------------------------------------
+// K-means assignment for callers that cannot allocate device memory.
+//
+// f2c_kmeans_assign leaves the undecided-point list to the caller, which means one device allocation per
+// call (or a buffer the caller has to carry around).  Some callers cannot do that: a data-loader or serving
+// thread that lives inside a process whose framework allocator already owns almost all of HBM (a raw
+// cudaMalloc there can fail, or make the framework drop its cache), and callers on a latency-critical
+// path, where cudaMalloc / cudaFree would stall every stream of the device.  For them the scratch lives in
+// a fixed array in the library's device image: 4 MiB + 256 B on every GPU that loads the library, held until
+// the process exits, enough for kStaticMaxPoints points per call.
+//
+// The array's name below is only a host-side handle; the device address is obtained once per device with
+// cudaGetSymbolAddress while that device is current.  That happens on the first call made on a device, so
+// make that first call outside any stream capture.  All calls on a device share the one array: the header is
+// cleared at the start of every call, the list behind it keeps whatever the previous call left and is only
+// read up to the new count.  Two calls that overlap on the GPU (different streams, or threads) would
+// overwrite each other's list - serialise them.
+namespace tc {
+constexpr int64_t kStaticMaxPoints = 1 << 20;
+static __device__ __align__(256) unsigned char g_static_scratch[256 + 4 * kStaticMaxPoints];
+}  // namespace tc
 }  // namespace f2c
+
+extern "C" int f2c_kmeans_assign_static(const float* x, const float* centers, int64_t* labels, int64_t n, int64_t k,
+                                        int64_t d, int metric, void* stream) {
+  using namespace f2c;
+  const char* op = "kmeans_assign_static";
+  F2C_REQUIRE(n >= 0 && k >= 1 && d >= 1, F2C_ERR_INVALID, "%s: bad shape n=%lld k=%lld d=%lld", op, (long long)n, (long long)k,
+              (long long)d);
+  F2C_REQUIRE(metric == F2C_L2 || metric == F2C_COSINE, F2C_ERR_INVALID, "%s: unknown metric", op);
+  F2C_REQUIRE(n <= tc::kStaticMaxPoints, F2C_ERR_LIMIT,
+              "%s: %lld points exceed the %lld the built-in scratch holds; split the call or use kmeans_assign with a workspace", op,
+              (long long)n, (long long)tc::kStaticMaxPoints);
+  F2C_REQUIRE(k <= tc::kMaxN && d <= 64, F2C_ERR_LIMIT, "%s: at most %d centres of at most 64 dimensions", op, tc::kMaxN);
+  if (n == 0) return F2C_OK;
+  F2C_REQUIRE(x && centers && labels, F2C_ERR_INVALID, "%s: null pointer", op);
+
+  // device address of the scratch array, looked up once per device (with that device current)
+  static std::mutex mu;
+  static void* scratch_of_device[64] = {nullptr};
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= 64) return set_error(F2C_ERR_CUDA, "%s: cudaGetDevice: %s", op, cudaGetErrorString(e));
+  void* scratch = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    if (scratch_of_device[dev] == nullptr) {
+      void* ptr = nullptr;
+      e = cudaGetSymbolAddress(&ptr, tc::g_static_scratch);
+      if (e != cudaSuccess || ptr == nullptr) return set_error(F2C_ERR_CUDA, "%s: cudaGetSymbolAddress: %s", op, cudaGetErrorString(e));
+      scratch_of_device[dev] = ptr;
+    }
+    scratch = scratch_of_device[dev];
+  }
+  // same kernels as kmeans_assign; the header (count, error code) is cleared inside
+  return kmeans_assign_tc(x, centers, labels, n, k, d, metric, scratch, (cudaStream_t)stream);
+}
+

@@ -155,6 +155,16 @@ int64_t f2c_kmeans_assign_workspace(int64_t n, int64_t k, int64_t d);
 int f2c_kmeans_assign(const float* x, const float* centers, int64_t* labels, int64_t n, int64_t k, int64_t d,
                       int metric, void* workspace, void* stream);
 
+/* K-means assignment for callers that cannot allocate device memory - no counterpart in the reference.
+ * Same result as f2c_kmeans_assign, but the scratch it needs is a fixed 4 MiB + 256 B array inside the library
+ * (present on every GPU that loads it, until exit) instead of a caller-supplied workspace, and the call itself
+ * allocates nothing.  Meant for threads inside a process whose framework allocator owns nearly all of HBM, or on
+ * a latency-critical path where cudaMalloc / cudaFree would stall the device.  Limits: n <= 1,048,576 points per
+ * call (F2C_ERR_LIMIT beyond), k <= 256, d <= 64.  The first call on a device looks up the array's address; make
+ * it outside any stream capture.  All calls on a device share the array: calls that overlap on the GPU race. */
+int f2c_kmeans_assign_static(const float* x, const float* centers, int64_t* labels, int64_t n, int64_t k, int64_t d,
+                             int metric, void* stream);
+
 /* Debug helper (no counterpart: the reference never checks that indices < compress_feat.size(0)).
  * Writes 0 to *flag_device if indptr is non-decreasing from 0.. and every index is in [0, n_src),
  * else a non-zero code.  Asynchronous; the caller reads the flag. */
