@@ -654,10 +654,39 @@ extern "C" int f2c_sq_spmm_csr_peer(const void* const* shard_ptrs_host, int worl
               "%s: column_slice (%lld) must be a multiple of %d for %d-bit codes", op, (long long)column_slice, 8 / bits, bits);
   F2C_REQUIRE(n_dst * feat_dim == 0 || (indptr && out && codebooks), F2C_ERR_INVALID, "%s: null pointer", op);
   PeerInfo peer{};
+  int here = 0;
+#define F2C_PEER_CUDA(call)                                                                       \
+  do {                                                                                           \
+    cudaError_t e_ = (call);                                                                     \
+    if (e_ != cudaSuccess) {                                                                     \
+      (void)cudaGetLastError();                                                                  \
+      return set_error(F2C_ERR_CUDA, "%s: %s failed: %s", op, #call, cudaGetErrorString(e_));  \
+    }                                                                                            \
+  } while (0)
+  F2C_PEER_CUDA(cudaGetDevice(&here));
   for (int r = 0; r < world; ++r) {
     F2C_REQUIRE(shard_ptrs_host[r] != nullptr, F2C_ERR_INVALID, "%s: shard %d is null", op, r);
     peer.shard[r] = shard_ptrs_host[r];
+    // A shard that lives on another GPU must be readable from the launching device: peer access is one-directional
+    // and an IPC mapping opened under the owner's device does not grant it, so it is requested here (idempotent).
+    cudaPointerAttributes attr{};
+    F2C_PEER_CUDA(cudaPointerGetAttributes(&attr, shard_ptrs_host[r]));
+    F2C_REQUIRE(attr.type == cudaMemoryTypeDevice || attr.type == cudaMemoryTypeManaged, F2C_ERR_INVALID,
+                "%s: shard %d is not device memory", op, r);
+    if (attr.type == cudaMemoryTypeDevice && attr.device != here) {
+      int can = 0;
+      F2C_PEER_CUDA(cudaDeviceCanAccessPeer(&can, here, attr.device));
+      F2C_REQUIRE(can, F2C_ERR_UNSUPPORTED, "%s: GPU %d cannot read shard %d on GPU %d (no peer access)", op, here, r,
+                  attr.device);
+      cudaError_t e = cudaDeviceEnablePeerAccess(attr.device, 0);
+      if (e == cudaErrorPeerAccessAlreadyEnabled) {
+        (void)cudaGetLastError();
+      } else {
+        F2C_PEER_CUDA(e);
+      }
+    }
   }
+#undef F2C_PEER_CUDA
   peer.world = world;
   peer.rows_per_shard = rows_per_shard;
   DropoutArgs drop = make_dropout(epilogue);

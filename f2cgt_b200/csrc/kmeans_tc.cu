@@ -295,8 +295,8 @@ int kmeans_assign_tc(const float* x, const float* y, int64_t* labels, int64_t n,
 // the process exits, enough for kStaticMaxPoints points per call.
 //
 // The array's name below is only a host-side handle; the device address is obtained once per device with
-// cudaGetSymbolAddress while that device is current.  That happens on the first call made on a device, so
-// make that first call outside any stream capture.  All calls on a device share the one array: the header is
+// cudaGetSymbolAddress while that device is current.  That happens on the first call made on a device (a
+// synchronising runtime query, once).  All calls on a device share the one array: the header is
 // cleared at the start of every call, the list behind it keeps whatever the previous call left and is only
 // read up to the new count.  Two calls that overlap on the GPU (different streams, or threads) would
 // overwrite each other's list - serialise them.

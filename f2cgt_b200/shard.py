@@ -127,8 +127,8 @@ class PeerTable:
             # owner's device ordinal (all GPUs of the box are visible to every rank)
             st = torch.UntypedStorage._new_shared_cuda(*h)
             t = torch.empty(0, dtype=dtype, device=torch.device("cuda", h[0])).set_(st, offset, shape)
-            # a first device-to-device copy makes torch enable peer access between the two devices
-            torch.empty(1, dtype=dtype, device=local_rows.device).copy_(t.reshape(-1)[:1])
+            # reading it from this rank's GPU needs peer access from this device to the owner's; the library
+            # entry point requests that itself (f2c_sq_spmm_csr_peer), nothing to do here
             self.tensors.append(t)
         self.ptrs = torch.tensor([t.data_ptr() for t in self.tensors], dtype=torch.int64, device=local_rows.device)
         dist.barrier(group=self.group)

@@ -160,8 +160,8 @@ int f2c_kmeans_assign(const float* x, const float* centers, int64_t* labels, int
  * (present on every GPU that loads it, until exit) instead of a caller-supplied workspace, and the call itself
  * allocates nothing.  Meant for threads inside a process whose framework allocator owns nearly all of HBM, or on
  * a latency-critical path where cudaMalloc / cudaFree would stall the device.  Limits: n <= 1,048,576 points per
- * call (F2C_ERR_LIMIT beyond), k <= 256, d <= 64.  The first call on a device looks up the array's address; make
- * it outside any stream capture.  All calls on a device share the array: calls that overlap on the GPU race. */
+ * call (F2C_ERR_LIMIT beyond), k <= 256, d <= 64.  The first call on a device looks up the array's address
+ * (a synchronising runtime query).  All calls on a device share the array: calls that overlap on the GPU race. */
 int f2c_kmeans_assign_static(const float* x, const float* centers, int64_t* labels, int64_t n, int64_t k, int64_t d,
                              int metric, void* stream);
 

@@ -1,0 +1,75 @@
+"""Two GPUs, one process each (NCCL): the row-sharded table read through CUDA-IPC peer mappings and through the
+all-to-all row exchange gives the same aggregated rows as the whole table on one GPU.  Skipped on a one-GPU box."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    return port
+
+
+def _worker(rank, world, port, q):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    torch.cuda.set_device(rank)
+    device = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=device)
+    try:
+        import F2CGTLib as capi
+        from f2cgt_b200 import ops, shard
+        n_rows, D = 20011, 128
+        for bits in (1, 4, 8):
+            g = torch.Generator().manual_seed(bits)  # the same table, codebook and block on every rank
+            width = D * bits // 8
+            table = torch.randint(0, 256, (n_rows, width), generator=g, dtype=torch.uint8).to(device)
+            cb = torch.tensor([[1e-3, 4.0, -9.97, 2.0, 0.7]], dtype=torch.float32, device=device)
+            g2 = torch.Generator().manual_seed(1000 + rank)  # a different block per rank
+            deg = torch.randint(0, 30, (700,), generator=g2)
+            indptr = torch.cat([torch.zeros(1, dtype=torch.int64), torch.cumsum(deg, 0)]).to(device)
+            indices = torch.randint(0, n_rows, (int(deg.sum()),), generator=g2).to(device)
+            want = capi.sq_decompress_spmm_csr(table, cb, indptr, indices, bits, D, D)
+            lo, hi = shard.shard_bounds(n_rows, world, rank)
+            local = table[lo:hi].clone()
+            peers = shard.PeerTable(local, n_rows)
+            got = ops.sq_decompress_spmm_csr_peer(peers, cb, indptr, indices, bits, D, D)
+            torch.cuda.synchronize()
+            assert torch.equal(got, want), f"peer loads differ at {bits} bits"
+            st = shard.ShardedTable(local, n_rows)
+            src, inverse = torch.unique(indices, return_inverse=True)
+            rows = st.fetch(src)
+            got2 = capi.sq_decompress_spmm_csr(rows, cb, indptr, inverse, bits, D, D)
+            assert torch.equal(got2, want), f"all-to-all fetch differs at {bits} bits"
+            dist.barrier()  # nobody frees its shard while a peer may still read it
+            del peers
+        q.put((rank, "ok"))
+    except Exception as e:  # noqa: BLE001
+        q.put((rank, repr(e)))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_sharded_table_two_gpus():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    results = dict(q.get(timeout=300) for _ in procs)
+    for p in procs:
+        p.join(timeout=60)
+    assert results == {0: "ok", 1: "ok"}, results
