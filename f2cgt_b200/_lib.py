@@ -49,6 +49,11 @@ SIGNATURES = {
     "f2c_spmm_csr": [p, ci, p, p, ci, p, i64, i64, ci, p],
     "f2c_sq_spmm_csr": [p, ci, p, i64, p, p, ci, p, i64, i64, i64, i64, ci, i64, ci, EP, p],
     "f2c_sq_spmm_csr_peer": [p, ci, i64, ci, p, i64, p, p, ci, p, i64, i64, i64, i64, ci, i64, ci, EP, p],
+    "f2c_shard_create": [p, i64, p, p, p],
+    "f2c_shard_free": [p],
+    "f2c_shard_open": [p, p],
+    "f2c_shard_close": [p],
+    "f2c_shard_copy": [p, p, i64, p],
     "f2c_vq_spmm_csr": [p, ci, p, p, p, ci, p, i64, i64, i64, i64, i64, ci, EP, p],
     "f2c_hybrid_decompress": [p, ci, p, i64, ci, i64, i64, i64, p, ci, p, i64, i64, i64, i64, p, i64, p],
     "f2c_hybrid_spmm_csr": [p, ci, p, i64, ci, i64, i64, p, ci, p, i64, i64, i64, p, p, p, ci, p, i64, i64, ci, EP, p],

@@ -667,8 +667,8 @@ extern "C" int f2c_sq_spmm_csr_peer(const void* const* shard_ptrs_host, int worl
   for (int r = 0; r < world; ++r) {
     F2C_REQUIRE(shard_ptrs_host[r] != nullptr, F2C_ERR_INVALID, "%s: shard %d is null", op, r);
     peer.shard[r] = shard_ptrs_host[r];
-    // A shard that lives on another GPU must be readable from the launching device: peer access is one-directional
-    // and an IPC mapping opened under the owner's device does not grant it, so it is requested here (idempotent).
+    // A shard that lives on another GPU must be readable from the launching device: peer access is one-directional,
+    // so it is requested here (idempotent; f2c_shard_open has normally enabled it already).
     cudaPointerAttributes attr{};
     F2C_PEER_CUDA(cudaPointerGetAttributes(&attr, shard_ptrs_host[r]));
     F2C_REQUIRE(attr.type == cudaMemoryTypeDevice || attr.type == cudaMemoryTypeManaged, F2C_ERR_INVALID,

@@ -188,16 +188,18 @@ def sq_decompress_spmm_csr_peer(peer_table, codebooks, indptr, indices, target_b
     """``sq_decompress_spmm_csr`` over a row-sharded table (``f2cgt_b200.shard.PeerTable``): indices are global row ids,
     remote rows are read by the kernel itself over NVLink."""
     import ctypes
-    local = peer_table.local
     _chk(codebooks, "codebooks", (torch.float32,))
     n_dst = _csc(indptr, indices)
-    out = torch.empty((n_dst, feat_dim), dtype=torch.float32, device=local.device)
-    ptrs = (ctypes.c_void_p * peer_table.world)(*[t.data_ptr() for t in peer_table.tensors])
+    out = torch.empty((n_dst, feat_dim), dtype=torch.float32, device=indptr.device)
+    if len(peer_table.pointers) != peer_table.world:
+        raise RuntimeError("the peer table is closed")
+    ptrs = (ctypes.c_void_p * peer_table.world)(*peer_table.pointers)
     ep = _epilogue(dropout)
-    with _on(local):
-        check(lib.f2c_sq_spmm_csr_peer(ptrs, peer_table.world, peer_table.rpr, _DT[local.dtype], _ptr(codebooks), codebooks.shape[0],
-                                       _ptr(indptr), _ptr(indices), _DT[indptr.dtype], _ptr(out), n_dst, peer_table.n_rows,
-                                       local.shape[1], feat_dim, target_bit, column_slice, _REDUCE[reduce], ep, _stream(local)))
+    with _on(indptr):
+        check(lib.f2c_sq_spmm_csr_peer(ptrs, peer_table.world, peer_table.rpr, _DT[peer_table.dtype], _ptr(codebooks),
+                                       codebooks.shape[0], _ptr(indptr), _ptr(indices), _DT[indptr.dtype], _ptr(out), n_dst,
+                                       peer_table.n_rows, peer_table.row_width, feat_dim, target_bit, column_slice,
+                                       _REDUCE[reduce], ep, _stream(indptr)))
     return out
 
 

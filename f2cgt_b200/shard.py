@@ -7,8 +7,9 @@ Two ways to aggregate a block whose source rows live on other GPUs:
   are exchanged back, all as point-to-point operations grouped into one NCCL all-to-all
   (``dist.batch_isend_irecv``; the same code runs over gloo on CPU, which is how the tests cover it).
   The fused kernel then runs on the fetched, block-local rows.
-* ``PeerTable`` - every rank maps the other ranks' shards through CUDA IPC and the fused kernel reads remote rows
-  itself with ordinary loads over NVLink (``f2c_sq_spmm_csr_peer``): no collective, no host synchronisation.
+* ``PeerTable`` - every rank maps the other ranks' shards through CUDA IPC (``f2c_shard_create`` / ``f2c_shard_open``)
+  and the fused kernel reads remote rows itself with ordinary loads over NVLink (``f2c_sq_spmm_csr_peer``): no
+  collective, no host synchronisation.
 
 Host logic only; all arithmetic is in the CUDA library.
 """
@@ -103,32 +104,72 @@ class ShardedTable:
 class PeerTable:
     """Shards of all ranks mapped into this process through CUDA IPC (plain peer mappings, no multicast).
 
-    ``ptrs`` is a device tensor of ``world`` uint64 base addresses, ``tensors`` keeps the mappings alive.  Every
-    rank must construct it collectively; the local shard must stay allocated as long as any peer uses it."""
+    The local rows are copied once into an allocation of their own that the library exports
+    (``f2c_shard_create``); every other rank opens the handle while ITS GPU is the current device
+    (``f2c_shard_open``), which maps the memory into that GPU's address space with peer access.
+    ``pointers[r]`` is the device address of rank r's shard as seen from this rank.  Construct and ``close`` it
+    collectively: every rank closes its mappings before any owner frees its shard."""
 
     def __init__(self, local_rows, n_rows, group=None):
+        import ctypes
+        from ._lib import lib, check
+        if not local_rows.is_cuda or not local_rows.is_contiguous() or local_rows.dim() != 2:
+            raise ValueError("local_rows must be a contiguous 2-D CUDA tensor")
         self.group = group
         self.world = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
         self.n_rows = int(n_rows)
         self.rpr = rows_per_rank(self.n_rows, self.world)
-        self.local = local_rows
-        storage = local_rows.untyped_storage()
-        handle = storage._share_cuda_()  # (device, ipc handle, size, offset, ref-counter handle, ...)
-        meta = (handle, tuple(local_rows.shape), local_rows.dtype, local_rows.storage_offset())
-        metas = [None] * self.world
-        dist.all_gather_object(metas, meta, group=self.group)
-        self.tensors = []
-        for r, (h, shape, dtype, offset) in enumerate(metas):
-            if r == self.rank:
-                self.tensors.append(local_rows)
-                continue
-            # h = (owner device, ipc handle, bytes, offset, ref-counter handle, ...): the mapping is opened on the
-            # owner's device ordinal (all GPUs of the box are visible to every rank)
-            st = torch.UntypedStorage._new_shared_cuda(*h)
-            t = torch.empty(0, dtype=dtype, device=torch.device("cuda", h[0])).set_(st, offset, shape)
-            # reading it from this rank's GPU needs peer access from this device to the owner's; the library
-            # entry point requests that itself (f2c_sq_spmm_csr_peer), nothing to do here
-            self.tensors.append(t)
-        self.ptrs = torch.tensor([t.data_ptr() for t in self.tensors], dtype=torch.int64, device=local_rows.device)
+        lo, hi = shard_bounds(self.n_rows, self.world, self.rank)
+        if local_rows.shape[0] != hi - lo:
+            raise ValueError(f"rank {self.rank} must hold rows [{lo}, {hi}) - got {local_rows.shape[0]} rows")
+        self.device = local_rows.device
+        self.dtype = local_rows.dtype
+        self.row_width = int(local_rows.shape[1])
+        self.nbytes = local_rows.numel() * local_rows.element_size()
+        self._own = ctypes.c_void_p()
+        self._opened = []
+        handle = (ctypes.c_ubyte * 64)()
+        with torch.cuda.device(self.device):
+            check(lib.f2c_shard_create(local_rows.data_ptr(), self.nbytes, ctypes.byref(self._own), handle,
+                                       torch.cuda.current_stream(self.device).cuda_stream))
+            metas = [None] * self.world
+            dist.all_gather_object(metas, (bytes(handle), self.nbytes), group=self.group)
+            self.pointers = []
+            self.shard_bytes = []
+            for r, (h, nbytes) in enumerate(metas):
+                self.shard_bytes.append(nbytes)
+                if r == self.rank:
+                    self.pointers.append(self._own.value)
+                    continue
+                ptr = ctypes.c_void_p()
+                check(lib.f2c_shard_open((ctypes.c_ubyte * 64).from_buffer_copy(h), ctypes.byref(ptr)))
+                self._opened.append(ptr)
+                self.pointers.append(ptr.value)
         dist.barrier(group=self.group)
+
+    def read(self, r, byte_offset, nbytes):
+        """Bytes [byte_offset, byte_offset + nbytes) of rank r's shard as a uint8 tensor on this GPU (copy engine)."""
+        from ._lib import lib, check
+        if byte_offset < 0 or byte_offset + nbytes > self.shard_bytes[r]:
+            raise IndexError("range outside the shard")
+        out = torch.empty(nbytes, dtype=torch.uint8, device=self.device)
+        with torch.cuda.device(self.device):
+            check(lib.f2c_shard_copy(out.data_ptr(), self.pointers[r] + byte_offset, nbytes,
+                                     torch.cuda.current_stream(self.device).cuda_stream))
+        return out
+
+    def close(self):
+        """Collective: unmap the other ranks' shards, then free the local one."""
+        from ._lib import lib, check
+        if self._own is None:
+            return
+        with torch.cuda.device(self.device):
+            torch.cuda.synchronize(self.device)
+            for ptr in self._opened:
+                check(lib.f2c_shard_close(ptr))
+            self._opened = []
+            dist.barrier(group=self.group)
+            check(lib.f2c_shard_free(self._own))
+        self._own = None
+        self.pointers = []

@@ -100,14 +100,29 @@ int f2c_sq_spmm_csr(const void* codes, int code_dtype, const float* codebooks, i
 /* The same operator over a table that is row-sharded across the GPUs of one NVSwitch box (no counterpart in
  * the reference, which keeps one host replica per machine: examples/load_dataset.py:63-85).  Row r of the table
  * is row r % rows_per_shard of shard r / rows_per_shard; shard_ptrs_host is a HOST array of `world` (<= 8)
- * device pointers, every one dereferenceable from the current device (the local shard and CUDA-IPC / peer
- * mappings of the others).  The kernel reads remote rows itself with ordinary loads over NVLink: there is no
+ * device pointers, every one dereferenceable from the current device (the local shard and the other ranks'
+ * shards mapped with f2c_shard_open).  The kernel reads remote rows itself with ordinary loads over NVLink: there is no
  * collective and nothing waits on another rank; the caller keeps all shards alive and unmodified during the call. */
 int f2c_sq_spmm_csr_peer(const void* const* shard_ptrs_host, int world, int64_t rows_per_shard, int code_dtype,
                          const float* codebooks, int64_t n_codebooks, const void* indptr, const void* indices,
                          int index_dtype, float* out, int64_t n_dst, int64_t n_src, int64_t src_dim,
                          int64_t feat_dim, int bits, int64_t column_slice, int reduce,
                          const f2c_epilogue* epilogue, void* stream);
+
+/* Shard memory that the other ranks of the box can map (no counterpart in the reference).  These five are the only
+ * entry points that allocate, free or map device memory.
+ *   f2c_shard_create  allocates `bytes` on the current device, copies `rows` (device memory) into it on `stream`
+ *                     (synchronised before return) and writes the 64-byte handle other processes open.
+ *   f2c_shard_open    maps a handle exported by ANOTHER process into the current device's address space with peer
+ *                     access; call it with the GPU that will launch the kernels as the current device.
+ *   f2c_shard_close / f2c_shard_free  undo them; every consumer closes before the owner frees.
+ *   f2c_shard_copy    asynchronous copy of a byte range between local memory and a mapped shard (copy engine). */
+#define F2C_SHARD_HANDLE_BYTES 64
+int f2c_shard_create(const void* rows, int64_t bytes, void** shard, unsigned char* handle, void* stream);
+int f2c_shard_free(void* shard);
+int f2c_shard_open(const unsigned char* handle, void** shard);
+int f2c_shard_close(void* shard);
+int f2c_shard_copy(void* dst, const void* src, int64_t bytes, void* stream);
 
 /* vq_decompress_spmm_csr(compress_feat, codebooks, indptr, indices, feat_dim)  -
  * src/fusion_spmm.cu:107-141 (kernel :72-105).  codebooks f32 only (as in the reference, :124-134). */

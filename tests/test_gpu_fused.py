@@ -279,8 +279,9 @@ def test_peer_sharded_table_equals_whole_table(capi, oracle, bits, world):
         pass
     pt = FakePeers()
     pt.world, pt.rpr, pt.n_rows = world, rpr, n_src
-    pt.tensors = [table[r * rpr:(r + 1) * rpr].clone() if r * rpr < n_src else table[:1].clone() for r in range(world)]
-    pt.local = pt.tensors[0]
+    tensors = [table[r * rpr:(r + 1) * rpr].clone() if r * rpr < n_src else table[:1].clone() for r in range(world)]
+    pt.pointers = [t.data_ptr() for t in tensors]
+    pt.dtype, pt.row_width = table.dtype, table.shape[1]
     got = ops.sq_decompress_spmm_csr_peer(pt, dev(cb), dev(indptr), dev(indices), bits, 128, D)
     want = capi.sq_decompress_spmm_csr(table, dev(cb), dev(indptr), dev(indices), bits, 128, D)
     assert torch.equal(got, want)

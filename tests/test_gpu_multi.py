@@ -2,6 +2,7 @@
 all-to-all row exchange gives the same aggregated rows as the whole table on one GPU.  Skipped on a one-GPU box."""
 import os
 import socket
+import sys
 
 import pytest
 import torch
@@ -42,17 +43,28 @@ def _worker(rank, world, port, q):
             want = capi.sq_decompress_spmm_csr(table, cb, indptr, indices, bits, D, D)
             lo, hi = shard.shard_bounds(n_rows, world, rank)
             local = table[lo:hi].clone()
-            peers = shard.PeerTable(local, n_rows)
-            got = ops.sq_decompress_spmm_csr_peer(peers, cb, indptr, indices, bits, D, D)
-            torch.cuda.synchronize()
-            assert torch.equal(got, want), f"peer loads differ at {bits} bits"
+            # 1. all-to-all row exchange (NCCL), kernel on block-local rows
             st = shard.ShardedTable(local, n_rows)
             src, inverse = torch.unique(indices, return_inverse=True)
             rows = st.fetch(src)
             got2 = capi.sq_decompress_spmm_csr(rows, cb, indptr, inverse, bits, D, D)
             assert torch.equal(got2, want), f"all-to-all fetch differs at {bits} bits"
-            dist.barrier()  # nobody frees its shard while a peer may still read it
-            del peers
+            print(f"rank {rank} bits {bits}: all-to-all ok", file=sys.stderr, flush=True)
+            # 2. the peer mappings, through the copy engine: head and tail of every shard
+            peers = shard.PeerTable(local, n_rows)
+            for r in range(world):
+                rlo, rhi = shard.shard_bounds(n_rows, world, r)
+                whole = table[rlo:rhi].reshape(-1)
+                n = min(4096, whole.numel())
+                assert torch.equal(peers.read(r, 0, n), whole[:n]), f"mapping of shard {r}: head differs"
+                assert torch.equal(peers.read(r, whole.numel() - n, n), whole[-n:]), f"mapping of shard {r}: tail differs"
+            print(f"rank {rank} bits {bits}: mappings ok", file=sys.stderr, flush=True)
+            # 3. the kernel reads remote rows itself
+            got = ops.sq_decompress_spmm_csr_peer(peers, cb, indptr, indices, bits, D, D)
+            torch.cuda.synchronize()
+            assert torch.equal(got, want), f"peer loads differ at {bits} bits"
+            print(f"rank {rank} bits {bits}: peer loads ok", file=sys.stderr, flush=True)
+            peers.close()  # collective: nobody frees its shard while a peer may still read it
         q.put((rank, "ok"))
     except Exception as e:  # noqa: BLE001
         q.put((rank, repr(e)))
