@@ -339,7 +339,7 @@ def run_ours(args):
             line["cpu_baseline"] = cpu_leg(blocks[0], steps=1, warmup=1, tables_dev=tables)
         if world == 1:
             line["reference_cuda_kernels"] = reference_cuda_leg(tables, blocks)
-        print(json.dumps(line), flush=True)
+        emit(line)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
@@ -461,7 +461,18 @@ def run_reference(args):
             "cpu_baseline": {"value": value, "unit": "edges/s", "cores": cores, "kind": "port",
                              "sample": "every step is one full block at all three widths (no sub-sampling)"},
             "e2e": {"value": value, "unit": "edges/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
-    print(json.dumps(line), flush=True)
+    emit(line)
+
+
+_RESULT_FD = None
+
+
+def emit(line):
+    data = (json.dumps(line) + "\n").encode()
+    if _RESULT_FD is None:
+        sys.stdout.write(data.decode()); sys.stdout.flush()
+    else:
+        os.write(_RESULT_FD, data)
 
 
 def main():
@@ -472,6 +483,12 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
+    # Libraries (NCCL's version banner, for one) write to file descriptor 1; the JSON line must be the only thing
+    # on stdout, so everything else is sent to stderr and the line is written to the saved descriptor.
+    global _RESULT_FD
+    sys.stdout.flush()
+    _RESULT_FD = os.dup(1)
+    os.dup2(2, 1)
     if args.impl == "reference":
         run_reference(args)
     else:
