@@ -42,6 +42,7 @@ int validate_sq(const char* op, int code_dtype, int64_t n_codebooks, int64_t src
 // experiment knobs (0 = built-in choice), set through f2c_set_tuning
 int g_tune_vec = 0, g_tune_u = 0, g_tune_lut = -1, g_tune_ctas_per_sm = 0;
 extern int g_kmeans_force_exact;
+extern int g_tune_vq_fast;
 
 template <int VEC> struct VecLoad;
 template <> struct VecLoad<4> {
@@ -709,13 +710,14 @@ extern "C" int f2c_sq_spmm_csr_peer(const void* const* shard_ptrs_host, int worl
 
 // Experiment knobs of the fused SQ kernel (no counterpart in the reference).  key 0: bytes per lane per
 // row load (4/8), 1: neighbours held in registers per row (8/12/16), 2: table decode on/off, 3: CTAs per
-// SM.  value 0 (key 2: -1) restores the built-in choice.
+// SM, 4: pipelined VQ / two-level kernel on (1) / off (0).  value 0 (key 2: -1, key 4: 1) restores the built-in choice.
 extern "C" int f2c_set_tuning(int key, int value) {
   switch (key) {
     case 0: g_tune_vec = value; break;
     case 1: g_tune_u = value; break;
     case 2: g_tune_lut = value; break;
     case 3: g_tune_ctas_per_sm = value; break;
+    case 4: g_tune_vq_fast = value; break;
     case 10: g_kmeans_force_exact = value; break;
     default: return set_error(F2C_ERR_INVALID, "set_tuning: unknown key %d", key);
   }

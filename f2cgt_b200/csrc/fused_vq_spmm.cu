@@ -19,6 +19,7 @@
 // for the lane's four columns are decoded with the element-wise SQ expression; the branch is
 // uniform across the warp because all lanes work on the same edge.
 #include "common.cuh"
+#include "vq_params.cuh"
 
 namespace f2c {
 
@@ -29,27 +30,6 @@ int validate_sq(const char* op, int code_dtype, int64_t n_codebooks, int64_t src
 constexpr int kVqThreads = 1024;  // one CTA per SM: the staged codebooks leave room for one
 constexpr size_t kVqSmemBudget = 200 * 1024;  // per CTA, leaves room for the static part and L1
 
-struct VqParams {
-  const void* codes;       // [n_src, n_cb]
-  const float* codebooks;  // [n_cb, K, cs]
-  const void* indptr;
-  const void* indices;
-  float* out;
-  int64_t n_dst;
-  int n_cb, cs, feat_dim;
-  uint32_t K;
-  int code_kind;           // 0 u8, 1 i8, 2 i16
-  int cb_per_part;         // codebooks (subspaces) handled by one blockIdx.y
-  int reduce;
-  int vec_store;
-  DropoutArgs drop;
-  // two-level extension
-  const uint8_t* sq_codes;  // [n_hot, sq_row_bytes]
-  const float* sq_codebooks;
-  const int32_t* slot;
-  int64_t sq_row_bytes;
-  int sq_cs, sq_n_cb, sq_signed;
-};
 
 __device__ __forceinline__ uint32_t vq_code(const void* codes, int kind, int64_t pos, uint32_t K) {
   int v;
@@ -276,6 +256,9 @@ extern "C" int f2c_vq_spmm_csr(const void* codes, int code_dtype, const float* c
     else vq_spmm_generic_kernel<int64_t><<<(unsigned)blocks, 256, 0, st>>>(p);
     return check_launch(op);
   }
+  bool served = false;
+  rc = launch_vq_fast(p, 0, index_dtype, st, op, &served);
+  if (served || rc) return rc;
   return index_dtype == F2C_I32 ? launch_vq<0, int32_t>(p, st, op) : launch_vq<0, int64_t>(p, st, op);
 }
 
@@ -313,6 +296,9 @@ extern "C" int f2c_hybrid_spmm_csr(const void* sq_codes, int sq_dtype, const flo
   p.sq_codes = (const uint8_t*)sq_codes; p.sq_codebooks = sq_codebooks; p.slot = slot; p.sq_row_bytes = sq_row_bytes;
   p.sq_cs = (int)sq_column_slice; p.sq_n_cb = (int)sq_n_codebooks; p.sq_signed = sq_dtype == F2C_I8;
   cudaStream_t st = (cudaStream_t)stream;
+  bool served = false;
+  rc = launch_vq_fast(p, bits, index_dtype, st, op, &served);
+  if (served || rc) return rc;
 #define F2C_HY(B) \
   return index_dtype == F2C_I32 ? launch_vq<B, int32_t>(p, st, op) : launch_vq<B, int64_t>(p, st, op)
   switch (bits) {

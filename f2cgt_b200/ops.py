@@ -366,8 +366,9 @@ class KMeans:
 
 
 def set_tuning(key, value):
-    """Experiment knob of the fused SQ kernel: key in {"vec", "inflight", "lut", "ctas_per_sm"}."""
-    check(lib.f2c_set_tuning({"vec": 0, "inflight": 1, "lut": 2, "ctas_per_sm": 3, "kmeans_exact": 10}[key], int(value)))
+    """Experiment knobs: key in {"vec", "inflight", "lut", "ctas_per_sm"} (fused SQ kernel), "vq_fast" (1/0: pipelined
+    VQ / two-level kernel or the general one), "kmeans_exact" (1: exact fp32 scorer, -1: tensor-core scorer, 0: heuristic)."""
+    check(lib.f2c_set_tuning({"vec": 0, "inflight": 1, "lut": 2, "ctas_per_sm": 3, "vq_fast": 4, "kmeans_exact": 10}[key], int(value)))
 
 
 # ------------------------------------------------------------------ neighbour sampling

@@ -183,9 +183,10 @@ int f2c_kmeans_assign_static(const float* x, const float* centers, int64_t* labe
 /* Debug helper (no counterpart: the reference never checks that indices < compress_feat.size(0)).
  * Writes 0 to *flag_device if indptr is non-decreasing from 0.. and every index is in [0, n_src),
  * else a non-zero code.  Asynchronous; the caller reads the flag. */
-/* Experiment knobs of the fused SQ kernel (no counterpart in the reference).  key 0: bytes per lane per
- * row load (4/8/16), 1: row loads in flight (4/8), 2: table decode on/off, 3: CTAs per SM.
- * value 0 (key 2: -1) restores the built-in choice. */
+/* Experiment knobs (no counterpart in the reference).  Fused SQ kernel - key 0: bytes per lane per row load
+ * (4/8), 1: neighbours held in registers per row (8/12/16), 2: table decode on/off, 3: CTAs per SM; value 0
+ * (key 2: -1) restores the built-in choice.  Key 4: pipelined VQ / two-level kernel on (1, default) or off (0).
+ * Key 10: k-means scorer, 1 exact fp32, -1 tensor cores, 0 heuristic. */
 int f2c_set_tuning(int key, int value);
 
 int f2c_check_csc(const void* indptr, const void* indices, int index_dtype, int64_t n_dst, int64_t n_src,

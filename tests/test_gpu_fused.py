@@ -182,6 +182,60 @@ def test_two_level_is_composition(capi, oracle, bits, D, n_cb, cs):
     assert torch.equal(cold, capi.vq_decompress_spmm_csr(dev(codes), dev(cbs), dev(indptr), dev(indices), D))
 
 
+@pytest.mark.parametrize("n_cb,K,cs,D", [(4, 256, 32, 128), (4, 100, 32, 100), (8, 200, 16, 128), (16, 256, 8, 128),
+                                         (16, 256, 4, 64), (4, 256, 64, 256), (8, 256, 32, 256), (4, 37, 128, 512)])
+@pytest.mark.parametrize("hot_bits,hot_cs", [(0, 0), (8, 0), (8, 32), (4, 0), (4, 64)])
+def test_pipelined_vq_kernel_equals_general_kernel(capi, oracle, n_cb, K, cs, D, hot_bits, hot_cs):
+    """The pipelined kernel (shared-memory codebooks, table decode of hot rows) against the general one and the oracle:
+    rows with 0, 1..16, 17..32 and more than 32 neighbours, codes >= K, ragged feat_dim, several column parts."""
+    from f2cgt_b200 import ops
+    rng = np.random.default_rng(n_cb * 7 + cs + hot_bits)
+    n_src, n_hot, n_dst = 700, 90, 333
+    cbs = rng.standard_normal((n_cb, K, cs)).astype(np.float32)
+    codes = rng.integers(0, 256, (n_src, n_cb)).astype(np.uint8)  # some codes >= K when K < 256
+    if D % 4:
+        pytest.skip("two-level needs feat_dim % 4 == 0")
+    deg = rng.integers(0, 14, n_dst)
+    deg[::5] = rng.integers(17, 33, len(deg[::5]))
+    deg[::11] = rng.integers(33, 100, len(deg[::11]))
+    deg[::7] = 0
+    indptr = np.concatenate([[0], np.cumsum(deg)]).astype(np.int64)
+    indices = rng.integers(0, n_src, int(indptr[-1])).astype(np.int64)
+    drop = dict(p=0.3, seed=5, offset=1, training=True)
+
+    def both(fn):
+        ops.set_tuning("vq_fast", 1)
+        a = fn()
+        ops.set_tuning("vq_fast", 0)
+        try:
+            b = fn()
+        finally:
+            ops.set_tuning("vq_fast", 1)
+        return a, b
+
+    for idx in (np.int64, np.int32):
+        ip, ix = dev(indptr.astype(idx)), dev(indices.astype(idx))
+        if hot_bits == 0:
+            for kw in (dict(), dict(reduce="sum"), dict(dropout=drop)):
+                a, b = both(lambda: capi.vq_decompress_spmm_csr(dev(codes), dev(cbs), ip, ix, D, **kw))
+                assert torch.equal(a, b), kw
+            want = oracle.vq_decompress_spmm_csr(np.minimum(codes, K - 1).astype(np.uint8), cbs, indptr, indices, D, "mean")
+            assert np.array_equal(host(capi.vq_decompress_spmm_csr(dev(codes), dev(cbs), ip, ix, D)), want)
+        else:
+            hcs = hot_cs or D
+            for signed in (True, False):
+                _, cb, sq = sq_table(oracle, rng, n_hot, D, hot_bits, hcs)
+                if hot_bits == 8 and not signed:
+                    sq = sq.view(np.uint8)
+                slot = np.full(n_src, -1, np.int32)
+                hot = rng.choice(n_src, n_hot, replace=False)
+                slot[hot] = rng.permutation(n_hot).astype(np.int32)
+                for kw in (dict(), dict(reduce="sum"), dict(dropout=drop)):
+                    a, b = both(lambda: capi.two_level_decompress_spmm_csr(dev(sq), dev(cb), hot_bits, hcs, dev(codes), dev(cbs),
+                                                                           dev(slot), ip, ix, D, **kw))
+                    assert torch.equal(a, b), (kw, signed)
+
+
 @pytest.mark.parametrize("kind", ["sq", "vq", "two_level"])
 def test_fused_dropout_equals_dropout_after(capi, oracle, kind):
     rng = np.random.default_rng(99)
