@@ -82,29 +82,30 @@ __global__ void __launch_bounds__(kThreads, 1) vq_fast_kernel(const VqParams p) 
   const int col_end = min(s_end * p.cs, p.feat_dim);
   const int K = (int)p.K, cs = p.cs, spq = p.fast_spq, stride = p.fast_stride;
 
-  // ---- stage this part's codebooks (layout in the header comment)
+  // ---- stage this part's codebooks (layout in the header comment); column_slice is a power of two here
   {
-    const int cs4 = cs >> 2;
-    const int n4 = (s_end - s_begin) * K * cs4;
+    const int lg4 = 31 - __clz(cs >> 2);  // log2(float4 pieces per centroid)
+    const int per_sub = K << lg4;
     const float4* src = reinterpret_cast<const float4*>(p.codebooks + (int64_t)s_begin * K * cs);
-    for (int i = threadIdx.x; i < n4; i += kThreads) {
-      const int q = i % cs4, t = i / cs4;
-      const int code = t % K, sl = t / K;
-      const int dst = spq > 1 ? ((sl / spq) * K + code) * 128 + (sl % spq) * cs * 4 + q * 16 : (sl * K + code) * stride + q * 16;
-      *reinterpret_cast<float4*>(cb_s + dst) = __ldg(src + i);
+    for (int sl = 0; sl < s_end - s_begin; ++sl) {
+      const int sub_base = spq > 1 ? (sl / spq) * K * 128 + (sl % spq) * cs * 4 : sl * K * stride;
+      for (int i = threadIdx.x; i < per_sub; i += kThreads) {
+        const int q = i & ((1 << lg4) - 1), code = i >> lg4;
+        *reinterpret_cast<float4*>(cb_s + sub_base + code * stride + q * 16) = __ldg(src + sl * per_sub + i);
+      }
     }
   }
   // ---- hot-row decode table: entry (byte, lane) = the floats that `byte` decodes to with the codebook row of
   //      that lane's columns; slab `byte` starts at byte * 256, a lane's entry is 4 (8-bit) or 8 (4-bit) bytes
   if (HB != 0) {
-    for (int i = threadIdx.x; i < 256 * 32; i += kThreads) {
-      const int byte = i >> 5, l = i & 31;
-      int col = col_begin + 4 * l;
-      if (col >= col_end) col = col_begin;
-      int row = col / p.sq_cs;
-      if (row >= p.sq_n_cb) row = p.sq_n_cb - 1;
-      const float emin = __ldg(p.sq_codebooks + row * kCodebookDim + 2), emax = __ldg(p.sq_codebooks + row * kCodebookDim + 3);
-      const float mean = __ldg(p.sq_codebooks + row * kCodebookDim + 4);
+    const int l = threadIdx.x & 31;
+    int lcol = col_begin + 4 * l;
+    if (lcol >= col_end) lcol = col_begin;
+    int row = lcol / p.sq_cs;
+    if (row >= p.sq_n_cb) row = p.sq_n_cb - 1;
+    const float emin = __ldg(p.sq_codebooks + row * kCodebookDim + 2), emax = __ldg(p.sq_codebooks + row * kCodebookDim + 3);
+    const float mean = __ldg(p.sq_codebooks + row * kCodebookDim + 4);
+    for (int byte = threadIdx.x >> 5; byte < 256; byte += kWarps) {
       if (HB == 8) {
         const float c = p.sq_signed ? (float)(int8_t)byte : (float)byte;
         reinterpret_cast<float*>(lut_s + byte * 256)[l] = sq_decode<8>(c, sq_scale<8>(emin, emax), emin, mean);
@@ -127,8 +128,8 @@ __global__ void __launch_bounds__(kThreads, 1) vq_fast_kernel(const VqParams p) 
   const uint32_t cb_addr = smem_u32(cb_s) + lane_base;
   uint32_t* wbuf = reinterpret_cast<uint32_t*>(wbuf_all) + wid * 32 * ROWW;
   const uint32_t wb_addr = smem_u32(wbuf) + (uint32_t)s;  // byte s of every staged code row
-  const uint32_t lut_addr = smem_u32(lut_s) + (uint32_t)lane * (HB == 4 ? 8u : 4u);
   const uint8_t* hot_base = HB != 0 ? p.sq_codes + (colc * (HB == 0 ? 8 : HB)) / 8 : nullptr;
+  const uint32_t hot_row_bytes = (uint32_t)p.sq_row_bytes;
   const bool clamp = K < 256;
 
   const IdxT* __restrict__ indptr = reinterpret_cast<const IdxT*>(p.indptr);
@@ -141,18 +142,20 @@ __global__ void __launch_bounds__(kThreads, 1) vq_fast_kernel(const VqParams p) 
     const float4 v = lds_f4(cb_addr + code * (uint32_t)stride);
     acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
   };
+  const uint32_t lane_off = (uint32_t)lane * (HB == 4 ? 8u : 4u);  // < 256: fits the low byte of the permute result
+  const uint32_t lut_base = smem_u32(lut_s);
   auto add_hot = [&](uint32_t w) {
     if (HB == 8) {
-      const float v0 = lds_f1(lut_addr + ((w & 0xFFu) << 8)), v1 = lds_f1(lut_addr + ((w >> 8 & 0xFFu) << 8));
-      const float v2 = lds_f1(lut_addr + ((w >> 16 & 0xFFu) << 8)), v3 = lds_f1(lut_addr + ((w >> 24) << 8));
+      const float v0 = lds_f1(lut_base + __byte_perm(w, lane_off, 0x7704)), v1 = lds_f1(lut_base + __byte_perm(w, lane_off, 0x7714));
+      const float v2 = lds_f1(lut_base + __byte_perm(w, lane_off, 0x7724)), v3 = lds_f1(lut_base + __byte_perm(w, lane_off, 0x7734));
       acc.x += v0; acc.y += v1; acc.z += v2; acc.w += v3;
     } else {
-      const float2 a = lds_f2(lut_addr + ((w & 0xFFu) << 8)), b = lds_f2(lut_addr + ((w >> 8 & 0xFFu) << 8));
+      const float2 a = lds_f2(lut_base + __byte_perm(w, lane_off, 0x7704)), b = lds_f2(lut_base + __byte_perm(w, lane_off, 0x7714));
       acc.x += a.x; acc.y += a.y; acc.z += b.x; acc.w += b.y;
     }
   };
   auto load_hot = [&](int sl_) -> uint32_t {
-    const uint8_t* q = hot_base + (int64_t)sl_ * p.sq_row_bytes;
+    const uint8_t* q = hot_base + (uint64_t)(uint32_t)sl_ * hot_row_bytes;
     return HB == 8 ? ldg_nc_u32(q) : ldg_nc_u16(q);
   };
   auto stage_codes = [&](const CodeRow<ROWW>& c, int cnt) {
@@ -205,10 +208,9 @@ __global__ void __launch_bounds__(kThreads, 1) vq_fast_kernel(const VqParams p) 
       if (HB != 0) {
 #pragma unroll
         for (int u = 0; u < U; ++u) {
-          if (u < cnt0) {
-            if ((mask4 >> u) & 1u) add_hot(hot[u]);
-            else add_vq(wb_addr + u * ROWB);
-          }
+          if (u >= cnt0) break;
+          if ((mask4 >> u) & 1u) add_hot(hot[u]);
+          else add_vq(wb_addr + u * ROWB);
         }
         for (int u = U; u < cnt0; ++u) {
           const int sl_ = __shfl_sync(0xffffffffu, slot4, u);
@@ -253,9 +255,7 @@ __global__ void __launch_bounds__(kThreads, 1) vq_fast_kernel(const VqParams p) 
       if (active) {
         if (p.reduce == F2C_MEAN) {
           const float degf = deg4 == 0 ? 1.0f : (float)deg4;
-          const float rcp = __frcp_rn(degf);
-          acc.x = div_exact(acc.x, degf, rcp); acc.y = div_exact(acc.y, degf, rcp);
-          acc.z = div_exact(acc.z, degf, rcp); acc.w = div_exact(acc.w, degf, rcp);
+          acc.x = acc.x / degf; acc.y = acc.y / degf; acc.z = acc.z / degf; acc.w = acc.w / degf;
         }
         const int64_t flat = (int64_t)rE * p.feat_dim + col;
         if (p.drop.enabled) acc = dropout_apply4(acc, (uint64_t)flat, p.drop);
@@ -272,10 +272,12 @@ __global__ void __launch_bounds__(kThreads, 1) vq_fast_kernel(const VqParams p) 
       if (HB != 0) {
         slot4 = on ? slot3 : -1;
         mask4 = __ballot_sync(0xffffffffu, slot4 >= 0);
+        if (mask4 != 0u) {
 #pragma unroll
-        for (int u = 0; u < U; ++u) {
-          const int sl_ = __shfl_sync(0xffffffffu, slot4, u);
-          if (sl_ >= 0) hot[u] = load_hot(sl_);
+          for (int u = 0; u < U; ++u) {
+            if ((mask4 >> u) == 0u) break;
+            if ((mask4 >> u) & 1u) hot[u] = load_hot(__shfl_sync(0xffffffffu, slot4, u));
+          }
         }
       }
     }
@@ -336,7 +338,7 @@ int launch_vq_fast(VqParams& p, int hot_bits, int index_dtype, cudaStream_t st, 
   if (hot_bits != 0) {
     if (p.sq_n_cb > 1 && p.sq_cs % 4 != 0) return F2C_OK;
     const int align = hot_bits == 8 ? 4 : 2;
-    if (p.sq_row_bytes % align != 0 || !aligned(p.sq_codes, align)) return F2C_OK;
+    if (p.sq_row_bytes % align != 0 || p.sq_row_bytes >= (1ll << 31) || !aligned(p.sq_codes, align)) return F2C_OK;
   }
   // a column part = at most 128 columns whose codebooks fit beside the table and the code tiles
   const int sub_per_128 = 128 / cs;
