@@ -6,6 +6,8 @@
 // 16-byte vector of outputs (two for 1-bit codes, so that it consumes a whole byte); ragged shapes
 // fall back to one thread per element.  The arithmetic is the reference's expression compiled with
 // the same math flags, so codes and decoded values carry the reference kernel's bits.
+#include <type_traits>
+
 #include "common.cuh"
 
 namespace f2c {
@@ -152,6 +154,101 @@ __global__ void __launch_bounds__(256) sq_decompress_vec_kernel(const void* __re
   for (int q = 0; q < EPT / 4; ++q) stg_cs_f4(reinterpret_cast<float*>(o + q), make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]));
 }
 
+// Table variant of the vector path for 1..8-bit codes stored in bytes: a persistent grid whose CTAs first decode
+// every code value once per codebook row WITH THE SAME EXPRESSION as the element-wise path (same bits) into shared
+// memory - 2^BITS * n_codebooks exp2f per CTA instead of one per element - and then stream: a thread keeps one
+// column position for its whole life, so its codebook row is fixed, row advance is an add, and an element costs a
+// bit-field extract, a shift-add and one shared-memory read.  The table is replicated COPIES times (one copy per
+// lane modulo COPIES) to spread the reads over the banks.
+constexpr int kSqLutThreads = 256;
+constexpr int kSqLutBytes = 64 * 1024;
+
+template <int BITS>
+__global__ void __launch_bounds__(kSqLutThreads) sq_decompress_lut_kernel(
+    const uint8_t* __restrict__ codes, float* __restrict__ out, const float* __restrict__ codebooks, int64_t rows,
+    int64_t row_bytes, int feat_dim, int chunks_per_row, int column_slice, int n_cb, int log_copies, int is_signed) {
+  constexpr int EPT = BITS == 1 ? 8 : 4;
+  constexpr int NCODE = 1 << BITS;
+  constexpr uint32_t MASK = NCODE - 1;
+  extern __shared__ float sq_tab[];
+  const int copies = 1 << log_copies;
+  for (int i = threadIdx.x; i < n_cb * NCODE; i += kSqLutThreads) {
+    const int row = i >> BITS, code = i & (int)MASK;
+    const float emin = __ldg(codebooks + row * kCodebookDim + 2), emax = __ldg(codebooks + row * kCodebookDim + 3);
+    const float mean = __ldg(codebooks + row * kCodebookDim + 4);
+    const float c = (BITS == 8 && is_signed) ? (float)(int8_t)code : (float)code;
+    const float v = sq_decode<BITS>(c, sq_scale<BITS>(emin, emax), emin, mean);
+    for (int k = 0; k < copies; ++k) sq_tab[(i << log_copies) + k] = v;
+  }
+  __syncthreads();
+  const int rows_per_cta = kSqLutThreads / chunks_per_row;
+  const int c0 = (threadIdx.x % chunks_per_row) * EPT;
+  int cb_row = c0 / column_slice;
+  if (cb_row >= n_cb) cb_row = n_cb - 1;
+  // byte address of entry (cb_row, code 0, this lane's copy); entry `code` is code << (log_copies + 2) further
+  const uint32_t tab = (uint32_t)__cvta_generic_to_shared(sq_tab) + ((((uint32_t)cb_row << BITS) << log_copies) + (threadIdx.x & (copies - 1))) * 4u;
+  const int sh = log_copies + 2;
+  const int64_t step = (int64_t)gridDim.x * rows_per_cta;
+  int64_t row = (int64_t)blockIdx.x * rows_per_cta + threadIdx.x / chunks_per_row;
+  const uint8_t* cp = codes + row * row_bytes + (c0 * BITS) / 8;
+  float* op = out + row * feat_dim + c0;
+  const int64_t cstep = step * row_bytes, ostep = step * feat_dim;
+  auto fetch = [&](const uint8_t* q) -> uint32_t {
+    if (BITS == 8) return *reinterpret_cast<const uint32_t*>(q);
+    if (BITS == 4) return *reinterpret_cast<const uint16_t*>(q);
+    return *q;
+  };
+  auto emit = [&](uint32_t raw, float* o) {
+    float v[EPT];
+#pragma unroll
+    for (int e = 0; e < EPT; ++e) {
+      const uint32_t code = (raw >> (BITS * e)) & MASK;
+      asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v[e]) : "r"(tab + (code << sh)));
+    }
+#pragma unroll
+    for (int q = 0; q < EPT / 4; ++q) stg_cs_f4(o + 4 * q, make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]));
+  };
+  for (; row + 3 * step < rows; row += 4 * step, cp += 4 * cstep, op += 4 * ostep) {
+    uint32_t raw[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) raw[u] = fetch(cp + u * cstep);
+#pragma unroll
+    for (int u = 0; u < 4; ++u) emit(raw[u], op + u * ostep);
+  }
+  for (; row < rows; row += step, cp += cstep, op += ostep) emit(fetch(cp), op);
+}
+
+// Returns true when the table kernel was launched (shape served).
+template <int BITS, typename CodeT>
+static bool try_decompress_lut(const void* codes, float* out, const float* cb, int64_t rows, int64_t src_dim, int64_t D,
+                               int64_t cs, cudaStream_t st) {
+  if (BITS > 8 || sizeof(CodeT) != 1) return false;
+  constexpr int EPT = BITS == 1 ? 8 : 4;
+  constexpr int LOAD_BYTES = BITS == 8 ? 4 : (BITS == 4 ? 2 : 1);
+  const int64_t n_cb = ceil_div(D, cs);
+  if (D % EPT != 0 || rows < 4096 || !aligned(out, 16) || !aligned(codes, LOAD_BYTES) || src_dim % LOAD_BYTES != 0) return false;
+  const int64_t cpr = D / EPT;
+  if (cpr > kSqLutThreads || kSqLutThreads % cpr != 0) return false;
+  if (n_cb > 1 && cs % EPT != 0) return false;  // a thread's columns must share one codebook row
+  const int64_t entries = n_cb << BITS;
+  if (entries * 4 > kSqLutBytes) return false;
+  int log_copies = 0;
+  while (log_copies < 5 && (entries << (log_copies + 1)) * 4 <= kSqLutBytes) ++log_copies;
+  const size_t smem = (size_t)(entries << log_copies) * 4;
+  auto kern = sq_decompress_lut_kernel<BITS <= 8 ? BITS : 8>;
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSqLutBytes) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return false;
+  }
+  const int rows_per_cta = kSqLutThreads / (int)cpr;
+  int64_t grid = ceil_div(rows, rows_per_cta);
+  const int64_t cap = (int64_t)kSmCount * (smem > 32 * 1024 ? 3 : 6);
+  if (grid > cap) grid = cap;
+  kern<<<(unsigned)grid, kSqLutThreads, smem, st>>>((const uint8_t*)codes, out, cb, rows, src_dim, (int)D, (int)cpr, (int)cs,
+                                                    (int)n_cb, log_copies, std::is_signed<CodeT>::value ? 1 : 0);
+  return true;
+}
+
 template <int BITS, typename CodeT>
 static int launch_decompress(const void* codes, float* out, const float* cb, int64_t rows, int64_t src_dim, int64_t D,
                              int64_t cs, cudaStream_t st) {
@@ -162,6 +259,7 @@ static int launch_decompress(const void* codes, float* out, const float* cb, int
   constexpr int LOAD_BYTES = BITS >= 8 ? 4 * (int)sizeof(CodeT) : (BITS == 4 ? 2 : 1);
   int64_t row_bytes = src_dim * (int64_t)sizeof(CodeT);
   bool vec = D % EPT == 0 && aligned(out, 16) && aligned(codes, LOAD_BYTES) && row_bytes % LOAD_BYTES == 0;
+  if (try_decompress_lut<BITS, CodeT>(codes, out, cb, rows, src_dim, D, cs, st)) return check_launch("sq_decompress");
   if (vec) {
     int64_t n_chunks = numel / EPT;
     sq_decompress_vec_kernel<BITS, CodeT><<<(unsigned)ceil_div(n_chunks, 256), 256, 0, st>>>(

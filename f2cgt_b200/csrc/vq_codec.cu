@@ -6,6 +6,8 @@
 // emits one float4 when the slice width and feat_dim are multiples of four.  A code outside
 // [0, length) cannot be told from a valid one by the reference (it reads out of bounds); here it is
 // clamped to the last centroid so that a bad table cannot fault the device.
+#include <type_traits>
+
 #include "common.cuh"
 
 namespace f2c {
@@ -54,12 +56,91 @@ __global__ void __launch_bounds__(256) vq_decompress_scalar_kernel(const void* _
   out[i] = load_cb1(cbs + ((int64_t)s * length + code) * cs + off);
 }
 
+// Streaming variant for the common shapes (uint8 codes, fp32 codebooks that fit in shared memory, vec_per_row
+// dividing the CTA size): the codebooks are staged once per CTA of a persistent grid, a thread keeps one float4
+// column position for its whole life (so its subspace and offset are computed once, and row advance is an add),
+// and four rows are in flight per thread.  Subspaces narrower than 32 columns are interleaved inside 128-byte
+// lines, so that the eight lanes of a quarter-warp read eight different 16-byte bank groups whatever the codes.
+constexpr int kVqStreamThreads = 1024;
+constexpr size_t kVqStreamSmem = 200 * 1024;
+
+__global__ void __launch_bounds__(kVqStreamThreads, 1) vq_decompress_stream_kernel(
+    const uint8_t* __restrict__ codes, const float* __restrict__ cbs, float* __restrict__ out, int64_t rows, int vec_per_row,
+    int n_cb, int K, int cs, int feat_dim, int spq, int stride) {
+  extern __shared__ __align__(128) unsigned char vq_smem[];
+  {
+    const int lg4 = 31 - __clz(cs >> 2);
+    const int per_sub = K << lg4;
+    const float4* src = reinterpret_cast<const float4*>(cbs);
+    for (int sl = 0; sl < n_cb; ++sl) {
+      const int sub_base = spq > 1 ? (sl / spq) * K * 128 + (sl % spq) * cs * 4 : sl * K * stride;
+      for (int i = threadIdx.x; i < per_sub; i += kVqStreamThreads) {
+        const int q = i & ((1 << lg4) - 1), code = i >> lg4;
+        *reinterpret_cast<float4*>(vq_smem + sub_base + code * stride + q * 16) = __ldg(src + sl * per_sub + i);
+      }
+    }
+  }
+  __syncthreads();
+  const int rows_per_cta = kVqStreamThreads / vec_per_row;
+  const int j = (threadIdx.x % vec_per_row) * 4;
+  const int s = j / cs, off = j - s * cs;
+  const uint32_t lane_base = (uint32_t)__cvta_generic_to_shared(vq_smem) +
+                             (spq > 1 ? (uint32_t)((s / spq) * K * 128 + (s % spq) * cs * 4 + off * 4) : (uint32_t)(s * K * stride + off * 4));
+  const int64_t step = (int64_t)gridDim.x * rows_per_cta;
+  int64_t row = (int64_t)blockIdx.x * rows_per_cta + threadIdx.x / vec_per_row;
+  const uint8_t* cp = codes + row * n_cb + s;
+  float* op = out + row * feat_dim + j;
+  const int64_t cstep = step * n_cb, ostep = step * feat_dim;
+  const uint32_t kmax = (uint32_t)K - 1u;
+  for (; row + 3 * step < rows; row += 4 * step, cp += 4 * cstep, op += 4 * ostep) {
+    uint32_t c[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) c[u] = min((uint32_t)__ldg(cp + u * cstep), kmax);
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      float4 v;
+      asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(lane_base + c[u] * (uint32_t)stride));
+      stg_cs_f4(op + u * ostep, v);
+    }
+  }
+  for (; row < rows; row += step, cp += cstep, op += ostep) {
+    const uint32_t c = min((uint32_t)__ldg(cp), kmax);
+    float4 v;
+    asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(lane_base + c * (uint32_t)stride));
+    stg_cs_f4(op, v);
+  }
+}
+
+// Returns true when the streaming kernel was launched.
+static bool try_vq_decompress_stream(const void* codes, const float* cbs, float* out, int64_t rows, int64_t n_cb, int64_t K,
+                                     int64_t cs, int64_t D, cudaStream_t st) {
+  if (K > 256 || cs < 4 || (cs & (cs - 1)) != 0 || D % 4 != 0 || D / 4 > kVqStreamThreads || kVqStreamThreads % (D / 4) != 0) return false;
+  if (!aligned(out, 16) || !aligned(cbs, 16) || rows < 4096) return false;
+  const int spq = cs < 32 ? (int)(32 / cs) : 1;
+  const int stride = cs < 32 ? 128 : (int)cs * 4;
+  const size_t smem = spq > 1 ? (size_t)ceil_div(n_cb, spq) * K * 128 : (size_t)n_cb * K * cs * 4;
+  if (smem > kVqStreamSmem) return false;
+  if (cudaFuncSetAttribute(vq_decompress_stream_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kVqStreamSmem) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return false;
+  }
+  const int rows_per_cta = kVqStreamThreads / (int)(D / 4);
+  int64_t grid = ceil_div(rows, rows_per_cta);
+  if (grid > kSmCount) grid = kSmCount;
+  vq_decompress_stream_kernel<<<(unsigned)grid, kVqStreamThreads, smem, st>>>(
+      (const uint8_t*)codes, cbs, out, rows, (int)(D / 4), (int)n_cb, (int)K, (int)cs, (int)D, spq, stride);
+  return true;
+}
+
 template <typename CodeT, typename CbT>
 static int launch_vq_decompress(const void* codes, const void* cbs, float* out, int64_t rows, int64_t n_cb, int64_t length,
                                 int64_t cs, int64_t D, cudaStream_t st) {
   int64_t numel = rows * D;
   if (numel == 0) return F2C_OK;
   bool vec = cs % 4 == 0 && D % 4 == 0 && aligned(out, 16) && aligned(cbs, 4 * sizeof(CbT));
+  if (sizeof(CodeT) == 1 && !std::is_signed<CodeT>::value && std::is_same<CbT, float>::value &&
+      try_vq_decompress_stream(codes, (const float*)cbs, out, rows, n_cb, length, cs, D, st))
+    return check_launch("vq_decompress");
   if (vec) {
     int64_t n_vec = numel / 4;
     vq_decompress_vec_kernel<CodeT, CbT><<<(unsigned)ceil_div(n_vec, 256), 256, 0, st>>>(

@@ -133,6 +133,41 @@ def test_vq_golden(capi, golden):
     assert np.array_equal(host(capi.vq_decompress(codes.to(torch.int16), cbs, 110)), golden["vq_dec_i16"])
 
 
+@pytest.mark.parametrize("bits", [1, 2, 4, 8])
+@pytest.mark.parametrize("D,cs", [(128, 128), (128, 32), (128, 8), (64, 16), (256, 256), (512, 64)])
+def test_sq_decompress_streaming_table_kernel(capi, oracle, bits, D, cs):
+    """Tables of >= 4096 rows take the persistent table-decode kernel; its rows must have the bits of the
+    element-wise kernel (which small calls use) and stay within the exp2f tolerance of the oracle."""
+    rng = np.random.default_rng(bits * 100 + D + cs)
+    rows = 4096 + 777
+    _, cb, stored = sq_table(oracle, rng, rows, D, bits, cs)
+    variants = [stored]
+    if bits == 8:
+        variants.append(stored.view(np.uint8))
+    for st in variants:
+        big = capi.sq_decompress(dev(st), dev(cb), bits, cs, D)
+        for lo in (0, 2000, rows - 300):
+            small = capi.sq_decompress(dev(st[lo:lo + 300]), dev(cb), bits, cs, D)
+            assert torch.equal(big[lo:lo + 300], small), (lo, st.dtype)
+    want = oracle.sq_decompress(stored, cb, bits, cs, D)
+    assert ulp_diff(host(capi.sq_decompress(dev(stored), dev(cb), bits, cs, D)), want).max() <= SQ_MAX_ULP
+
+
+@pytest.mark.parametrize("n_cb,K,cs,D", [(16, 256, 8, 128), (4, 256, 32, 128), (4, 256, 64, 256), (8, 100, 16, 128),
+                                         (32, 256, 4, 128), (2, 256, 128, 256), (4, 256, 32, 100)])
+def test_vq_decompress_streaming_kernel(capi, oracle, n_cb, K, cs, D):
+    """>= 4096 rows with uint8 codes take the shared-memory streaming kernel (where the shape allows): same rows as the
+    gather kernel used by small calls and as index_select (tests/test_vq.py:51,86)."""
+    rng = np.random.default_rng(n_cb + K + cs)
+    rows = 4096 + 1234
+    cbs = rng.standard_normal((n_cb, K, cs)).astype(np.float32)
+    codes = rng.integers(0, 256, (rows, n_cb)).astype(np.uint8)  # codes >= K are clamped by both kernels
+    big = capi.vq_decompress(dev(codes), dev(cbs), D)
+    for lo in (0, 3000, rows - 500):
+        assert torch.equal(big[lo:lo + 500], capi.vq_decompress(dev(codes[lo:lo + 500]), dev(cbs), D)), lo
+    assert np.array_equal(host(big), oracle.vq_decompress(np.minimum(codes, K - 1).astype(np.uint8), cbs, D))
+
+
 @pytest.mark.parametrize("bits", [1, 2, 4, 8, 16])
 @pytest.mark.parametrize("D,sq_cs,n_cb,cs", [(128, 128, 4, 32), (128, 32, 16, 8), (256, 256, 4, 64), (110, 110, 2, 60)])
 def test_fusion_decompress_is_concatenation(capi, oracle, bits, D, sq_cs, n_cb, cs):
