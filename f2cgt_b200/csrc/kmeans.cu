@@ -73,15 +73,15 @@ __global__ void __launch_bounds__(256) kmeans_thread_kernel(const float* __restr
                                                             int64_t* __restrict__ labels, const int32_t* __restrict__ subset,
                                                             const int32_t* __restrict__ count_dev, int64_t n, int k, int d, int kc) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  // count_dev != nullptr: the number of listed points is only known on the device; surplus blocks leave at once
+  // count_dev != nullptr: the number of listed points is only known on the device; a small grid walks the list
   if (count_dev != nullptr) {
     const int64_t cnt = *count_dev;
-    if ((int64_t)blockIdx.x * blockDim.x >= cnt) return;
     n = cnt < n ? cnt : n;
   }
   float* yc_s = reinterpret_cast<float*>(smem_raw);  // [kc][DMAX]
   float* cc_s = yc_s + (size_t)kc * DMAX;            // [kc]
-  const int64_t slot = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  for (int64_t base = (int64_t)blockIdx.x * blockDim.x; base < n; base += (int64_t)gridDim.x * blockDim.x) {
+  const int64_t slot = base + threadIdx.x;
   const bool valid = slot < n;
   // subset != nullptr: only the listed points are (re)scored
   const int64_t i = valid ? (subset ? (int64_t)subset[slot] : slot) : 0;
@@ -130,6 +130,7 @@ __global__ void __launch_bounds__(256) kmeans_thread_kernel(const float* __restr
     }
   }
   if (valid) labels[i] = best_c;
+  }
 }
 
 template <int DMAX>
@@ -140,6 +141,7 @@ static int launch_thread_assign(const float* x, const float* y, int64_t* labels,
   while ((size_t)kc * (DMAX + 1) * sizeof(float) > budget) kc = (kc + 1) / 2;
   size_t smem = (size_t)kc * (DMAX + 1) * sizeof(float);
   unsigned grid = (unsigned)ceil_div(n, 256);
+  if (count_dev != nullptr && grid > 2u * kSmCount) grid = 2u * kSmCount;  // the list is short: a small grid walks it
   cudaError_t e;
   if (metric == F2C_COSINE) {
     auto kern = kmeans_thread_kernel<DMAX, F2C_COSINE>;
@@ -230,9 +232,9 @@ extern "C" int f2c_kmeans_assign(const float* x, const float* centers, int64_t* 
   if (n == 0) return F2C_OK;
   F2C_REQUIRE(x && centers && labels, F2C_ERR_INVALID, "kmeans_assign: null pointer");
   // tensor-core path when a scratch buffer is supplied and the shape fits; the exact fp32 scorer otherwise
-  // (measured on B200: the tensor-core path wins from d = 16 up and for the cosine metric; at d = 8 the L2 scorer
-  //  in CUDA cores is as fast, because both are bound by the 256-way argmin, not by the contraction)
-  const bool prefer_tc = d >= 16 || metric == F2C_COSINE || g_kmeans_force_exact == -1;
+  // (measured on B200 with 256 centres: the tensor-core path is faster from d = 8 up for both metrics; below that
+  //  the CUDA-core scorer reads so little per point that the 128-point tiles only add latency)
+  const bool prefer_tc = d >= 8 || g_kmeans_force_exact == -1;
   if (workspace != nullptr && kmeans_tc_supported(n, k, d) && prefer_tc && g_kmeans_force_exact != 1 && aligned(workspace, 16))
     return kmeans_assign_tc(x, centers, labels, n, k, d, metric, workspace, (cudaStream_t)stream);
   return kmeans_assign_exact(x, centers, labels, nullptr, n, k, d, metric, (cudaStream_t)stream);

@@ -3,23 +3,28 @@
 // labels[i] = first argmin_c dist(x_i, y_c) with dist = squared L2 or cosine distance.
 //
 // The n*k*d contraction S = X * Y^T is the only dense GEMM on the path, so it runs as
-// tcgen05.mma.kind::tf32 with M = 128 points per tile, N = all (<= 256) centres, accumulators in TMEM
-// (256 columns), operands in shared memory in the canonical no-swizzle K-major layout.  TF32 keeps 10
-// mantissa bits, which would flip near ties, so both operands are split x = hi + lo (hi = top 19
-// bits) and the products hi*hi + lo*hi + hi*lo are obtained in ONE GEMM by concatenating along K:
-//     A' = [x_hi | x_lo | x_hi]   B' = [y_hi | y_hi | y_lo]      (K = 3d)
-// which is fp32-accurate to ~2^-19.  For d > 32 (operands would not fit in shared memory) a single
-// TF32 pass is used with a proportionally wider tolerance.  The epilogue reads the 128 x 256 scores
-// with tcgen05.ld (one point per thread), forms  |y_c|^2 - 2 S  (L2)  or  -S / |y_c|  (cosine), and
-// keeps the best and second best score.  A point whose two best scores are closer than the error
-// bound of the split product is NOT decided here: its index is appended to a scratch list and the
-// exact fp32 scorer (kmeans.cu) assigns it afterwards, so every label equals the label of the exact
-// fp32 kernel.
+// tcgen05.mma.kind::tf32 with M = 128 points per tile, N = all (<= 256) centres, accumulators in TMEM,
+// operands in shared memory in the canonical no-swizzle K-major layout.
 //
-// Shape of a CTA: 128 threads = 4 warps; thread t owns point t of the tile when loading / splitting
-// the A tile and TMEM lane t in the epilogue; thread 0 issues the MMAs.  Centres are staged once per
-// persistent CTA.  Every wait on the MMA-completion mbarrier is bounded; on expiry the CTA records
-// an error code, frees its TMEM and returns.
+//  * Accuracy.  TF32 keeps 10 mantissa bits, which would flip near ties, so both operands are split
+//    x = hi + lo (hi = top 19 bits) and the products hi*hi + lo*hi + hi*lo are obtained in ONE GEMM by
+//    concatenating along K:  A' = [x_hi | x_lo | x_hi],  B' = [y_hi | y_hi | y_lo]  (K = 3d), which is
+//    fp32-accurate to ~2^-19.  For d > 32 (operands would not fit in shared memory) a single TF32 pass is
+//    used with a proportionally wider tolerance.
+//  * The whole score comes out of the GEMM.  argmin_c |y_c|^2 - 2 x.y_c = argmax_c (x.y_c - |y_c|^2 / 2): one
+//    more K step carries [1, 1, 0...] on the point side and the split of -|y_c|^2/2 on the centre side
+//    (cosine: the centre rows are pre-scaled by 1/|y_c| instead), so the epilogue is a pure running
+//    arg-max - five instructions per (point, centre) - with no per-centre term to fetch.
+//  * The epilogue reads the 128 x 256 scores with tcgen05.ld (one point per thread) and keeps the best and
+//    second best score.  A point whose two best scores are closer than the error bound of the product is
+//    NOT decided here: its index is appended to a scratch list and the exact fp32 scorer (kmeans.cu)
+//    assigns it afterwards, so every label equals the label of the exact fp32 kernel.
+//  * Overlap.  A CTA is two groups of four warps that share the staged centre tile; each group has its own
+//    point tile, mbarrier and 256 TMEM columns and runs load -> MMA -> epilogue on alternate tiles, so the
+//    tensor pipe works on one group's tile while the other group is in its epilogue.  Thread t of a group
+//    owns point t of the tile when loading / splitting and TMEM lane t in the epilogue; the group's first
+//    thread issues the MMAs.  Every wait on an MMA-completion mbarrier is bounded; on expiry the group
+//    records an error code and leaves, and the CTA frees its TMEM at the common exit.
 #include <mutex>
 
 #include "common.cuh"
@@ -79,117 +84,168 @@ struct Params {
   int k, d;
   int dp;      // d padded to a multiple of 8
   int terms;   // 3: split product, 1: plain TF32
-  int n_pad;   // k padded to a multiple of 16 (MMA N)
+  int n_pad;   // k padded to a multiple of 32 (epilogue reads 32 columns at a time; MMA N needs 16)
   int metric;
+  int vec4;    // rows of x can be read as float4
   float eps;   // relative error bound of one score
 };
 
-// Shared memory: [B tile][A tile][cnorm 256 floats][mbarrier 8 B][tmem slot 4 B]
-__global__ void __launch_bounds__(128) kmeans_tc_kernel(const Params p) {
+constexpr int kGroupThreads = 128;
+constexpr int kCtaThreads = 2 * kGroupThreads;
+
+__device__ __forceinline__ void group_sync(int g) { asm volatile("bar.sync %0, 128;" ::"r"(g + 1) : "memory"); }
+
+__device__ __forceinline__ void split4(const float (&v)[4], float4& hi, float4& lo) {
+  hi.x = __uint_as_float(__float_as_uint(v[0]) & 0xFFFFE000u); lo.x = v[0] - hi.x;
+  hi.y = __uint_as_float(__float_as_uint(v[1]) & 0xFFFFE000u); lo.y = v[1] - hi.y;
+  hi.z = __uint_as_float(__float_as_uint(v[2]) & 0xFFFFE000u); lo.z = v[2] - hi.z;
+  hi.w = __uint_as_float(__float_as_uint(v[3]) & 0xFFFFE000u); lo.w = v[3] - hi.w;
+}
+
+// running (best, second best, index of best) over a stream of scores, larger = better
+struct Top2 {
+  float best, second;
+  int idx;
+  __device__ __forceinline__ void init() { best = -INFINITY; second = -INFINITY; idx = 0; }
+  __device__ __forceinline__ void push(float s, int c) {
+    const bool gt = s > best;
+    second = gt ? best : fmaxf(second, s);
+    idx = gt ? c : idx;
+    best = gt ? s : best;
+  }
+  __device__ __forceinline__ void merge(const Top2& o) {
+    const bool gt = o.best > best || (o.best == best && o.idx < idx);
+    second = gt ? fmaxf(best, o.second) : fmaxf(second, o.best);
+    idx = gt ? o.idx : idx;
+    best = gt ? o.best : best;
+  }
+};
+
+// Shared memory: [B tile][A tile group 0][A tile group 1][scratch 256 floats][2 mbarriers][tmem slot][2 fail flags]
+__global__ void __launch_bounds__(kCtaThreads, 1) kmeans_tc_kernel(const Params p) {
   extern __shared__ __align__(128) unsigned char smem[];
-  const int tid = threadIdx.x, warp = tid >> 5;
-  const int kc = p.terms * p.dp / 4;                 // 16-byte K chunks per operand row
+  const int tid = threadIdx.x;
+  const int g = tid >> 7;            // group
+  const int lt = tid & 127;          // thread within the group = point of the tile = TMEM lane
+  const int warp_in_group = lt >> 5;
+  const int kc = (p.terms * p.dp + 8) / 4;  // 16-byte K chunks per operand row (the last two carry the norm term)
+  const int kc_x = p.terms * p.dp / 4;
   const uint32_t lbo_b = kMaxN * 16, lbo_a = kTileM * 16, sbo = 128;
   unsigned char* b_tile = smem;
-  unsigned char* a_tile = smem + (size_t)kc * lbo_b;
-  float* cnorm = reinterpret_cast<float*>(a_tile + (size_t)kc * lbo_a);
-  uint64_t* mbar = reinterpret_cast<uint64_t*>(cnorm + kMaxN);
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(mbar + 1);
+  unsigned char* a_tile = smem + (size_t)kc * lbo_b + (size_t)g * kc * lbo_a;
+  float* scratch = reinterpret_cast<float*>(smem + (size_t)kc * lbo_b + (size_t)2 * kc * lbo_a);
+  uint64_t* mbar = reinterpret_cast<uint64_t*>(scratch + kMaxN);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(mbar + 2);
+  volatile uint32_t* fail = tmem_slot + 1;
 
-  // ---- one-time setup: TMEM, mbarrier, centre tile ----
-  if (warp == 0) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(256u) : "memory");
+  // ---- one-time setup: TMEM (all 512 columns: 256 per group), mbarriers, centre tile ----
+  if (tid < 32) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512u) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   if (tid == 0) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(mbar)) : "memory");
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(mbar + 1)) : "memory");
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    fail[0] = 0u; fail[1] = 0u;
   }
-  // centres: rows c = tid, tid + 128; padded rows / columns are zero; norm of padded rows = +inf (never chosen)
-  for (int c = tid; c < kMaxN; c += 128) {
+  // centre c = tid (256 threads, 256 rows); padded rows are zero with a norm term that never wins
+  {
+    const int c = tid;
+    const int G = p.dp / 4;
     float nrm = 0.0f;
-    for (int g = 0; g < p.dp / 4; ++g) {
+    if (c < p.k)
+      for (int t = 0; t < p.d; ++t) { const float v = __ldg(p.y + (int64_t)c * p.d + t); nrm = fmaf(v, v, nrm); }
+    // cosine: rows are scaled to unit length (zero rows stay zero); L2: rows as they are
+    const float row_scale = p.metric == F2C_COSINE ? (nrm > 0.0f ? 1.0f / sqrtf(nrm) : 0.0f) : 1.0f;
+    for (int gq = 0; gq < G; ++gq) {
       float v[4];
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
-        const int t = 4 * g + e;
-        v[e] = (c < p.k && t < p.d) ? __ldg(p.y + (int64_t)c * p.d + t) : 0.0f;
-        nrm = fmaf(v[e], v[e], nrm);
+        const int t = 4 * gq + e;
+        v[e] = (c < p.k && t < p.d) ? __ldg(p.y + (int64_t)c * p.d + t) * row_scale : 0.0f;
       }
       float4 hi, lo;
-      hi.x = __uint_as_float(__float_as_uint(v[0]) & 0xFFFFE000u); lo.x = v[0] - hi.x;
-      hi.y = __uint_as_float(__float_as_uint(v[1]) & 0xFFFFE000u); lo.y = v[1] - hi.y;
-      hi.z = __uint_as_float(__float_as_uint(v[2]) & 0xFFFFE000u); lo.z = v[2] - hi.z;
-      hi.w = __uint_as_float(__float_as_uint(v[3]) & 0xFFFFE000u); lo.w = v[3] - hi.w;
-      const int G = p.dp / 4;
+      split4(v, hi, lo);
       if (p.terms == 3) {  // B' = [y_hi | y_hi | y_lo]
-        *reinterpret_cast<float4*>(b_tile + (size_t)(g) * lbo_b + c * 16) = hi;
-        *reinterpret_cast<float4*>(b_tile + (size_t)(G + g) * lbo_b + c * 16) = hi;
-        *reinterpret_cast<float4*>(b_tile + (size_t)(2 * G + g) * lbo_b + c * 16) = lo;
+        *reinterpret_cast<float4*>(b_tile + (size_t)(gq) * lbo_b + c * 16) = hi;
+        *reinterpret_cast<float4*>(b_tile + (size_t)(G + gq) * lbo_b + c * 16) = hi;
+        *reinterpret_cast<float4*>(b_tile + (size_t)(2 * G + gq) * lbo_b + c * 16) = lo;
       } else {
-        *reinterpret_cast<float4*>(b_tile + (size_t)g * lbo_b + c * 16) = make_float4(v[0], v[1], v[2], v[3]);
+        *reinterpret_cast<float4*>(b_tile + (size_t)gq * lbo_b + c * 16) = make_float4(v[0], v[1], v[2], v[3]);
       }
     }
-    if (p.metric == F2C_L2) cnorm[c] = c < p.k ? nrm : INFINITY;
-    else cnorm[c] = c < p.k ? (nrm > 0.0f ? 1.0f / sqrtf(nrm) : 0.0f) : 0.0f;  // cosine: 1/|y_c|
+    // norm term: -|y_c|^2 / 2 split in two TF32 values (L2), 0 (cosine), a value that never wins (padding)
+    float h = c < p.k ? (p.metric == F2C_L2 ? -0.5f * nrm : 0.0f) : -1e30f;
+    const float h_hi = __uint_as_float(__float_as_uint(h) & 0xFFFFE000u);
+    *reinterpret_cast<float4*>(b_tile + (size_t)kc_x * lbo_b + c * 16) = make_float4(h_hi, h - h_hi, 0.0f, 0.0f);
+    *reinterpret_cast<float4*>(b_tile + (size_t)(kc_x + 1) * lbo_b + c * 16) = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    scratch[c] = c < p.k ? nrm : 0.0f;
   }
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-  const uint32_t tmem_base = *tmem_slot;
-  // largest centre norm (tolerance of the L2 score)
-  float cmax = 0.0f;
-  if (p.metric == F2C_L2)
-    for (int c = 0; c < p.k; ++c) cmax = fmaxf(cmax, cnorm[c]);
+  const uint32_t tmem_base = *tmem_slot + (uint32_t)g * 256u;
+  // largest centre norm (tolerance of the L2 score); a non-finite centre sends every point to the exact scorer
+  float cmax = 0.0f, poison = 0.0f;
+  for (int c = 0; c < p.k; ++c) { cmax = fmaxf(cmax, scratch[c]); poison = fmaf(scratch[c], 0.0f, poison); }  // inf, NaN -> NaN
+  const bool bad_centres = !(poison == 0.0f);
   cmax = sqrtf(cmax);
 
   const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(p.n_pad >> 3) << 17) | ((uint32_t)(kTileM >> 4) << 24);
-  const int ksteps = p.terms * p.dp / 8;  // one MMA consumes 8 tf32 = two 16-byte chunks of K
+  const int ksteps = kc / 2;  // one MMA consumes 8 tf32 = two 16-byte chunks of K
+  const uint32_t mbar_addr = smem_u32(mbar + g);
   uint32_t parity = 0;
-  bool failed = false;
 
   const int64_t n_tiles = (p.n + kTileM - 1) / kTileM;
-  for (int64_t tile = blockIdx.x; tile < n_tiles && !failed; tile += gridDim.x) {
-    // ---- A tile: thread t loads, splits and stores point tile*128 + t ----
-    const int64_t i = tile * kTileM + tid;
+  const int64_t first = (int64_t)blockIdx.x * 2 + g, stride = (int64_t)gridDim.x * 2;
+  for (int64_t tile = first; tile < n_tiles; tile += stride) {
+    // ---- A tile: thread lt loads, splits and stores point tile*128 + lt ----
+    const int64_t i = tile * kTileM + lt;
     float xx = 0.0f;
-    for (int g = 0; g < p.dp / 4; ++g) {
-      float v[4];
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int t = 4 * g + e;
-        v[e] = (i < p.n && t < p.d) ? __ldg(p.x + i * p.d + t) : 0.0f;
-        xx = fmaf(v[e], v[e], xx);
-      }
-      float4 hi, lo;
-      hi.x = __uint_as_float(__float_as_uint(v[0]) & 0xFFFFE000u); lo.x = v[0] - hi.x;
-      hi.y = __uint_as_float(__float_as_uint(v[1]) & 0xFFFFE000u); lo.y = v[1] - hi.y;
-      hi.z = __uint_as_float(__float_as_uint(v[2]) & 0xFFFFE000u); lo.z = v[2] - hi.z;
-      hi.w = __uint_as_float(__float_as_uint(v[3]) & 0xFFFFE000u); lo.w = v[3] - hi.w;
+    {
       const int G = p.dp / 4;
-      if (p.terms == 3) {  // A' = [x_hi | x_lo | x_hi]
-        *reinterpret_cast<float4*>(a_tile + (size_t)(g) * lbo_a + tid * 16) = hi;
-        *reinterpret_cast<float4*>(a_tile + (size_t)(G + g) * lbo_a + tid * 16) = lo;
-        *reinterpret_cast<float4*>(a_tile + (size_t)(2 * G + g) * lbo_a + tid * 16) = hi;
-      } else {
-        *reinterpret_cast<float4*>(a_tile + (size_t)g * lbo_a + tid * 16) = make_float4(v[0], v[1], v[2], v[3]);
+      for (int gq = 0; gq < G; ++gq) {
+        float v[4];
+        if (p.vec4 && i < p.n && 4 * gq + 3 < p.d) {
+          const float4 q = __ldg(reinterpret_cast<const float4*>(p.x + i * p.d) + gq);
+          v[0] = q.x; v[1] = q.y; v[2] = q.z; v[3] = q.w;
+        } else {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int t = 4 * gq + e;
+            v[e] = (i < p.n && t < p.d) ? __ldg(p.x + i * p.d + t) : 0.0f;
+          }
+        }
+        xx = fmaf(v[0], v[0], xx); xx = fmaf(v[1], v[1], xx); xx = fmaf(v[2], v[2], xx); xx = fmaf(v[3], v[3], xx);
+        float4 hi, lo;
+        split4(v, hi, lo);
+        if (p.terms == 3) {  // A' = [x_hi | x_lo | x_hi]
+          *reinterpret_cast<float4*>(a_tile + (size_t)(gq) * lbo_a + lt * 16) = hi;
+          *reinterpret_cast<float4*>(a_tile + (size_t)(G + gq) * lbo_a + lt * 16) = lo;
+          *reinterpret_cast<float4*>(a_tile + (size_t)(2 * G + gq) * lbo_a + lt * 16) = hi;
+        } else {
+          *reinterpret_cast<float4*>(a_tile + (size_t)gq * lbo_a + lt * 16) = make_float4(v[0], v[1], v[2], v[3]);
+        }
       }
+      *reinterpret_cast<float4*>(a_tile + (size_t)kc_x * lbo_a + lt * 16) = make_float4(1.0f, 1.0f, 0.0f, 0.0f);
+      *reinterpret_cast<float4*>(a_tile + (size_t)(kc_x + 1) * lbo_a + lt * 16) = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
     }
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    __syncthreads();  // A tile complete; every warp has finished reading the previous tile's accumulators
+    group_sync(g);  // A tile complete; every warp of the group has finished reading the previous tile's accumulators
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 
-    // ---- S = A' * B'^T into TMEM ----
-    if (tid == 0) {
+    // ---- S = A' * B'^T into this group's TMEM columns ----
+    if (lt == 0) {
       const uint32_t a_addr = smem_u32(a_tile), b_addr = smem_u32(b_tile);
-      for (int s = 0; s < ksteps; ++s) {
-        const uint64_t a_desc = make_desc(a_addr + (uint32_t)s * 2u * lbo_a, lbo_a, sbo);
-        const uint64_t b_desc = make_desc(b_addr + (uint32_t)s * 2u * lbo_b, lbo_b, sbo);
-        mma_tf32(tmem_base, a_desc, b_desc, idesc, s > 0 ? 1u : 0u);
+      for (int s_ = 0; s_ < ksteps; ++s_) {
+        const uint64_t a_desc = make_desc(a_addr + (uint32_t)s_ * 2u * lbo_a, lbo_a, sbo);
+        const uint64_t b_desc = make_desc(b_addr + (uint32_t)s_ * 2u * lbo_b, lbo_b, sbo);
+        mma_tf32(tmem_base, a_desc, b_desc, idesc, s_ > 0 ? 1u : 0u);
       }
-      asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(mbar)) : "memory");
+      asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(mbar_addr) : "memory");
     }
     // ---- bounded wait for the MMAs ----
     uint32_t done = 0;
@@ -198,46 +254,44 @@ __global__ void __launch_bounds__(128) kmeans_tc_kernel(const Params p) {
           "{\n\t.reg .pred p;\n\t"
           "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
           "selp.u32 %0, 1, 0, p;\n\t}\n"
-          : "=r"(done) : "r"(smem_u32(mbar)), "r"(parity) : "memory");
+          : "=r"(done) : "r"(mbar_addr), "r"(parity) : "memory");
     }
     parity ^= 1u;
-    if (__syncthreads_or(done == 0)) {  // somebody gave up: record it and leave through the common exit
-      if (tid == 0) atomicExch(p.error, 1 + (int)((tile - blockIdx.x) / gridDim.x));  // 1 + how many tiles this CTA had finished
-      failed = true;
+    if (!done) fail[g] = 1u;
+    group_sync(g);
+    if (fail[g] != 0u) {  // somebody gave up: record it and leave through the common exit
+      if (lt == 0) atomicExch(p.error, 1 + (int)((tile - first) / stride));  // 1 + how many tiles this group had finished
       break;
     }
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 
-    // ---- epilogue: thread t = TMEM lane t = point i ----
-    float best = INFINITY, second = INFINITY;
-    int best_c = 0;
-    bool odd = false;  // NaN seen: let the exact scorer decide
-    const uint32_t lane_addr = tmem_base + ((uint32_t)(warp * 32) << 16);
+    // ---- epilogue: thread lt = TMEM lane lt = point i; four independent trackers over interleaved columns ----
+    Top2 t0, t1, t2, t3;
+    t0.init(); t1.init(); t2.init(); t3.init();
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(warp_in_group * 32) << 16);
     for (int c0 = 0; c0 < p.n_pad; c0 += 32) {
       uint32_t r[32];
       tmem_ld32(lane_addr + (uint32_t)c0, r);
       asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-      for (int j = 0; j < 32; ++j) {
-        const int c = c0 + j;
-        const float s = __uint_as_float(r[j]);
-        const float score = p.metric == F2C_L2 ? fmaf(-2.0f, s, cnorm[c]) : -s * cnorm[c];
-        if (c < p.k) {
-          odd |= !(score == score);
-          if (score < best) { second = best; best = score; best_c = c; }
-          else if (score < second) second = score;
-        }
+      for (int j = 0; j < 32; j += 4) {
+        t0.push(__uint_as_float(r[j]), c0 + j);
+        t1.push(__uint_as_float(r[j + 1]), c0 + j + 1);
+        t2.push(__uint_as_float(r[j + 2]), c0 + j + 2);
+        t3.push(__uint_as_float(r[j + 3]), c0 + j + 3);
       }
     }
+    t0.merge(t1); t2.merge(t3); t0.merge(t2);
+    const float xn = sqrtf(xx);
+    // error bound of a score: L2  eps*|x||y|max ;  cosine  eps*|x|
+    const float tol = p.metric == F2C_L2 ? p.eps * xn * cmax : p.eps * xn;
+    const bool odd = bad_centres || !(xx < INFINITY) || !(t0.best > -INFINITY);  // NaN / inf somewhere: exact scorer
     if (i < p.n) {
-      const float xn = sqrtf(xx);
-      // error bound of a score: L2  2*eps*|x||y|max ;  cosine  eps*|x|
-      const float tol = p.metric == F2C_L2 ? 2.0f * p.eps * xn * cmax : p.eps * xn;
-      if (odd || !(second - best > 2.0f * tol)) {
+      if (odd || !(t0.best - t0.second > 2.0f * tol)) {  // undecided: the exact scorer assigns it afterwards
         const int slot = atomicAdd(p.amb_count, 1);
         p.amb_list[slot] = (int32_t)i;
       } else {
-        p.labels[i] = best_c;
+        p.labels[i] = t0.idx;
       }
     }
   }
@@ -245,9 +299,9 @@ __global__ void __launch_bounds__(128) kmeans_tc_kernel(const Params p) {
   // ---- common exit: all TMEM reads retired, then the allocating warp frees the columns ----
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
-  if (warp == 0) {
+  if (tid < 32) {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(256u) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(*tmem_slot), "r"(512u) : "memory");
   }
 }
 
@@ -263,20 +317,22 @@ int kmeans_assign_tc(const float* x, const float* y, int64_t* labels, int64_t n,
   p.x = x; p.y = y; p.labels = labels; p.n = n; p.k = (int)k; p.d = (int)d; p.metric = metric;
   p.dp = (int)((d + 7) / 8 * 8);
   p.terms = p.dp <= 32 ? 3 : 1;
-  p.n_pad = (int)((k + 15) / 16 * 16);
+  p.n_pad = (int)((k + 31) / 32 * 32);
+  p.vec4 = d % 4 == 0 && aligned(x, 16);
   p.eps = p.terms == 3 ? 1.0f / 65536.0f : 1.0f / 256.0f;  // 2^-16 (split product, true error ~2^-18.4) or 2^-8 (plain TF32)
   int32_t* head = reinterpret_cast<int32_t*>(workspace);
   p.amb_count = head; p.error = head + 1; p.amb_list = head + 64;
   cudaError_t e = cudaMemsetAsync(head, 0, 256, st);
   if (e != cudaSuccess) return set_error(F2C_ERR_CUDA, "kmeans_assign: %s", cudaGetErrorString(e));
-  const int kc = p.terms * p.dp / 4;
-  size_t smem = (size_t)kc * (tc::kMaxN + tc::kTileM) * 16 + tc::kMaxN * 4 + 16;
+  const int kc = (p.terms * p.dp + 8) / 4;
+  size_t smem = (size_t)kc * (tc::kMaxN + 2 * tc::kTileM) * 16 + tc::kMaxN * 4 + 64;
+  if (smem < 120 * 1024) smem = 120 * 1024;  // one CTA per SM: a second one would only wait for the TMEM columns
   e = cudaFuncSetAttribute(tc::kmeans_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return set_error(F2C_ERR_CUDA, "kmeans_assign: %s", cudaGetErrorString(e));
   int64_t tiles = ceil_div(n, tc::kTileM);
-  int per_sm = smem <= 100 * 1024 ? 2 : 1;  // two CTAs share the 512 TMEM columns of an SM
-  int64_t grid = tiles < (int64_t)kSmCount * per_sm ? tiles : (int64_t)kSmCount * per_sm;
-  tc::kmeans_tc_kernel<<<(unsigned)grid, 128, smem, st>>>(p);
+  int64_t grid = ceil_div(tiles, 2);  // one CTA per SM (it owns all 512 TMEM columns), two tiles in flight per CTA
+  if (grid > kSmCount) grid = kSmCount;
+  tc::kmeans_tc_kernel<<<(unsigned)grid, tc::kCtaThreads, smem, st>>>(p);
   int rc = check_launch("kmeans_assign (tensor cores)");
   if (rc) return rc;
   // undecided points: exact fp32 scorer over the device-side list
