@@ -19,12 +19,14 @@
 //    second best score.  A point whose two best scores are closer than the error bound of the product is
 //    NOT decided here: its index is appended to a scratch list and the exact fp32 scorer (kmeans.cu)
 //    assigns it afterwards, so every label equals the label of the exact fp32 kernel.
-//  * Overlap.  A CTA is two groups of four warps that share the staged centre tile; each group has its own
+//  * Overlap.  A CTA is two groups of eight warps that share the staged centre tile; each group has its own
 //    point tile, mbarrier and 256 TMEM columns and runs load -> MMA -> epilogue on alternate tiles, so the
-//    tensor pipe works on one group's tile while the other group is in its epilogue.  Thread t of a group
-//    owns point t of the tile when loading / splitting and TMEM lane t in the epilogue; the group's first
-//    thread issues the MMAs.  Every wait on an MMA-completion mbarrier is bounded; on expiry the group
-//    records an error code and leaves, and the CTA frees its TMEM at the common exit.
+//    tensor pipe works on one group's tile while the other group is in its epilogue.  A point of the tile
+//    belongs to two threads of its group (same TMEM lane, warps w and w + 4): they load and split alternate
+//    chunks of its row and scan one half of the centres each - the epilogue, not the MMA, is what the kernel
+//    spends its issue slots on, and twice the warps fill them better.  The group's first thread issues the
+//    MMAs.  Every wait on an MMA-completion mbarrier is bounded; on expiry the group records an error code
+//    and leaves, and the CTA frees its TMEM at the common exit.
 #include <mutex>
 
 #include "common.cuh"
@@ -73,6 +75,14 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
       : "r"(taddr));
 }
 
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];\n"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+        "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr));
+}
+
 struct Params {
   const float* x;
   const float* y;
@@ -90,10 +100,10 @@ struct Params {
   float eps;   // relative error bound of one score
 };
 
-constexpr int kGroupThreads = 128;
+constexpr int kGroupThreads = 256;  // two threads per point of the tile
 constexpr int kCtaThreads = 2 * kGroupThreads;
 
-__device__ __forceinline__ void group_sync(int g) { asm volatile("bar.sync %0, 128;" ::"r"(g + 1) : "memory"); }
+__device__ __forceinline__ void group_sync(int g) { asm volatile("bar.sync %0, 256;" ::"r"(g + 1) : "memory"); }
 
 __device__ __forceinline__ void split4(const float (&v)[4], float4& hi, float4& lo) {
   hi.x = __uint_as_float(__float_as_uint(v[0]) & 0xFFFFE000u); lo.x = v[0] - hi.x;
@@ -121,20 +131,24 @@ struct Top2 {
   }
 };
 
-// Shared memory: [B tile][A tile group 0][A tile group 1][scratch 256 floats][2 mbarriers][tmem slot][2 fail flags]
+// Shared memory: [B tile][A tile group 0][A tile group 1][scratch 256 floats][exchange 2 x 128 x 16 B][2 mbarriers]
+// [tmem slot][2 fail flags]
 __global__ void __launch_bounds__(kCtaThreads, 1) kmeans_tc_kernel(const Params p) {
   extern __shared__ __align__(128) unsigned char smem[];
   const int tid = threadIdx.x;
-  const int g = tid >> 7;            // group
-  const int lt = tid & 127;          // thread within the group = point of the tile = TMEM lane
-  const int warp_in_group = lt >> 5;
+  const int g = tid >> 8;            // group
+  const int lt = tid & 255;          // thread within the group
+  const int pt = lt & 127;           // its point of the tile = its TMEM lane
+  const int half = lt >> 7;          // which half of the row's K chunks it loads and which half of the centres it scans
+  const int lane_quarter = (lt >> 5) & 3;
   const int kc = (p.terms * p.dp + 8) / 4;  // 16-byte K chunks per operand row (the last two carry the norm term)
   const int kc_x = p.terms * p.dp / 4;
   const uint32_t lbo_b = kMaxN * 16, lbo_a = kTileM * 16, sbo = 128;
   unsigned char* b_tile = smem;
   unsigned char* a_tile = smem + (size_t)kc * lbo_b + (size_t)g * kc * lbo_a;
   float* scratch = reinterpret_cast<float*>(smem + (size_t)kc * lbo_b + (size_t)2 * kc * lbo_a);
-  uint64_t* mbar = reinterpret_cast<uint64_t*>(scratch + kMaxN);
+  float4* exch = reinterpret_cast<float4*>(scratch + kMaxN) + g * kTileM;  // (best, second, index, |x|^2 part) of half 1
+  uint64_t* mbar = reinterpret_cast<uint64_t*>(scratch + kMaxN + 2 * kTileM * 4);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(mbar + 2);
   volatile uint32_t* fail = tmem_slot + 1;
 
@@ -149,8 +163,8 @@ __global__ void __launch_bounds__(kCtaThreads, 1) kmeans_tc_kernel(const Params 
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     fail[0] = 0u; fail[1] = 0u;
   }
-  // centre c = tid (256 threads, 256 rows); padded rows are zero with a norm term that never wins
-  {
+  // centre c = tid (first 256 threads, 256 rows); padded rows are zero with a norm term that never wins
+  if (tid < kMaxN) {
     const int c = tid;
     const int G = p.dp / 4;
     float nrm = 0.0f;
@@ -200,37 +214,58 @@ __global__ void __launch_bounds__(kCtaThreads, 1) kmeans_tc_kernel(const Params 
 
   const int64_t n_tiles = (p.n + kTileM - 1) / kTileM;
   const int64_t first = (int64_t)blockIdx.x * 2 + g, stride = (int64_t)gridDim.x * 2;
-  for (int64_t tile = first; tile < n_tiles; tile += stride) {
-    // ---- A tile: thread lt loads, splits and stores point tile*128 + lt ----
-    const int64_t i = tile * kTileM + lt;
-    float xx = 0.0f;
-    {
-      const int G = p.dp / 4;
-      for (int gq = 0; gq < G; ++gq) {
-        float v[4];
-        if (p.vec4 && i < p.n && 4 * gq + 3 < p.d) {
-          const float4 q = __ldg(reinterpret_cast<const float4*>(p.x + i * p.d) + gq);
-          v[0] = q.x; v[1] = q.y; v[2] = q.z; v[3] = q.w;
+  // This thread's chunks of its point's row, fetched one tile ahead so that the global-load latency hides behind the
+  // previous tile's MMA and epilogue: chunk q of the thread is 16-byte chunk half + 2q of the row (at most 8: d <= 64).
+  constexpr int kMaxChunks = 8;
+  float4 xv[kMaxChunks];
+  auto fetch_row = [&](int64_t tile_) {
+    const int64_t i_ = tile_ * kTileM + pt;
+    const int G = p.dp / 4;
+#pragma unroll
+    for (int q = 0; q < kMaxChunks; ++q) {
+      const int gq = half + 2 * q;
+      xv[q] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+      if (gq < G && tile_ < n_tiles && i_ < p.n) {
+        if (p.vec4 && 4 * gq + 3 < p.d) {
+          xv[q] = __ldg(reinterpret_cast<const float4*>(p.x + i_ * p.d) + gq);
         } else {
+          float v[4];
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
             const int t = 4 * gq + e;
-            v[e] = (i < p.n && t < p.d) ? __ldg(p.x + i * p.d + t) : 0.0f;
+            v[e] = t < p.d ? __ldg(p.x + i_ * p.d + t) : 0.0f;
           }
-        }
-        xx = fmaf(v[0], v[0], xx); xx = fmaf(v[1], v[1], xx); xx = fmaf(v[2], v[2], xx); xx = fmaf(v[3], v[3], xx);
-        float4 hi, lo;
-        split4(v, hi, lo);
-        if (p.terms == 3) {  // A' = [x_hi | x_lo | x_hi]
-          *reinterpret_cast<float4*>(a_tile + (size_t)(gq) * lbo_a + lt * 16) = hi;
-          *reinterpret_cast<float4*>(a_tile + (size_t)(G + gq) * lbo_a + lt * 16) = lo;
-          *reinterpret_cast<float4*>(a_tile + (size_t)(2 * G + gq) * lbo_a + lt * 16) = hi;
-        } else {
-          *reinterpret_cast<float4*>(a_tile + (size_t)gq * lbo_a + lt * 16) = make_float4(v[0], v[1], v[2], v[3]);
+          xv[q] = make_float4(v[0], v[1], v[2], v[3]);
         }
       }
-      *reinterpret_cast<float4*>(a_tile + (size_t)kc_x * lbo_a + lt * 16) = make_float4(1.0f, 1.0f, 0.0f, 0.0f);
-      *reinterpret_cast<float4*>(a_tile + (size_t)(kc_x + 1) * lbo_a + lt * 16) = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    }
+  };
+  fetch_row(first);
+  for (int64_t tile = first; tile < n_tiles; tile += stride) {
+    // ---- A tile: the two threads of point tile*128 + pt split and store alternate 16-byte chunks of its row ----
+    const int64_t i = tile * kTileM + pt;
+    float xx = 0.0f;
+    {
+      const int G = p.dp / 4;
+#pragma unroll
+      for (int q = 0; q < kMaxChunks; ++q) {
+        const int gq = half + 2 * q;
+        if (gq < G) {
+          const float v[4] = {xv[q].x, xv[q].y, xv[q].z, xv[q].w};
+          xx = fmaf(v[0], v[0], xx); xx = fmaf(v[1], v[1], xx); xx = fmaf(v[2], v[2], xx); xx = fmaf(v[3], v[3], xx);
+          float4 hi, lo;
+          split4(v, hi, lo);
+          if (p.terms == 3) {  // A' = [x_hi | x_lo | x_hi]
+            *reinterpret_cast<float4*>(a_tile + (size_t)(gq) * lbo_a + pt * 16) = hi;
+            *reinterpret_cast<float4*>(a_tile + (size_t)(G + gq) * lbo_a + pt * 16) = lo;
+            *reinterpret_cast<float4*>(a_tile + (size_t)(2 * G + gq) * lbo_a + pt * 16) = hi;
+          } else {
+            *reinterpret_cast<float4*>(a_tile + (size_t)gq * lbo_a + pt * 16) = xv[q];
+          }
+        }
+      }
+      *reinterpret_cast<float4*>(a_tile + (size_t)(kc_x + half) * lbo_a + pt * 16) =
+          half == 0 ? make_float4(1.0f, 1.0f, 0.0f, 0.0f) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
     }
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -247,6 +282,7 @@ __global__ void __launch_bounds__(kCtaThreads, 1) kmeans_tc_kernel(const Params 
       }
       asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(mbar_addr) : "memory");
     }
+    fetch_row(tile + stride);  // next tile's row, in flight during this tile's MMA and epilogue
     // ---- bounded wait for the MMAs ----
     uint32_t done = 0;
     for (uint32_t it = 0; it < kWaitLimit && !done; ++it) {
@@ -265,23 +301,45 @@ __global__ void __launch_bounds__(kCtaThreads, 1) kmeans_tc_kernel(const Params 
     }
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 
-    // ---- epilogue: thread lt = TMEM lane lt = point i; four independent trackers over interleaved columns ----
+    // ---- epilogue: TMEM lane pt = point i; its two threads scan one half of the centres each, with four
+    //      independent trackers over interleaved columns; half 1 hands its result to half 0 through shared memory ----
     Top2 t0, t1, t2, t3;
     t0.init(); t1.init(); t2.init(); t3.init();
-    const uint32_t lane_addr = tmem_base + ((uint32_t)(warp_in_group * 32) << 16);
-    for (int c0 = 0; c0 < p.n_pad; c0 += 32) {
-      uint32_t r[32];
-      tmem_ld32(lane_addr + (uint32_t)c0, r);
-      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(lane_quarter * 32) << 16);
+    const int c_split = ((p.n_pad / 32 + 1) / 2) * 32;
+    const int c_begin = half == 0 ? 0 : c_split, c_end = half == 0 ? c_split : p.n_pad;
+    {
+      uint32_t ra[16], rb[16];  // two 16-column loads alternate: one is consumed while the other is in flight
+      auto scan = [&](const uint32_t (&r)[16], int c0) {
 #pragma unroll
-      for (int j = 0; j < 32; j += 4) {
-        t0.push(__uint_as_float(r[j]), c0 + j);
-        t1.push(__uint_as_float(r[j + 1]), c0 + j + 1);
-        t2.push(__uint_as_float(r[j + 2]), c0 + j + 2);
-        t3.push(__uint_as_float(r[j + 3]), c0 + j + 3);
+        for (int j = 0; j < 16; j += 4) {
+          t0.push(__uint_as_float(r[j]), c0 + j);
+          t1.push(__uint_as_float(r[j + 1]), c0 + j + 1);
+          t2.push(__uint_as_float(r[j + 2]), c0 + j + 2);
+          t3.push(__uint_as_float(r[j + 3]), c0 + j + 3);
+        }
+      };
+      if (c_begin < c_end) tmem_ld16(lane_addr + (uint32_t)c_begin, ra);
+      for (int c0 = c_begin; c0 < c_end; c0 += 32) {  // c_end - c_begin is a multiple of 32
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        tmem_ld16(lane_addr + (uint32_t)(c0 + 16), rb);
+        scan(ra, c0);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        if (c0 + 32 < c_end) tmem_ld16(lane_addr + (uint32_t)(c0 + 32), ra);
+        scan(rb, c0 + 16);
       }
     }
     t0.merge(t1); t2.merge(t3); t0.merge(t2);
+    if (half == 1) exch[pt] = make_float4(t0.best, t0.second, __int_as_float(t0.idx), xx);
+    group_sync(g);
+    if (half == 1) continue;
+    {
+      const float4 o = exch[pt];
+      Top2 other;
+      other.best = o.x; other.second = o.y; other.idx = __float_as_int(o.z);
+      t0.merge(other);
+      xx += o.w;
+    }
     const float xn = sqrtf(xx);
     // error bound of a score: L2  eps*|x||y|max ;  cosine  eps*|x|
     const float tol = p.metric == F2C_L2 ? p.eps * xn * cmax : p.eps * xn;
@@ -325,7 +383,7 @@ int kmeans_assign_tc(const float* x, const float* y, int64_t* labels, int64_t n,
   cudaError_t e = cudaMemsetAsync(head, 0, 256, st);
   if (e != cudaSuccess) return set_error(F2C_ERR_CUDA, "kmeans_assign: %s", cudaGetErrorString(e));
   const int kc = (p.terms * p.dp + 8) / 4;
-  size_t smem = (size_t)kc * (tc::kMaxN + 2 * tc::kTileM) * 16 + tc::kMaxN * 4 + 64;
+  size_t smem = (size_t)kc * (tc::kMaxN + 2 * tc::kTileM) * 16 + tc::kMaxN * 4 + 2 * tc::kTileM * 16 + 64;
   if (smem < 120 * 1024) smem = 120 * 1024;  // one CTA per SM: a second one would only wait for the TMEM columns
   e = cudaFuncSetAttribute(tc::kmeans_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return set_error(F2C_ERR_CUDA, "kmeans_assign: %s", cudaGetErrorString(e));
