@@ -172,13 +172,28 @@ __global__ void __launch_bounds__(kSqLutThreads) sq_decompress_lut_kernel(
   constexpr uint32_t MASK = NCODE - 1;
   extern __shared__ float sq_tab[];
   const int copies = 1 << log_copies;
-  for (int i = threadIdx.x; i < n_cb * NCODE; i += kSqLutThreads) {
-    const int row = i >> BITS, code = i & (int)MASK;
-    const float emin = __ldg(codebooks + row * kCodebookDim + 2), emax = __ldg(codebooks + row * kCodebookDim + 3);
-    const float mean = __ldg(codebooks + row * kCodebookDim + 4);
-    const float c = (BITS == 8 && is_signed) ? (float)(int8_t)code : (float)code;
-    const float v = sq_decode<BITS>(c, sq_scale<BITS>(emin, emax), emin, mean);
-    for (int k = 0; k < copies; ++k) sq_tab[(i << log_copies) + k] = v;
+  {
+    // a warp decodes 32 entries (one per lane), then hands them round by shuffle so that every store instruction
+    // writes 32 consecutive words (entry-major, copy-minor): no bank conflicts while building
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int n_entries = n_cb * NCODE;
+    const int per_store = 32 >> log_copies;  // entries covered by one store instruction
+    for (int e0 = warp * 32; e0 < n_entries; e0 += (kSqLutThreads / 32) * 32) {
+      const int i = e0 + lane;
+      float v = 0.0f;
+      if (i < n_entries) {
+        const int row = i >> BITS, code = i & (int)MASK;
+        const float emin = __ldg(codebooks + row * kCodebookDim + 2), emax = __ldg(codebooks + row * kCodebookDim + 3);
+        const float mean = __ldg(codebooks + row * kCodebookDim + 4);
+        const float c = (BITS == 8 && is_signed) ? (float)(int8_t)code : (float)code;
+        v = sq_decode<BITS>(c, sq_scale<BITS>(emin, emax), emin, mean);
+      }
+      for (int j = 0; j < 32; j += per_store) {
+        const int src = j + (lane >> log_copies);
+        const float vv = __shfl_sync(0xffffffffu, v, src);
+        if (e0 + src < n_entries) sq_tab[((e0 + src) << log_copies) + (lane & (copies - 1))] = vv;
+      }
+    }
   }
   __syncthreads();
   const int rows_per_cta = kSqLutThreads / chunks_per_row;
