@@ -63,13 +63,16 @@ SIGNATURES = {
     "f2c_kmeans_assign": [p, p, p, i64, i64, i64, ci, p, p],
     "f2c_kmeans_assign_static": [p, p, p, i64, i64, i64, ci, p],
     "f2c_check_csc": [p, p, ci, i64, i64, p, p],
+    "f2c_relabel_capacity": [i64],
+    "f2c_relabel_mark": [p, ci, i64, p, p, i64, p, p, p],
+    "f2c_relabel_assign": [p, ci, i64, p, p, i64, p, p, p, p, p],
     "f2c_set_tuning": [ci, ci],
     "f2c_sample_degrees": [p, p, p, ci, i64, ci, p],
     "f2c_sample_neighbors": [p, p, p, p, p, ci, i64, ci, u64, u64, p],
     "f2c_last_error": [],
     "f2c_version": [],
 }
-_RESTYPE = {"f2c_last_error": C.c_char_p, "f2c_kmeans_assign_workspace": C.c_int64}
+_RESTYPE = {"f2c_last_error": C.c_char_p, "f2c_kmeans_assign_workspace": C.c_int64, "f2c_relabel_capacity": C.c_int64}
 
 for _name, _args in SIGNATURES.items():
     _fn = getattr(lib, _name)  # AttributeError here = header and library out of step

@@ -394,3 +394,44 @@ def csr_sampling(indptr, indices, seeds, num_pick, replace=False, rng_seed=0, rn
                                        _DT[indptr.dtype], n, int(num_pick), int(rng_seed) & 0xFFFFFFFFFFFFFFFF,
                                        int(rng_offset), st))
     return sub_indptr, sub_indices
+
+
+def tensor_relabel(tensors):
+    """The reference's ``ShmTensorLib.tensor_relabel([seeds, sub_indices])`` (call sites
+    examples/dataloader.py:176-177,289-290): returns ``(unique, relabelled)`` where ``unique`` holds the distinct ids of
+    the concatenation in order of first occurrence (distinct seeds keep positions 0..len(seeds)-1, which the model
+    relies on: examples/conv.py:48-49) and ``relabelled[j]`` is ``tensors[j]`` rewritten to positions in ``unique``."""
+    tensors = list(tensors)
+    if not tensors:
+        raise RuntimeError("tensor_relabel: needs at least one tensor")
+    for t in tensors:
+        _chk(t, "ids", (torch.int32, torch.int64))
+        if t.dtype != tensors[0].dtype or t.device != tensors[0].device:
+            raise RuntimeError("tensor_relabel: all tensors must share dtype and device")
+    keys = torch.cat([t.reshape(-1) for t in tensors])
+    n = keys.numel()
+    dev, dt = keys.device, keys.dtype
+    if n == 0:
+        return keys, [t.clone() for t in tensors]
+    cap = lib.f2c_relabel_capacity(n)
+    tab_keys = torch.empty((cap,), dtype=torch.int64, device=dev)
+    tab_pos = torch.empty((cap,), dtype=torch.int32, device=dev)
+    first = torch.empty((n,), dtype=torch.int32, device=dev)
+    err = torch.empty((1,), dtype=torch.int32, device=dev)
+    st = _stream(keys)
+    with _on(keys):
+        check(lib.f2c_relabel_mark(_ptr(keys), _DT[dt], n, _ptr(tab_keys), _ptr(tab_pos), cap, _ptr(first), _ptr(err), st))
+        incl = torch.cumsum(first, 0, dtype=dt)
+        rank = incl - first.to(dt)
+        n_unique = int(incl[-1].item())
+        if int(err.item()) != 0:
+            raise RuntimeError("tensor_relabel: hash table overflow")
+        unique = torch.empty((n_unique,), dtype=dt, device=dev)
+        relabelled = torch.empty((n,), dtype=dt, device=dev)
+        check(lib.f2c_relabel_assign(_ptr(keys), _DT[dt], n, _ptr(tab_keys), _ptr(tab_pos), cap, _ptr(first), _ptr(rank),
+                                     _ptr(unique), _ptr(relabelled), st))
+    out, off = [], 0
+    for t in tensors:
+        out.append(relabelled[off:off + t.numel()].reshape(t.shape))
+        off += t.numel()
+    return unique, out

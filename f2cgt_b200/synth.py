@@ -47,21 +47,15 @@ def sample_blocks(indptr, indices, seeds, fan_out, rng_seed=0):
       indices_global         neighbour ids in the graph's numbering (index the full table directly),
       indices_local          the same edges relabelled to positions in src_nodes (index gathered rows).
     """
-    num_nodes = indptr.numel() - 1
-    device = indptr.device
     frontier = seeds
     blocks = []
     for hop, num_pick in enumerate(reversed(list(fan_out))):
         sub_indptr, sub_indices = ops.csr_sampling(indptr, indices, frontier, num_pick, False, rng_seed, hop)
-        mark = torch.zeros(num_nodes, dtype=torch.bool, device=device)
-        mark[frontier] = True
-        fresh = sub_indices[~mark[sub_indices]]
-        fresh = torch.unique(fresh)
-        src_nodes = torch.cat([frontier, fresh])
-        pos = torch.full((num_nodes,), -1, dtype=indptr.dtype, device=device)
-        pos[src_nodes] = torch.arange(src_nodes.numel(), dtype=indptr.dtype, device=device)
+        # relabel as the reference's loader does (examples/dataloader.py:176-177): distinct ids of [frontier,
+        # sampled neighbours] in order of first occurrence, so the frontier stays a prefix
+        src_nodes, (_, local) = ops.tensor_relabel([frontier, sub_indices])
         blocks.insert(0, dict(dst_nodes=frontier, src_nodes=src_nodes, indptr=sub_indptr, indices_global=sub_indices,
-                              indices_local=pos[sub_indices]))
+                              indices_local=local))
         frontier = src_nodes
     return blocks
 

@@ -203,6 +203,21 @@ int f2c_sample_neighbors(const void* indptr, const void* indices, const void* se
                          void* out_indices, int index_dtype, int64_t n_seeds, int num_pick, uint64_t rng_seed,
                          uint64_t rng_offset, void* stream);
 
+/* tensor_relabel([seeds, sub_indices]) of the reference's absent ShmTensor submodule (call sites
+ * examples/dataloader.py:176-177,289-290): the distinct ids of `keys` (the concatenation, seeds first) are numbered
+ * 0..n_unique-1 in order of first occurrence, so distinct seeds keep their positions.  Two steps around a prefix sum
+ * the caller owns: mark writes first[i] = 1 where position i is the first occurrence of its id (building a hash table
+ * of `capacity` = f2c_relabel_capacity(n) slots: table_keys 8 B, table_pos 4 B per slot); the caller computes
+ * rank = exclusive prefix sum of first (same dtype as the ids) and n_unique = its total; assign writes
+ * unique[rank[i]] = keys[i] at first occurrences and relabelled[i] = new number of keys[i].  *error_flag (device)
+ * becomes non-zero if the table overflowed (never with the advised capacity). */
+int64_t f2c_relabel_capacity(int64_t n_keys);
+int f2c_relabel_mark(const void* keys, int index_dtype, int64_t n_keys, void* table_keys, void* table_pos, int64_t capacity,
+                     int32_t* first, int32_t* error_flag, void* stream);
+int f2c_relabel_assign(const void* keys, int index_dtype, int64_t n_keys, const void* table_keys, const void* table_pos,
+                       int64_t capacity, const int32_t* first, const void* rank, void* unique, void* relabelled,
+                       void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -237,3 +237,22 @@ def sample_neighbors(indptr, indices, seeds, num_pick, rng_seed=0, rng_offset=0)
     lib().orc_sample_neighbors(_p(indptr), _p(indices), _p(seeds), _p(out_indptr), _p(out_indices), i64(seeds.shape[0]),
                                ci(num_pick), C.c_uint64(rng_seed), C.c_uint64(rng_offset))
     return out_indptr, out_indices
+
+
+def tensor_relabel(tensors):
+    """Contract of the reference's ``tensor_relabel([seeds, sub_indices])`` as its call sites use it
+    (examples/dataloader.py:176-177,289-290; examples/conv.py:48-49): distinct ids of the concatenation numbered in
+    order of first occurrence (so distinct seeds keep positions 0..len(seeds)-1), every id replaced by its number."""
+    arrs = [np.asarray(t).reshape(-1) for t in tensors]
+    keys = np.concatenate(arrs) if arrs else np.zeros(0, np.int64)
+    _, first_idx, inverse = np.unique(keys, return_index=True, return_inverse=True)
+    order = np.argsort(first_idx, kind="stable")          # sorted-unique slots in order of first occurrence
+    rank_of_slot = np.empty_like(order)
+    rank_of_slot[order] = np.arange(order.size)
+    unique = keys[np.sort(first_idx)]
+    relabelled = rank_of_slot[inverse].astype(keys.dtype)
+    out, off = [], 0
+    for a in arrs:
+        out.append(relabelled[off:off + a.size])
+        off += a.size
+    return unique, out

@@ -1,0 +1,97 @@
+"""GPU parity of the minibatch builders: neighbour sampling and relabelling (stand-ins for the reference's absent
+ShmTensor operators, contracts read from examples/dataloader.py:167-182) against the CPU oracle."""
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+torch = pytest.importorskip("torch")
+
+
+def dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def host(t):
+    torch.cuda.synchronize()
+    return t.cpu().numpy()
+
+
+def small_graph(rng, n, max_deg, dtype=np.int64):
+    deg = rng.integers(0, max_deg + 1, n)
+    indptr = np.concatenate([[0], np.cumsum(deg)]).astype(dtype)
+    indices = rng.integers(0, n, int(indptr[-1])).astype(dtype)
+    return indptr, indices
+
+
+@pytest.mark.parametrize("idx", [np.int64, np.int32])
+@pytest.mark.parametrize("num_pick", [1, 5, 12, 64])
+def test_csr_sampling_equals_oracle(capi, oracle, idx, num_pick):
+    from f2cgt_b200 import ops
+    rng = np.random.default_rng(num_pick)
+    indptr, indices = small_graph(rng, 3000, 40, idx)
+    seeds = rng.choice(3000, 700, replace=False).astype(idx)
+    ip, ix = ops.csr_sampling(dev(indptr), dev(indices), dev(seeds), num_pick, False, rng_seed=11, rng_offset=3)
+    want_ip, want_ix = oracle.sample_neighbors(indptr, indices, seeds, num_pick, 11, 3)
+    assert np.array_equal(host(ip), want_ip) and np.array_equal(host(ix), want_ix)
+    # contract: min(deg, num_pick) distinct positions of the seed's own adjacency list
+    ip, ix = host(ip), host(ix)
+    for j, v in enumerate(seeds[:200]):
+        mine = ix[ip[j]:ip[j + 1]]
+        adj = indices[indptr[v]:indptr[v + 1]]
+        assert len(mine) == min(len(adj), num_pick)
+        assert np.all(np.isin(mine, adj))
+        if len(adj) <= num_pick:
+            assert np.array_equal(mine, adj)
+
+
+def test_csr_sampling_is_uniform():
+    """Every neighbour of a high-degree seed is picked with probability num_pick / degree (chi-square over seeds)."""
+    from f2cgt_b200 import ops
+    deg, num_pick, copies = 40, 10, 20000
+    indptr = np.arange(0, (copies + 1) * deg, deg, dtype=np.int64)
+    indices = np.tile(np.arange(deg, dtype=np.int64), copies)  # every node has neighbours 0..39
+    seeds = np.arange(copies, dtype=np.int64)
+    _, ix = ops.csr_sampling(dev(indptr), dev(indices), dev(seeds), num_pick, False, rng_seed=5)
+    counts = np.bincount(host(ix), minlength=deg).astype(np.float64)
+    expect = copies * num_pick / deg
+    chi2 = ((counts - expect) ** 2 / expect).sum()
+    assert chi2 < 90.0  # 39 degrees of freedom: P(chi2 > 90) ~ 1e-5
+
+
+@pytest.mark.parametrize("idx", [np.int64, np.int32])
+@pytest.mark.parametrize("n_seeds,n_ids,space", [(0, 0, 10), (5, 0, 100), (1024, 12000, 5000), (300, 50000, 1 << 30), (1, 100000, 7)])
+def test_tensor_relabel_equals_oracle(capi, oracle, idx, n_seeds, n_ids, space):
+    from f2cgt_b200 import ops
+    rng = np.random.default_rng(n_seeds + n_ids)
+    seeds = rng.choice(space, n_seeds, replace=False).astype(idx) if n_seeds else np.zeros(0, idx)
+    ids = rng.integers(0, space, n_ids).astype(idx)
+    uniq, (rs, ri) = ops.tensor_relabel([dev(seeds), dev(ids)])
+    want_u, (want_s, want_i) = oracle.tensor_relabel([seeds, ids])
+    assert np.array_equal(host(uniq), want_u)
+    assert np.array_equal(host(rs), want_s) and np.array_equal(host(ri), want_i)
+    # the contract itself: seeds keep their positions, unique[relabelled] reproduces the ids
+    assert np.array_equal(host(rs), np.arange(n_seeds))
+    if n_ids:
+        assert np.array_equal(host(uniq)[host(ri)], ids)
+
+
+def test_blocks_feed_the_fused_kernel(capi, oracle):
+    """sample -> relabel -> block: destination nodes are a prefix of the source nodes in every hop, and aggregating the
+    block-local rows gives the rows obtained by global ids."""
+    from f2cgt_b200 import synth
+    indptr, indices = synth.power_law_graph(20000, 20, 2.1, seed=3, device="cuda")
+    seeds = torch.randperm(20000, device="cuda")[:256]
+    blocks = synth.sample_blocks(indptr, indices, seeds, (5, 4, 3), rng_seed=2)
+    assert len(blocks) == 3 and torch.equal(blocks[-1]["dst_nodes"], seeds)
+    codes, cb = synth.sq_table_from_normal(20000, 128, 4, 128, seed=0, device="cuda")
+    for b in blocks:
+        n_dst = b["dst_nodes"].numel()
+        assert torch.equal(b["src_nodes"][:n_dst], b["dst_nodes"])
+        assert b["src_nodes"].unique().numel() == b["src_nodes"].numel()
+        assert torch.equal(b["src_nodes"][b["indices_local"]], b["indices_global"])
+        by_global = capi.sq_decompress_spmm_csr(codes, cb, b["indptr"], b["indices_global"], 4, 128, 128)
+        gathered = codes[b["src_nodes"]]
+        by_local = capi.sq_decompress_spmm_csr(gathered, cb, b["indptr"], b["indices_local"], 4, 128, 128)
+        assert torch.equal(by_global, by_local)
+    for outer, inner in zip(blocks[:-1], blocks[1:]):
+        assert torch.equal(outer["dst_nodes"], inner["src_nodes"])

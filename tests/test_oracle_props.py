@@ -148,3 +148,19 @@ def test_kmeans_oracle_matches_numpy(oracle):
     # first minimum wins on exact ties
     c2 = np.concatenate([c, c[:3]])
     assert oracle.kmeans_assign(x, c2, "l2").max() < 17
+
+
+def test_tensor_relabel_contract(oracle):
+    O = oracle
+    """Seeds keep their positions, ids are numbered by first occurrence, unique[relabelled] gives the ids back
+    (what examples/dataloader.py:176-182 and examples/conv.py:48-49 rely on)."""
+    rng = np.random.default_rng(4)
+    seeds = rng.choice(1000, 50, replace=False)
+    ids = rng.integers(0, 1000, 5000)
+    uniq, (rs, ri) = O.tensor_relabel([seeds, ids])
+    assert np.array_equal(rs, np.arange(50)) and np.array_equal(uniq[:50], seeds)
+    assert np.array_equal(uniq[ri], ids) and len(np.unique(uniq)) == len(uniq)
+    first_seen = [np.flatnonzero(np.concatenate([seeds, ids]) == u)[0] for u in uniq]
+    assert first_seen == sorted(first_seen)
+    u0, (e,) = O.tensor_relabel([np.zeros(0, np.int64)])
+    assert u0.size == 0 and e.size == 0
