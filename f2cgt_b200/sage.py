@@ -1,0 +1,170 @@
+"""DGL-free GraphSAGE over compressed features, mirroring the reference's training stack on top of the library:
+
+* ``CompressionManager`` - what examples/compress.py keeps: codecs, codebooks and tables of a one- or two-level
+  compressed feature matrix.  Here the tables stay resident in HBM and are addressed by GLOBAL node id, so there is
+  no gathered copy of the codes per minibatch: ``aggregate`` is the fused decode + mean over a block's CSC,
+  ``decode_rows`` decodes the rows of given nodes (the same fused kernel over an identity CSC: the mean of one
+  neighbour is that neighbour, bit for bit).
+* ``MySAGEConv`` - the fused first layer (examples/conv.py:9-76): ``fc_self(h_self) + fc_neigh(mean of decoded
+  neighbours)``, ``fc_neigh`` without bias.
+* ``SAGEConv`` - mean SAGE layer for hidden features (what the reference takes from DGL), aggregation through
+  ``spmm_csr`` with a backward pass over the transposed block.
+* ``SAGE`` - examples/models.py:10-42: ReLU + dropout between layers.
+* ``GPUSamplingDataloader`` - examples/dataloader.py:154-192: per minibatch, hops in reversed(fan_out) order from the
+  seeds with ``csr_sampling`` + ``tensor_relabel``; yields (input_nodes, output_nodes, blocks).
+
+Blocks are dicts with ``indptr`` (CSC over the destination nodes), ``indices_local`` (positions in ``src_nodes``),
+``indices_global``, ``src_nodes``, ``dst_nodes``; destination nodes are a prefix of the source nodes.
+"""
+import torch
+from torch import nn
+
+from . import ops
+
+
+class CompressionManager:
+    """methods: ["sq"] | ["vq"] | ["sq", "vq"] (two-level: level 0 = hot rows, level 1 = every row)."""
+
+    def __init__(self, feat_dim, methods, configs, codebooks, tables, slot=None):
+        self.feat_dim = int(feat_dim)
+        self.methods = list(methods)
+        self.configs = list(configs)      # per level (column_slice, target_bits) as the reference stores them
+        self.codebooks = list(codebooks)
+        self.tables = list(tables)
+        self.slot = slot                  # int32 [n_nodes]: row of the hot table, -1 for cold nodes (two-level only)
+        self.is_two_level = len(self.methods) >= 2
+        if self.is_two_level and (self.methods != ["sq", "vq"] or slot is None):
+            raise ValueError("two-level compression is hot SQ rows over a VQ table, with a slot array")
+
+    def aggregate(self, indptr, indices_global, dropout=None):
+        if self.is_two_level:
+            cs, bits = self.configs[0]
+            return ops.two_level_decompress_spmm_csr(self.tables[0], self.codebooks[0], bits, cs, self.tables[1], self.codebooks[1],
+                                                     self.slot, indptr, indices_global, self.feat_dim, dropout=dropout)
+        if self.methods[0] == "vq":
+            return ops.vq_decompress_spmm_csr(self.tables[0], self.codebooks[0], indptr, indices_global, self.feat_dim, dropout=dropout)
+        cs, bits = self.configs[0]
+        return ops.sq_decompress_spmm_csr(self.tables[0], self.codebooks[0], indptr, indices_global, bits, cs, self.feat_dim,
+                                          dropout=dropout)
+
+    def decode_rows(self, nodes):
+        ident = torch.arange(nodes.numel() + 1, dtype=nodes.dtype, device=nodes.device)
+        return self.aggregate(ident, nodes)
+
+
+class _MeanAggregate(torch.autograd.Function):
+    """out[d] = mean over the block's neighbours of h[src]; backward scatters grad / deg along the transposed block."""
+
+    @staticmethod
+    def forward(ctx, h, indptr, indices, n_src):
+        ctx.save_for_backward(indptr, indices)
+        ctx.n_src = n_src
+        return ops.spmm_csr(h, indptr, indices)
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        indptr, indices = ctx.saved_tensors
+        n_dst = indptr.numel() - 1
+        deg = (indptr[1:] - indptr[:-1]).clamp_min(1).to(grad_out.dtype)
+        scaled = (grad_out / deg[:, None]).contiguous()
+        # transposed block: edges sorted by source, destination of every edge as the "neighbour"
+        dst_of_edge = torch.repeat_interleave(torch.arange(n_dst, device=indptr.device, dtype=indptr.dtype), indptr[1:] - indptr[:-1])
+        order = torch.argsort(indices, stable=True)
+        counts = torch.bincount(indices, minlength=ctx.n_src)
+        t_indptr = torch.zeros(ctx.n_src + 1, dtype=indptr.dtype, device=indptr.device)
+        torch.cumsum(counts, 0, out=t_indptr[1:])
+        grad_h = ops.spmm_csr(scaled, t_indptr, dst_of_edge[order].contiguous(), reduce="sum")
+        return grad_h, None, None, None
+
+
+class MySAGEConv(nn.Module):
+    def __init__(self, in_feats, out_feats, compression_manager, bias=True):
+        super().__init__()
+        self.fc_neigh = nn.Linear(in_feats, out_feats, bias=False)
+        self.fc_self = nn.Linear(in_feats, out_feats, bias=bias)
+        self.sm = compression_manager
+        gain = nn.init.calculate_gain("relu")
+        nn.init.xavier_uniform_(self.fc_self.weight, gain=gain)
+        nn.init.xavier_uniform_(self.fc_neigh.weight, gain=gain)
+
+    def forward(self, block, _unused=None):
+        h_neigh = self.sm.aggregate(block["indptr"], block["indices_global"])  # raw codes in, no autograd through it
+        h_self = self.sm.decode_rows(block["dst_nodes"])
+        return self.fc_self(h_self) + self.fc_neigh(h_neigh)
+
+
+class SAGEConv(nn.Module):
+    def __init__(self, in_feats, out_feats, bias=True):
+        super().__init__()
+        self.fc_neigh = nn.Linear(in_feats, out_feats, bias=False)
+        self.fc_self = nn.Linear(in_feats, out_feats, bias=bias)
+        gain = nn.init.calculate_gain("relu")
+        nn.init.xavier_uniform_(self.fc_self.weight, gain=gain)
+        nn.init.xavier_uniform_(self.fc_neigh.weight, gain=gain)
+
+    def forward(self, block, h):
+        n_dst = block["dst_nodes"].numel()
+        h32 = h.float().contiguous()
+        h_neigh = _MeanAggregate.apply(h32, block["indptr"], block["indices_local"], h.shape[0])
+        return self.fc_self(h[:n_dst]) + self.fc_neigh(h_neigh)
+
+
+class SAGE(nn.Module):
+    def __init__(self, in_feats, n_hidden, n_classes, n_layers, dropout, cm):
+        super().__init__()
+        self.layers = nn.ModuleList()
+        for i in range(n_layers):
+            in_dim = in_feats if i == 0 else n_hidden
+            out_dim = n_classes if i == n_layers - 1 else n_hidden
+            self.layers.append(MySAGEConv(in_dim, out_dim, cm) if i == 0 else SAGEConv(in_dim, out_dim))
+        self.dropout = nn.Dropout(dropout)
+
+    def forward(self, blocks, x=None):
+        h = x
+        for i, (layer, block) in enumerate(zip(self.layers, blocks)):
+            h = layer(block, h)
+            if i != len(self.layers) - 1:
+                h = self.dropout(torch.relu(h))
+        return h
+
+
+class GPUSamplingDataloader:
+    """Seeds are split contiguously over the ranks (examples/dataloader.py:102-108), shuffled per epoch."""
+
+    def __init__(self, indptr, indices, seeds, batchsize, num_picks, rank=0, world=1, shuffle=True, rng_seed=0):
+        self.indptr, self.indices = indptr, indices
+        self.batchsize, self.num_picks = int(batchsize), list(num_picks)
+        self.shuffle, self.rng_seed, self.epoch = shuffle, rng_seed, 0
+        per = (seeds.numel() + world - 1) // world
+        self.seeds = seeds[rank * per:(rank + 1) * per]
+        self.rank = rank
+
+    def __len__(self):
+        return (self.seeds.numel() + self.batchsize - 1) // self.batchsize
+
+    def __iter__(self):
+        self.curr = 0
+        if self.shuffle:
+            g = torch.Generator(device=self.seeds.device)
+            g.manual_seed(self.rng_seed * 1000003 + self.epoch)
+            self.order = self.seeds[torch.randperm(self.seeds.numel(), generator=g, device=self.seeds.device)]
+        else:
+            self.order = self.seeds
+        self.epoch += 1
+        return self
+
+    def __next__(self):
+        if self.curr >= len(self):
+            raise StopIteration
+        seeds = self.order[self.curr * self.batchsize:(self.curr + 1) * self.batchsize]
+        step = self.curr
+        self.curr += 1
+        output_nodes = seeds
+        blocks = []
+        for hop, num_pick in enumerate(reversed(self.num_picks)):
+            sub_indptr, sub_indices = ops.csr_sampling(self.indptr, self.indices, seeds, num_pick, False,
+                                                       rng_seed=(self.rng_seed * 7919 + self.epoch) * 65536 + self.rank, rng_offset=step * 8 + hop)
+            unique, (_, local) = ops.tensor_relabel([seeds, sub_indices])
+            blocks.insert(0, dict(dst_nodes=seeds, src_nodes=unique, indptr=sub_indptr, indices_global=sub_indices, indices_local=local))
+            seeds = unique
+        return seeds, output_nodes, blocks
