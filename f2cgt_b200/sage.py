@@ -52,6 +52,21 @@ class CompressionManager:
         return self.aggregate(ident, nodes)
 
 
+def _bucket(n):
+    """Row counts of sampled blocks change every step; the matrix products behind the Linear layers pick (and cache)
+    their algorithms per shape, so inputs are zero-padded to a few recurring row counts."""
+    step = 4096 if n > 16384 else 512 if n > 2048 else 128
+    return (n + step - 1) // step * step
+
+
+def _linear_rows(fc, x):
+    n = x.shape[0]
+    m = _bucket(n)
+    if m != n:
+        x = torch.nn.functional.pad(x, (0, 0, 0, m - n))
+    return fc(x)[:n]
+
+
 class _MeanAggregate(torch.autograd.Function):
     """out[d] = mean over the block's neighbours of h[src]; backward scatters grad / deg along the transposed block."""
 
@@ -68,7 +83,8 @@ class _MeanAggregate(torch.autograd.Function):
         deg = (indptr[1:] - indptr[:-1]).clamp_min(1).to(grad_out.dtype)
         scaled = (grad_out / deg[:, None]).contiguous()
         # transposed block: edges sorted by source, destination of every edge as the "neighbour"
-        dst_of_edge = torch.repeat_interleave(torch.arange(n_dst, device=indptr.device, dtype=indptr.dtype), indptr[1:] - indptr[:-1])
+        dst_of_edge = torch.repeat_interleave(torch.arange(n_dst, device=indptr.device, dtype=indptr.dtype), indptr[1:] - indptr[:-1],
+                                              output_size=indices.numel())
         order = torch.argsort(indices, stable=True)
         counts = torch.bincount(indices, minlength=ctx.n_src)
         t_indptr = torch.zeros(ctx.n_src + 1, dtype=indptr.dtype, device=indptr.device)
@@ -90,7 +106,7 @@ class MySAGEConv(nn.Module):
     def forward(self, block, _unused=None):
         h_neigh = self.sm.aggregate(block["indptr"], block["indices_global"])  # raw codes in, no autograd through it
         h_self = self.sm.decode_rows(block["dst_nodes"])
-        return self.fc_self(h_self) + self.fc_neigh(h_neigh)
+        return _linear_rows(self.fc_self, h_self) + _linear_rows(self.fc_neigh, h_neigh)
 
 
 class SAGEConv(nn.Module):
@@ -106,7 +122,7 @@ class SAGEConv(nn.Module):
         n_dst = block["dst_nodes"].numel()
         h32 = h.float().contiguous()
         h_neigh = _MeanAggregate.apply(h32, block["indptr"], block["indices_local"], h.shape[0])
-        return self.fc_self(h[:n_dst]) + self.fc_neigh(h_neigh)
+        return _linear_rows(self.fc_self, h[:n_dst]) + _linear_rows(self.fc_neigh, h_neigh)
 
 
 class SAGE(nn.Module):
