@@ -9,8 +9,9 @@
 //  * Accuracy.  TF32 keeps 10 mantissa bits, which would flip near ties, so both operands are split
 //    x = hi + lo (hi = top 19 bits) and the products hi*hi + lo*hi + hi*lo are obtained in ONE GEMM by
 //    concatenating along K:  A' = [x_hi | x_lo | x_hi],  B' = [y_hi | y_hi | y_lo]  (K = 3d), which is
-//    fp32-accurate to ~2^-19.  For d > 32 (operands would not fit in shared memory) a single TF32 pass is
-//    used with a proportionally wider tolerance.
+//    fp32-accurate to ~2^-19.  For 32 < d <= 64 those operands would not fit in shared memory; there the split is
+//    into bf16 pairs x = b1 + b2 (+ a rest below 2^-18 |x|) with the same concatenation on kind::f16
+//    (half the bytes per value), accurate to ~2^-16.
 //  * The whole score comes out of the GEMM.  argmin_c |y_c|^2 - 2 x.y_c = argmax_c (x.y_c - |y_c|^2 / 2): one
 //    more K step carries [1, 1, 0...] on the point side and the split of -|y_c|^2/2 on the centre side
 //    (cosine: the centre rows are pre-scaled by 1/|y_c| instead), so the epilogue is a pure running
@@ -28,6 +29,8 @@
 //    MMAs.  Every wait on an MMA-completion mbarrier is bounded; on expiry the group records an error code
 //    and leaves, and the CTA frees its TMEM at the common exit.
 #include <mutex>
+
+#include <cuda_bf16.h>
 
 #include "common.cuh"
 
@@ -64,6 +67,31 @@ __device__ __forceinline__ void mma_tf32(uint32_t d_tmem, uint64_t a_desc, uint6
       : "memory");
 }
 
+__device__ __forceinline__ void mma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t"
+      "}\n" ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u)
+      : "memory");
+}
+
+// x = b1 + b2 + (rest below 2^-18 |x|) with b1, b2 bf16 (round to nearest): eight values -> two 16-byte chunks
+__device__ __forceinline__ void split8_bf16(const float (&v)[8], uint4& c1, uint4& c2) {
+  uint32_t w1[4], w2[4];
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    const __nv_bfloat16 a1 = __float2bfloat16_rn(v[2 * e]), b1 = __float2bfloat16_rn(v[2 * e + 1]);
+    const __nv_bfloat16 a2 = __float2bfloat16_rn(v[2 * e] - __bfloat162float(a1));
+    const __nv_bfloat16 b2 = __float2bfloat16_rn(v[2 * e + 1] - __bfloat162float(b1));
+    w1[e] = (uint32_t)__bfloat16_as_ushort(a1) | ((uint32_t)__bfloat16_as_ushort(b1) << 16);
+    w2[e] = (uint32_t)__bfloat16_as_ushort(a2) | ((uint32_t)__bfloat16_as_ushort(b2) << 16);
+  }
+  c1 = make_uint4(w1[0], w1[1], w1[2], w1[3]);
+  c2 = make_uint4(w2[0], w2[1], w2[2], w2[3]);
+}
+
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
@@ -94,6 +122,7 @@ struct Params {
   int k, d;
   int dp;      // d padded to a multiple of 8
   int terms;   // 3: split product, 1: plain TF32
+  int bf16;    // 1: operands are bf16 pairs (x = b1 + b2), A' = [x1 | x2 | x1], B' = [y1 | y1 | y2], kind::f16 (32 < d <= 64)
   int n_pad;   // k padded to a multiple of 32 (epilogue reads 32 columns at a time; MMA N needs 16)
   int metric;
   int vec4;    // rows of x can be read as float4
@@ -141,8 +170,9 @@ __global__ void __launch_bounds__(kCtaThreads, 1) kmeans_tc_kernel(const Params 
   const int pt = lt & 127;           // its point of the tile = its TMEM lane
   const int half = lt >> 7;          // which half of the row's K chunks it loads and which half of the centres it scans
   const int lane_quarter = (lt >> 5) & 3;
-  const int kc = (p.terms * p.dp + 8) / 4;  // 16-byte K chunks per operand row (the last two carry the norm term)
-  const int kc_x = p.terms * p.dp / 4;
+  // 16-byte K chunks per operand row (the last two carry the norm term): 4 tf32 or 8 bf16 values per chunk
+  const int kc_x = p.bf16 ? 3 * p.dp / 8 : p.terms * p.dp / 4;
+  const int kc = kc_x + 2;
   const uint32_t lbo_b = kMaxN * 16, lbo_a = kTileM * 16, sbo = 128;
   unsigned char* b_tile = smem;
   unsigned char* a_tile = smem + (size_t)kc * lbo_b + (size_t)g * kc * lbo_a;
@@ -172,7 +202,23 @@ __global__ void __launch_bounds__(kCtaThreads, 1) kmeans_tc_kernel(const Params 
       for (int t = 0; t < p.d; ++t) { const float v = __ldg(p.y + (int64_t)c * p.d + t); nrm = fmaf(v, v, nrm); }
     // cosine: rows are scaled to unit length (zero rows stay zero); L2: rows as they are
     const float row_scale = p.metric == F2C_COSINE ? (nrm > 0.0f ? 1.0f / sqrtf(nrm) : 0.0f) : 1.0f;
-    for (int gq = 0; gq < G; ++gq) {
+    if (p.bf16) {
+      const int C = p.dp / 8;
+      for (int cq = 0; cq < C; ++cq) {
+        float v[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          const int t = 8 * cq + e;
+          v[e] = (c < p.k && t < p.d) ? __ldg(p.y + (int64_t)c * p.d + t) * row_scale : 0.0f;
+        }
+        uint4 c1, c2;
+        split8_bf16(v, c1, c2);  // B' = [y1 | y1 | y2]
+        *reinterpret_cast<uint4*>(b_tile + (size_t)(cq) * lbo_b + c * 16) = c1;
+        *reinterpret_cast<uint4*>(b_tile + (size_t)(C + cq) * lbo_b + c * 16) = c1;
+        *reinterpret_cast<uint4*>(b_tile + (size_t)(2 * C + cq) * lbo_b + c * 16) = c2;
+      }
+    }
+    for (int gq = 0; gq < (p.bf16 ? 0 : G); ++gq) {
       float v[4];
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
@@ -191,8 +237,16 @@ __global__ void __launch_bounds__(kCtaThreads, 1) kmeans_tc_kernel(const Params 
     }
     // norm term: -|y_c|^2 / 2 split in two TF32 values (L2), 0 (cosine), a value that never wins (padding)
     float h = c < p.k ? (p.metric == F2C_L2 ? -0.5f * nrm : 0.0f) : -1e30f;
-    const float h_hi = __uint_as_float(__float_as_uint(h) & 0xFFFFE000u);
-    *reinterpret_cast<float4*>(b_tile + (size_t)kc_x * lbo_b + c * 16) = make_float4(h_hi, h - h_hi, 0.0f, 0.0f);
+    if (p.bf16) {  // three bf16 pieces of h against three ones on the point side
+      const __nv_bfloat16 h1 = __float2bfloat16_rn(h);
+      const __nv_bfloat16 h2 = __float2bfloat16_rn(h - __bfloat162float(h1));
+      const __nv_bfloat16 h3 = __float2bfloat16_rn(h - __bfloat162float(h1) - __bfloat162float(h2));
+      *reinterpret_cast<uint4*>(b_tile + (size_t)kc_x * lbo_b + c * 16) =
+          make_uint4((uint32_t)__bfloat16_as_ushort(h1) | ((uint32_t)__bfloat16_as_ushort(h2) << 16), (uint32_t)__bfloat16_as_ushort(h3), 0u, 0u);
+    } else {
+      const float h_hi = __uint_as_float(__float_as_uint(h) & 0xFFFFE000u);
+      *reinterpret_cast<float4*>(b_tile + (size_t)kc_x * lbo_b + c * 16) = make_float4(h_hi, h - h_hi, 0.0f, 0.0f);
+    }
     *reinterpret_cast<float4*>(b_tile + (size_t)(kc_x + 1) * lbo_b + c * 16) = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
     scratch[c] = c < p.k ? nrm : 0.0f;
   }
@@ -207,7 +261,9 @@ __global__ void __launch_bounds__(kCtaThreads, 1) kmeans_tc_kernel(const Params 
   const bool bad_centres = !(poison == 0.0f);
   cmax = sqrtf(cmax);
 
-  const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(p.n_pad >> 3) << 17) | ((uint32_t)(kTileM >> 4) << 24);
+  // instruction descriptor: fp32 accumulate; A and B formats tf32 (2, kind::tf32) or bf16 (1, kind::f16); N / 8; M / 16
+  const uint32_t fmt = p.bf16 ? 1u : 2u;
+  const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(p.n_pad >> 3) << 17) | ((uint32_t)(kTileM >> 4) << 24);
   const int ksteps = kc / 2;  // one MMA consumes 8 tf32 = two 16-byte chunks of K
   const uint32_t mbar_addr = smem_u32(mbar + g);
   uint32_t parity = 0;
@@ -223,7 +279,7 @@ __global__ void __launch_bounds__(kCtaThreads, 1) kmeans_tc_kernel(const Params 
     const int G = p.dp / 4;
 #pragma unroll
     for (int q = 0; q < kMaxChunks; ++q) {
-      const int gq = half + 2 * q;
+      const int gq = p.bf16 ? 2 * (half + 2 * (q >> 1)) + (q & 1) : half + 2 * q;
       xv[q] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
       if (gq < G && tile_ < n_tiles && i_ < p.n) {
         if (p.vec4 && 4 * gq + 3 < p.d) {
@@ -247,8 +303,26 @@ __global__ void __launch_bounds__(kCtaThreads, 1) kmeans_tc_kernel(const Params 
     float xx = 0.0f;
     {
       const int G = p.dp / 4;
+      if (p.bf16) {
+        const int C = p.dp / 8;
 #pragma unroll
-      for (int q = 0; q < kMaxChunks; ++q) {
+        for (int q2 = 0; q2 < kMaxChunks / 2; ++q2) {
+          const int cq = half + 2 * q2;  // bf16 chunk = float4 chunks 2 cq, 2 cq + 1 = xv[2 q2], xv[2 q2 + 1]
+          if (cq < C) {
+            const float v[8] = {xv[2 * q2].x, xv[2 * q2].y, xv[2 * q2].z, xv[2 * q2].w,
+                                xv[2 * q2 + 1].x, xv[2 * q2 + 1].y, xv[2 * q2 + 1].z, xv[2 * q2 + 1].w};
+#pragma unroll
+            for (int e = 0; e < 8; ++e) xx = fmaf(v[e], v[e], xx);
+            uint4 c1, c2;
+            split8_bf16(v, c1, c2);  // A' = [x1 | x2 | x1]
+            *reinterpret_cast<uint4*>(a_tile + (size_t)(cq) * lbo_a + pt * 16) = c1;
+            *reinterpret_cast<uint4*>(a_tile + (size_t)(C + cq) * lbo_a + pt * 16) = c2;
+            *reinterpret_cast<uint4*>(a_tile + (size_t)(2 * C + cq) * lbo_a + pt * 16) = c1;
+          }
+        }
+      }
+#pragma unroll
+      for (int q = 0; q < (p.bf16 ? 0 : kMaxChunks); ++q) {
         const int gq = half + 2 * q;
         if (gq < G) {
           const float v[4] = {xv[q].x, xv[q].y, xv[q].z, xv[q].w};
@@ -264,8 +338,10 @@ __global__ void __launch_bounds__(kCtaThreads, 1) kmeans_tc_kernel(const Params 
           }
         }
       }
-      *reinterpret_cast<float4*>(a_tile + (size_t)(kc_x + half) * lbo_a + pt * 16) =
-          half == 0 ? make_float4(1.0f, 1.0f, 0.0f, 0.0f) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+      // norm-term columns: ones against the pieces of -|y|^2 / 2 (two tf32 ones, or three bf16 ones = 0x3F80 each)
+      *reinterpret_cast<uint4*>(a_tile + (size_t)(kc_x + half) * lbo_a + pt * 16) =
+          half != 0 ? make_uint4(0u, 0u, 0u, 0u)
+                    : (p.bf16 ? make_uint4(0x3F803F80u, 0x00003F80u, 0u, 0u) : make_uint4(0x3F800000u, 0x3F800000u, 0u, 0u));
     }
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -278,7 +354,8 @@ __global__ void __launch_bounds__(kCtaThreads, 1) kmeans_tc_kernel(const Params 
       for (int s_ = 0; s_ < ksteps; ++s_) {
         const uint64_t a_desc = make_desc(a_addr + (uint32_t)s_ * 2u * lbo_a, lbo_a, sbo);
         const uint64_t b_desc = make_desc(b_addr + (uint32_t)s_ * 2u * lbo_b, lbo_b, sbo);
-        mma_tf32(tmem_base, a_desc, b_desc, idesc, s_ > 0 ? 1u : 0u);
+        if (p.bf16) mma_bf16(tmem_base, a_desc, b_desc, idesc, s_ > 0 ? 1u : 0u);
+        else mma_tf32(tmem_base, a_desc, b_desc, idesc, s_ > 0 ? 1u : 0u);
       }
       asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(mbar_addr) : "memory");
     }
@@ -375,14 +452,18 @@ int kmeans_assign_tc(const float* x, const float* y, int64_t* labels, int64_t n,
   p.x = x; p.y = y; p.labels = labels; p.n = n; p.k = (int)k; p.d = (int)d; p.metric = metric;
   p.dp = (int)((d + 7) / 8 * 8);
   p.terms = p.dp <= 32 ? 3 : 1;
+  p.bf16 = p.dp > 32 ? 1 : 0;  // 3 x tf32 does not fit in shared memory beyond d = 32; 3 x bf16 does up to d = 64
+  if (p.bf16) p.dp = (int)((d + 15) / 16 * 16);  // one bf16 MMA consumes 16 values of K
   p.n_pad = (int)((k + 31) / 32 * 32);
   p.vec4 = d % 4 == 0 && aligned(x, 16);
-  p.eps = p.terms == 3 ? 1.0f / 65536.0f : 1.0f / 256.0f;  // 2^-16 (split product, true error ~2^-18.4) or 2^-8 (plain TF32)
+  // relative error bound of one score: 2^-16 for the tf32 split (true error ~2^-18.4); 2^-14 for the bf16 split
+  // (neglected terms x2.y2 + x.y3 + x3.y <= 3 * 2^-18 |x||y| = 2^-16.4)
+  p.eps = p.bf16 ? 1.0f / 16384.0f : 1.0f / 65536.0f;
   int32_t* head = reinterpret_cast<int32_t*>(workspace);
   p.amb_count = head; p.error = head + 1; p.amb_list = head + 64;
   cudaError_t e = cudaMemsetAsync(head, 0, 256, st);
   if (e != cudaSuccess) return set_error(F2C_ERR_CUDA, "kmeans_assign: %s", cudaGetErrorString(e));
-  const int kc = (p.terms * p.dp + 8) / 4;
+  const int kc = (p.bf16 ? 3 * p.dp / 8 : p.terms * p.dp / 4) + 2;
   size_t smem = (size_t)kc * (tc::kMaxN + 2 * tc::kTileM) * 16 + tc::kMaxN * 4 + 2 * tc::kTileM * 16 + 64;
   if (smem < 120 * 1024) smem = 120 * 1024;  // one CTA per SM: a second one would only wait for the TMEM columns
   e = cudaFuncSetAttribute(tc::kmeans_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
