@@ -55,6 +55,15 @@ template <> struct VecLoad<8> {
 };
 
 enum { DEC_ARITH = 0, DEC_LUT = 1 };
+// Table kernels for 4- and 8-bit codes run as ONE 512-thread CTA per SM whose table starts on a 64 KB boundary of the
+// shared window: the base address then lives in the upper half of the byte permute's second source and a lookup
+// address costs one instruction.  Measured on B200 (config-2 block): 4 bit 47.1 -> 45.1 us, 8 bit 55.3 -> 51.9 us; the
+// 1- and 2-bit kernels (fewer lookups per byte of code, larger staging area) are faster as two 256-thread CTAs.
+template <int BITS, int DEC> struct SqCta {
+  static constexpr bool kAligned = DEC == DEC_LUT && BITS >= 4;
+  static constexpr int kThreads = kAligned ? 512 : 256;
+  static constexpr int kCtasPerSm = kAligned ? 1 : 2;
+};
 enum { CODE_U8 = 0, CODE_I8 = 1, CODE_I16 = 2 };
 
 struct PeerInfo {
@@ -145,11 +154,13 @@ __device__ __forceinline__ float lds_f32(uint32_t a) {
 }
 
 // Add the decoded elements of one lane's share of a neighbour row to its accumulators.
-// `table` = shared-window address of the decode table; lane_off = this lane's copy offset in a slab.
+// `table` = shared-window address of the decode table, lane_off = this lane's copy offset in a slab; aligned-table
+// kernels pass table = 0 and the (64 KB aligned) address inside lane_off.
 template <int BITS, int VEC, int DEC, typename AccT>
 __device__ __forceinline__ void sq_accumulate(AccT& acc, const VecLoad<VEC>& data, uint32_t table, uint32_t lane_off, int code_kind,
                                               float scale, float emin, float mean) {
   constexpr int NW = VEC / 4;
+  constexpr bool ALIGNED = SqCta<BITS, DEC>::kAligned;
 #pragma unroll
   for (int w = 0; w < NW; ++w) {
     const uint32_t word = data.w[w];
@@ -158,7 +169,7 @@ __device__ __forceinline__ void sq_accumulate(AccT& acc, const VecLoad<VEC>& dat
 #pragma unroll
       for (int b = 0; b < 4; ++b) {
         // result bytes [lane_off.b0, word.b_b, lane_off.b2, lane_off.b3]  ==  (byte << 8) | lane_off
-        const uint32_t e = table + __byte_perm(word, lane_off, 0x7604u | (uint32_t)(b << 4));
+        const uint32_t e = (ALIGNED ? 0u : table) + __byte_perm(word, lane_off, 0x7604u | (uint32_t)(b << 4));
         const int k = w * 4 + b;  // byte number inside the lane's slice
         if (L::FLOATS == 1) {
           acc.add_one(k, lds_f32(e));
@@ -198,10 +209,15 @@ __device__ __forceinline__ void sq_accumulate(AccT& acc, const VecLoad<VEC>& dat
 // PEER: the table is row-sharded over the GPUs of one NVSwitch box and every shard is mapped into this process;
 // a neighbour's row is read from its owner's HBM with an ordinary load over NVLink (no collective, no staging copy).
 template <int BITS, int VEC, int U, typename IdxT, int DEC, bool PEER = false>
-__global__ void __launch_bounds__(256, 2) sq_spmm_kernel(const SqParams p) {
+__global__ void __launch_bounds__(SqCta<BITS, DEC>::kThreads, SqCta<BITS, DEC>::kCtasPerSm) sq_spmm_kernel(const SqParams p) {
+  constexpr bool ALIGNED = SqCta<BITS, DEC>::kAligned;
   constexpr int EPL = BITS == 16 ? VEC / 2 : VEC * 8 / BITS;  // output columns per lane
   constexpr bool PACKED = DEC == DEC_LUT && BITS <= 4;
-  extern __shared__ __align__(16) unsigned char smem_raw[];
+  extern __shared__ __align__(16) unsigned char smem_dyn[];
+  // Aligned-table kernels: everything starts at the next 64 KB boundary of the shared window (the launch reserves the
+  // slack), so the table's base address is a pure "upper half" value and rides in the permute that forms a lookup address.
+  unsigned char* const smem_raw =
+      ALIGNED ? smem_dyn + ((0x10000u - ((uint32_t)__cvta_generic_to_shared(smem_dyn) & 0xFFFFu)) & 0xFFFFu) : smem_dyn;
 
   const int lane = threadIdx.x & 31;
   const int G = 1 << p.logG;
@@ -258,8 +274,9 @@ __global__ void __launch_bounds__(256, 2) sq_spmm_kernel(const SqParams p) {
     for (int i = threadIdx.x; i < 64; i += blockDim.x) reinterpret_cast<float*>(smem_raw + L::TABLE_BYTES)[i] = 0.0f;
     __syncthreads();
     lane_off = L::lane_offset(lane);
+    if (ALIGNED) lane_off |= (uint32_t)__cvta_generic_to_shared(smem_raw);  // low 16 bits of the base are zero
   }
-  const uint32_t table = (uint32_t)__cvta_generic_to_shared(smem_raw);
+  const uint32_t table = ALIGNED ? 0u : (uint32_t)__cvta_generic_to_shared(smem_raw);  // aligned: the base is part of lane_off
 
   // Sums of decoded values are 0 or, in magnitude, between 2^(emin-24) and deg * 2^emax (1 bit: multiples of
   // ~mean); when that interval is well inside the normal range for every lane of the warp, the mean can use
@@ -494,15 +511,18 @@ static int launch_fast(SqParams p, bool vec_store, cudaStream_t st) {
     int n_rows = (1 << p.logG) < L::COPIES ? (1 << p.logG) : L::COPIES;
     smem = L::TABLE_BYTES + 256 + (size_t)n_rows * L::NCODE * sizeof(float);
   }
-  // staging area for coalesced output: 8 warps x 32 lanes x EPL floats
+  constexpr int kThreads = SqCta<BITS, DEC>::kThreads;
+  constexpr int kWarpsPerCta = kThreads / 32;
+  // staging area for coalesced output: warps x 32 lanes x EPL floats
   p.staged = 0;
   p.stage_offset = (int)smem;
   if (vec_store && EPL >= 4) {
     p.staged = 1;
-    smem += (size_t)8 * 32 * EPL * sizeof(float);
+    smem += (size_t)kWarpsPerCta * 32 * EPL * sizeof(float);
   }
+  if (SqCta<BITS, DEC>::kAligned) smem += 65536;  // slack for the 64 KB alignment of the table inside the shared window
   if (smem > 48 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 65536 + 256 + 32 * 256 * 4 + 32768);
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return set_error(F2C_ERR_CUDA, "sq_decompress_spmm_csr: %s", cudaGetErrorString(e));
   }
   // persistent grid: exactly as many CTAs as the device keeps resident (queried when the footprint changes)
@@ -510,15 +530,15 @@ static int launch_fast(SqParams p, bool vec_store, cudaStream_t st) {
   static size_t resident_smem = ~(size_t)0;
   if (resident == 0 || resident_smem != smem) {
     int n = 0;
-    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kern, 256, smem) != cudaSuccess || n < 1) n = 1;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kern, kThreads, smem) != cudaSuccess || n < 1) n = 1;
     resident = n;
     resident_smem = smem;
   }
   int ctas_per_sm = g_tune_ctas_per_sm > 0 ? g_tune_ctas_per_sm : resident;
-  int rows_per_cta = 8 * (32 >> p.logG);
+  int rows_per_cta = kWarpsPerCta * (32 >> p.logG);
   int64_t grid = ceil_div(p.n_dst, rows_per_cta);
   if (grid > (int64_t)kSmCount * ctas_per_sm) grid = (int64_t)kSmCount * ctas_per_sm;
-  kern<<<(unsigned)grid, 256, smem, st>>>(p);
+  kern<<<(unsigned)grid, kThreads, smem, st>>>(p);
   return check_launch("sq_decompress_spmm_csr");
 }
 

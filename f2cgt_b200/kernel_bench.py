@@ -65,6 +65,12 @@ class Bench:
             self._blocks[key] = (blk["indptr"].contiguous(), blk["indices_global"].contiguous())
         return self._blocks[key]
 
+    def wanted(self, *names):
+        """False when --only excludes every one of these case names (their inputs need not be built)."""
+        if not self.args.only:
+            return True
+        return any(f in n for f in self.args.only.split(",") for n in names)
+
     # ---- timing
     def run(self, name, fn, nbytes=None, flops=None, units=None, unit_name="edges", note=""):
         if self.args.only and not any(s in name for s in self.args.only.split(",")):
@@ -118,6 +124,8 @@ def cases(b):
     ip, ix = b.block()
     E, n_dst = ix.numel(), ip.numel() - 1
     for bits in (1, 2, 4, 8):
+        if not b.wanted(f"sq_spmm_{bits}bit", f"sq_decompress_{bits}bit"):
+            continue
         codes, cb = synth.sq_table_from_normal(N, FEAT, bits, FEAT, seed=0, device=dev)
         rb = codes.shape[1]
         b.run(f"sq_spmm_{bits}bit", lambda c=codes, k=cb, w=bits: ops.sq_decompress_spmm_csr(c, k, ip, ix, w, FEAT, FEAT),
@@ -142,6 +150,8 @@ def cases(b):
 
     # ------------------------------------------------ fused VQ (configurations 3 and 4) and the two-level kernel
     for n_cb, cs, tag in ((16, 8, "config3_16x8"), (4, 32, "config4_4x32")):
+        if not b.wanted(f"vq_spmm_{tag}", "vq_decompress_4x32", "two_level_spmm_sq8_vq4x32"):
+            continue
         vq = torch.randint(0, 256, (N, n_cb), generator=g, dtype=torch.uint8, device=dev)
         cbs = torch.randn(n_cb, 256, cs, generator=g, device=dev)
         b.run(f"vq_spmm_{tag}", lambda c=vq, k=cbs: ops.vq_decompress_spmm_csr(c, k, ip, ix, FEAT),
@@ -171,6 +181,9 @@ def cases(b):
         del vq
 
     # ------------------------------------------------ plain aggregation, dropout, packing, compress
+    if not b.wanted("spmm_csr_f32", "dropout_inplace", "sq_compress_4bit", "packbits_4bit", "unpackbits_4bit") and \
+            not b.wanted(*[f"kmeans_assign_d{d}_{m}" for d in (8, 32, 64) for m in ("l2", "cosine")]):
+        return
     rows = n_dst
     feat = torch.randn(min(N, 1_000_000), FEAT, generator=g, device=dev)
     ixs = ix % feat.shape[0]
