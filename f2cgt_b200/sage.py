@@ -51,6 +51,49 @@ class CompressionManager:
         ident = torch.arange(nodes.numel() + 1, dtype=nodes.dtype, device=nodes.device)
         return self.aggregate(ident, nodes)
 
+    def for_block(self, block):
+        """(manager, neighbour ids, destination ids) with which the first layer reads this block: the resident tables
+        are addressed by global id."""
+        return self, block["indices_global"], block["dst_nodes"]
+
+
+class ShardedCompressionManager:
+    """The same compressed feature matrix with every table ROW-SHARDED over the ranks of the process group (rank r owns
+    rows [r * ceil(n / world), ...) of the VQ table, of the slot array and - keyed by slot - of the hot SQ table).
+
+    Per minibatch the rows of the block's source nodes are fetched from their owners with the all-to-all exchange of
+    ``f2cgt_b200.shard.ShardedTable`` (ids out, rows back: NCCL over NVLink), which gives a block-local
+    ``CompressionManager`` over gathered rows; the fused kernel then runs on block-local ids.  ``for_block`` is a
+    collective: every rank calls it once per step."""
+
+    def __init__(self, feat_dim, methods, configs, codebooks, local_tables, table_rows, local_slot=None, group=None):
+        from . import shard
+        self.feat_dim, self.methods, self.configs, self.codebooks = int(feat_dim), list(methods), list(configs), list(codebooks)
+        self.is_two_level = len(self.methods) >= 2
+        self.level2 = shard.ShardedTable(local_tables[-1], table_rows[-1], group)
+        if self.is_two_level:
+            if self.methods != ["sq", "vq"] or local_slot is None:
+                raise ValueError("two-level compression is hot SQ rows over a VQ table, with a slot array")
+            self.hot = shard.ShardedTable(local_tables[0], table_rows[0], group)
+            self.slot = shard.ShardedTable(local_slot.reshape(-1, 1), table_rows[-1], group)
+
+    def for_block(self, block):
+        src = block["src_nodes"]
+        n_dst = block["dst_nodes"].numel()
+        plan = self.level2.plan(src)
+        rows = self.level2.fetch_rows(plan)
+        dst_local = torch.arange(n_dst, dtype=src.dtype, device=src.device)
+        if not self.is_two_level:
+            local = CompressionManager(self.feat_dim, self.methods, self.configs, self.codebooks, [rows])
+            return local, block["indices_local"], dst_local
+        slots = self.slot.fetch_rows(plan).reshape(-1)  # same ids, same row partition: the plan is shared
+        hot_pos = (slots >= 0).nonzero().reshape(-1)
+        hot_rows = self.hot.fetch(slots[hot_pos].to(src.dtype))
+        local_slot = torch.full_like(slots, -1)
+        local_slot[hot_pos] = torch.arange(hot_pos.numel(), dtype=slots.dtype, device=slots.device)
+        local = CompressionManager(self.feat_dim, self.methods, self.configs, self.codebooks, [hot_rows, rows], local_slot)
+        return local, block["indices_local"], dst_local
+
 
 def _bucket(n):
     """Row counts of sampled blocks change every step; the matrix products behind the Linear layers pick (and cache)
@@ -104,8 +147,9 @@ class MySAGEConv(nn.Module):
         nn.init.xavier_uniform_(self.fc_neigh.weight, gain=gain)
 
     def forward(self, block, _unused=None):
-        h_neigh = self.sm.aggregate(block["indptr"], block["indices_global"])  # raw codes in, no autograd through it
-        h_self = self.sm.decode_rows(block["dst_nodes"])
+        sm, neighbours, dst = self.sm.for_block(block)
+        h_neigh = sm.aggregate(block["indptr"], neighbours)  # raw codes in, no autograd through it
+        h_self = sm.decode_rows(dst)
         return _linear_rows(self.fc_self, h_self) + _linear_rows(self.fc_neigh, h_neigh)
 
 

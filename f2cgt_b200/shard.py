@@ -79,13 +79,21 @@ class ShardedTable:
     def plan(self, ids):
         """Everything about a fetch that depends only on the ids (can be computed when the block is sampled):
         bucketing, the count exchange and the id exchange.  Returns a dict consumed by ``fetch_rows``."""
-        if ids.numel() and (int(ids.min()) < 0 or int(ids.max()) >= self.n_rows):
-            raise IndexError("row id outside the table")
+        if ids.numel():
+            lo_hi = torch.stack(torch.aminmax(ids)).tolist()  # one host read for both bounds
+            if lo_hi[0] < 0 or lo_hi[1] >= self.n_rows:
+                raise IndexError("row id outside the table")
         order, sorted_ids, counts = bucket_by_owner(ids, self.rpr, self.world)
-        send_counts = counts.to("cpu").tolist()
-        all_counts = [None] * self.world
-        dist.all_gather_object(all_counts, send_counts, group=self.group)
-        recv_counts = [all_counts[r][self.rank] for r in range(self.world)]
+        if ids.is_cuda:  # one small all-to-all of the counts on the device, one host read for both directions
+            got = torch.empty_like(counts)
+            dist.all_to_all_single(got, counts.contiguous(), group=self.group)
+            both = torch.stack([counts, got]).to("cpu").tolist()
+            send_counts, recv_counts = both[0], both[1]
+        else:
+            send_counts = counts.to("cpu").tolist()
+            all_counts = [None] * self.world
+            dist.all_gather_object(all_counts, send_counts, group=self.group)
+            recv_counts = [all_counts[r][self.rank] for r in range(self.world)]
         wanted = _exchange(sorted_ids, send_counts, recv_counts, self.group)  # ids other ranks want from this shard
         return dict(order=order, send_counts=send_counts, recv_counts=recv_counts, local_index=wanted - self.lo)
 

@@ -39,7 +39,7 @@ PRESETS = {
 }
 
 
-def build_data(cfg, device, index_dtype):
+def build_data(cfg, device, index_dtype, table="replicated"):
     n = cfg["nodes"]
     indptr, indices = synth.power_law_graph(n, cfg["degree"], 2.1, seed=0, device=device, index_dtype=index_dtype)
     g = torch.Generator(device=device)
@@ -60,7 +60,18 @@ def build_data(cfg, device, index_dtype):
     sq_codes = torch.randint(-128, 128, (n_hot, row_bytes), generator=g, dtype=torch.int8, device=device)
     labels = torch.randint(0, cfg["classes"], (n,), generator=g, device=device)
     train_ids = torch.randperm(n, generator=g, device=device)[:cfg["train"]].to(index_dtype)
-    cm = sage.CompressionManager(cfg["feat"], ["sq", "vq"], [(cfg["feat"], bits), (cs, 8)], [sq_cb, vq_cbs], [sq_codes, vq_codes], slot)
+    methods, configs, cbs = ["sq", "vq"], [(cfg["feat"], bits), (cs, 8)], [sq_cb, vq_cbs]
+    if table == "sharded":  # every rank keeps only its row shard of the three tables
+        from f2cgt_b200 import shard
+        rank, world = dist.get_rank(), dist.get_world_size()
+        lo, hi = shard.shard_bounds(n, world, rank)
+        hlo, hhi = shard.shard_bounds(n_hot, world, rank)
+        cm = sage.ShardedCompressionManager(cfg["feat"], methods, configs, cbs, [sq_codes[hlo:hhi].clone(), vq_codes[lo:hi].clone()],
+                                            [n_hot, n], slot[lo:hi].clone())
+        del sq_codes, vq_codes, slot
+        torch.cuda.empty_cache()
+    else:
+        cm = sage.CompressionManager(cfg["feat"], methods, configs, cbs, [sq_codes, vq_codes], slot)
     return indptr, indices, labels, train_ids, cm
 
 
@@ -74,6 +85,8 @@ def main():
     ap.add_argument("--index-dtype", default="int64", choices=["int32", "int64"])
     ap.add_argument("--max-steps", type=int, default=0, help="cut every epoch after this many steps (0 = whole epoch)")
     ap.add_argument("--no-autocast", action="store_true")
+    ap.add_argument("--table", default="replicated", choices=["replicated", "sharded"],
+                    help="sharded: every table row-sharded over the ranks, rows fetched per minibatch with an all-to-all exchange")
     args = ap.parse_args()
     cfg = PRESETS[args.preset]
 
@@ -82,10 +95,13 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", 0))
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=device)
+    if world > 1 or args.table == "sharded":
+        if world == 1:
+            os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+            os.environ.setdefault("MASTER_PORT", "29577")
+        dist.init_process_group("nccl", device_id=device, rank=rank, world_size=world)
     idt = torch.int32 if args.index_dtype == "int32" else torch.int64
-    indptr, indices, labels, train_ids, cm = build_data(cfg, device, idt)
+    indptr, indices, labels, train_ids, cm = build_data(cfg, device, idt, args.table)
 
     torch.manual_seed(0)
     model = sage.SAGE(cfg["feat"], cfg["hidden"], cfg["classes"], len(cfg["fan_out"]), args.dropout, cm).to(device)
@@ -138,9 +154,9 @@ def main():
             "epoch_seconds_all": [round(t, 4) for t in epoch_s], "ms_per_step": float(tmax[0]) / steps * 1e3,
             "first_layer_edges_per_s": float(etot[0]) / float(tmax[0]), "loss_last_step_per_epoch": [round(v, 4) for v in losses],
             "config": {k: (list(v) if isinstance(v, tuple) else v) for k, v in cfg.items()}, "index_dtype": args.index_dtype,
-            "autocast_bf16": not args.no_autocast, "data": "synthetic", "scaling": "strong (train ids split over ranks)",
+            "autocast_bf16": not args.no_autocast, "table": args.table, "data": "synthetic", "scaling": "strong (train ids split over ranks)",
             "timing": "wall clock around barrier + synchronize delimited epochs, first epoch discarded, max over ranks"}), flush=True)
-    if world > 1:
+    if dist.is_initialized():
         dist.destroy_process_group()
 
 

@@ -72,16 +72,75 @@ def _worker(rank, world, port, q):
         dist.destroy_process_group()
 
 
-def test_sharded_table_two_gpus():
-    if torch.cuda.device_count() < 2:
-        pytest.skip("needs two GPUs")
+def _run(target, world):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
+    procs = [ctx.Process(target=target, args=(r, world, port, q)) for r in range(world)]
     for p in procs:
         p.start()
     results = dict(q.get(timeout=300) for _ in procs)
     for p in procs:
         p.join(timeout=60)
-    assert results == {0: "ok", 1: "ok"}, results
+    assert results == {r: "ok" for r in range(world)}, results
+
+
+def test_sharded_table_two_gpus():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    _run(_worker, 2)
+
+
+def _manager_worker(rank, world, port, q):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    torch.cuda.set_device(rank)
+    device = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=device)
+    try:
+        from f2cgt_b200 import sage, shard, synth
+        n, D, n_hot = 30011, 128, 1777
+        g = torch.Generator(device=device).manual_seed(7)  # the same tables on every rank
+        indptr, indices = synth.power_law_graph(n, 15, 2.1, seed=1, device=device)
+        vq_codes = torch.randint(0, 256, (n, 4), generator=g, dtype=torch.uint8, device=device)
+        vq_cbs = torch.randn(4, 256, 32, generator=g, device=device)
+        hot = torch.randperm(n, generator=g, device=device)[:n_hot]
+        slot = torch.full((n,), -1, dtype=torch.int32, device=device)
+        slot[hot] = torch.arange(n_hot, dtype=torch.int32, device=device)
+        sq_codes = torch.randint(-128, 128, (n_hot, D), generator=g, dtype=torch.int8, device=device)
+        sq_cb = synth.sq_codebook_from_sample(torch.randn(5000, D, generator=g, device=device), D)
+        methods, configs, cbs = ["sq", "vq"], [(D, 8), (32, 8)], [sq_cb, vq_cbs]
+        whole = sage.CompressionManager(D, methods, configs, cbs, [sq_codes, vq_codes], slot)
+        lo, hi = shard.shard_bounds(n, world, rank)
+        hlo, hhi = shard.shard_bounds(n_hot, world, rank)
+        parts = sage.ShardedCompressionManager(D, methods, configs, cbs, [sq_codes[hlo:hhi].clone(), vq_codes[lo:hi].clone()],
+                                               [n_hot, n], slot[lo:hi].clone())
+        g2 = torch.Generator(device=device).manual_seed(100 + rank)  # a different minibatch per rank
+        seeds = torch.randperm(n, generator=g2, device=device)[:200]
+        loader = sage.GPUSamplingDataloader(indptr, indices, seeds, 200, (5, 4), shuffle=False, rng_seed=rank)
+        for _ in range(2):
+            _, _, blocks = next(iter(loader))
+            b = blocks[0]
+            sm, neigh, dst = parts.for_block(b)
+            assert torch.equal(sm.aggregate(b["indptr"], neigh), whole.aggregate(b["indptr"], b["indices_global"]))
+            assert torch.equal(sm.decode_rows(dst), whole.decode_rows(b["dst_nodes"]))
+        # single-level table through the same path
+        one = sage.ShardedCompressionManager(D, ["vq"], [(32, 8)], [vq_cbs], [vq_codes[lo:hi].clone()], [n])
+        sm, neigh, dst = one.for_block(b)
+        ref = sage.CompressionManager(D, ["vq"], [(32, 8)], [vq_cbs], [vq_codes])
+        assert torch.equal(sm.aggregate(b["indptr"], neigh), ref.aggregate(b["indptr"], b["indices_global"]))
+        q.put((rank, "ok"))
+    except Exception as e:  # noqa: BLE001
+        import traceback
+        q.put((rank, repr(e) + traceback.format_exc()[-600:]))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [1, 2])
+def test_sharded_compression_manager_equals_resident_tables(world):
+    """Row-sharded tables + all-to-all row fetch feed the fused two-level kernel the same rows as the resident tables."""
+    if torch.cuda.device_count() < world:
+        pytest.skip("needs more GPUs")
+    _run(_manager_worker, world)

@@ -72,3 +72,54 @@ def test_bucketing_is_stable_and_complete():
     assert torch.equal(ids[order], sorted_ids)
     assert shard.shard_bounds(1001, 2, 0) == (0, 501) and shard.shard_bounds(1001, 2, 1) == (501, 1001)
     assert shard.shard_bounds(10, 4, 3) == (9, 10)
+
+
+def _manager_worker(rank, world, port, q):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from f2cgt_b200 import sage
+        n, n_hot = 5003, 611
+        g = torch.Generator().manual_seed(3)  # the same tables on every rank
+        vq = torch.randint(0, 256, (n, 4), generator=g, dtype=torch.uint8)
+        hot_rows = torch.randint(-128, 128, (n_hot, 128), generator=g, dtype=torch.int8)
+        slot = torch.full((n,), -1, dtype=torch.int32)
+        slot[torch.randperm(n, generator=g)[:n_hot]] = torch.arange(n_hot, dtype=torch.int32)
+        lo, hi = shard.shard_bounds(n, world, rank)
+        hlo, hhi = shard.shard_bounds(n_hot, world, rank)
+        cb = [torch.zeros(1, 5), torch.zeros(4, 256, 32)]
+        parts = sage.ShardedCompressionManager(128, ["sq", "vq"], [(128, 8), (32, 8)], cb, [hot_rows[hlo:hhi].clone(), vq[lo:hi].clone()],
+                                               [n_hot, n], slot[lo:hi].clone())
+        g2 = torch.Generator().manual_seed(50 + rank)  # a different block per rank
+        for n_src in (700, 1):
+            src = torch.randperm(n, generator=g2)[:n_src]
+            block = dict(src_nodes=src, dst_nodes=src[:min(50, n_src)], indices_local=torch.zeros(3, dtype=torch.int64))
+            local, neigh, dst = parts.for_block(block)
+            assert neigh is block["indices_local"] and torch.equal(dst, torch.arange(block["dst_nodes"].numel()))
+            assert torch.equal(local.tables[1], vq[src])
+            want_hot = slot[src] >= 0
+            assert torch.equal(local.slot >= 0, want_hot)
+            assert torch.equal(local.tables[0][local.slot[want_hot].long()], hot_rows[slot[src][want_hot].long()])
+            assert local.tables[0].shape[0] == int(want_hot.sum())
+        q.put((rank, "ok"))
+    except Exception as e:  # noqa: BLE001
+        import traceback
+        q.put((rank, repr(e) + traceback.format_exc()[-500:]))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_sharded_compression_manager_assembles_block_tables():
+    """Two ranks: the block-local tables handed to the fused two-level kernel hold exactly the rows of the block's source
+    nodes (VQ codes, slots re-numbered to the fetched hot rows)."""
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_manager_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    results = dict(q.get(timeout=120) for _ in procs)
+    for p in procs:
+        p.join(timeout=30)
+    assert results == {0: "ok", 1: "ok"}, results
