@@ -68,16 +68,21 @@ __global__ void __launch_bounds__(kVqStreamThreads, 1) vq_decompress_stream_kern
     const uint8_t* __restrict__ codes, const float* __restrict__ cbs, float* __restrict__ out, int64_t rows, int vec_per_row,
     int n_cb, int K, int cs, int feat_dim, int spq, int stride) {
   extern __shared__ __align__(128) unsigned char vq_smem[];
-  {
+  {  // consecutive threads write consecutive 16-byte pieces of shared memory (no bank conflicts while staging)
     const int lg4 = 31 - __clz(cs >> 2);
-    const int per_sub = K << lg4;
     const float4* src = reinterpret_cast<const float4*>(cbs);
-    for (int sl = 0; sl < n_cb; ++sl) {
-      const int sub_base = spq > 1 ? (sl / spq) * K * 128 + (sl % spq) * cs * 4 : sl * K * stride;
-      for (int i = threadIdx.x; i < per_sub; i += kVqStreamThreads) {
-        const int q = i & ((1 << lg4) - 1), code = i >> lg4;
-        *reinterpret_cast<float4*>(vq_smem + sub_base + code * stride + q * 16) = __ldg(src + sl * per_sub + i);
+    float4* dst = reinterpret_cast<float4*>(vq_smem);
+    if (spq > 1) {  // 128-byte line = the centroids `code` of spq consecutive subspaces
+      const int n16 = ((n_cb + spq - 1) / spq) * K * 8;
+      for (int i = threadIdx.x; i < n16; i += kVqStreamThreads) {
+        const int piece = i & 7, line = i >> 3;
+        const int code = line % K, grp = line / K;
+        const int sl = grp * spq + (piece >> lg4), q = piece & ((1 << lg4) - 1);
+        dst[i] = sl < n_cb ? __ldg(src + ((sl * K + code) << lg4) + q) : make_float4(0.f, 0.f, 0.f, 0.f);
       }
+    } else {
+      const int n16 = (n_cb * K) << lg4;
+      for (int i = threadIdx.x; i < n16; i += kVqStreamThreads) dst[i] = __ldg(src + i);
     }
   }
   __syncthreads();
