@@ -544,7 +544,10 @@ static int launch_fast(SqParams p, bool vec_store, cudaStream_t st) {
 
 template <int BITS, int VEC, typename IdxT, int DEC>
 static int pick_u(const SqParams& p, bool vec_store, cudaStream_t st) {
-  int u = g_tune_u > 0 ? g_tune_u : 12;
+  // neighbours held in registers per destination row; measured on B200 (config-2 block, fan-out 12): 8 is fastest
+  // for 2- and 4-bit codes (4 bit: 42-43 us against 46 with 12 - the four remaining neighbours take the unpipelined
+  // round, but 16 fewer live registers help more; 2 bit: a tie; 4 per row is slower again), 12 for 1- and 8-bit codes
+  int u = g_tune_u > 0 ? g_tune_u : (BITS == 2 || BITS == 4 ? 8 : 12);
   if (u >= 16) return launch_fast<BITS, VEC, 16, IdxT, DEC>(p, vec_store, st);
   if (u >= 12) return launch_fast<BITS, VEC, 12, IdxT, DEC>(p, vec_store, st);
   return launch_fast<BITS, VEC, 8, IdxT, DEC>(p, vec_store, st);
