@@ -7,7 +7,7 @@ import ctypes as C
 import os
 
 _PKG = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_PKG, "libf2cgt_b200.so")
+LIB_PATH = os.environ.get("F2CGT_B200_LIB") or os.path.join(_PKG, "libf2cgt_b200.so")  # override: another build of the same ABI
 
 # dtype tags of include/f2cgt_b200.h
 U8, I8, I16, I32, I64, F16, F32, F64 = range(8)

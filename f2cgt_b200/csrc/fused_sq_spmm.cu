@@ -59,11 +59,21 @@ enum { DEC_ARITH = 0, DEC_LUT = 1 };
 // shared window: the base address then lives in the upper half of the byte permute's second source and a lookup
 // address costs one instruction.  Measured on B200 (config-2 block): 4 bit 47.1 -> 45.1 us, 8 bit 55.3 -> 51.9 us; the
 // 1- and 2-bit kernels (fewer lookups per byte of code, larger staging area) are faster as two 256-thread CTAs.
-template <int BITS, int DEC> struct SqCta {
-  static constexpr bool kAligned = DEC == DEC_LUT && BITS >= 4;
-  static constexpr int kThreads = kAligned ? 512 : 256;
-  static constexpr int kCtasPerSm = kAligned ? 1 : 2;
+// ASYNC kernels keep no neighbour rows in registers: every lane copies its bytes of the next destination row's neighbour
+// rows into a per-warp shared-memory ring with cp.async and reads them back when the row is decoded, which frees the
+// 32-48 prefetch registers per thread and lets 24 warps run per SM (one 768-thread CTA).
+template <int BITS, int DEC, bool ASYNC = false> struct SqCta {
+  static constexpr bool kAligned = !ASYNC && DEC == DEC_LUT && BITS >= 4;
+  static constexpr int kThreads = ASYNC ? 768 : kAligned ? 512 : 256;
+  static constexpr int kCtasPerSm = (ASYNC || kAligned) ? 1 : 2;
 };
+
+__device__ __forceinline__ void cp_async_bytes4(uint32_t dst, const void* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_bytes8(uint32_t dst, const void* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(dst), "l"(src) : "memory");
+}
 enum { CODE_U8 = 0, CODE_I8 = 1, CODE_I16 = 2 };
 
 struct PeerInfo {
@@ -92,6 +102,7 @@ struct SqParams {
   unsigned long long shard_magic;  // floor(2^64 / rows_per_shard) + 1: exact 32-bit division by one multiply-high
   int staged;        // 1: rows leave through the shared-memory staging area (feat_dim % 4 == 0)
   int stage_offset;  // byte offset of that area in dynamic shared memory
+  int ring_offset;   // ASYNC kernels: byte offset of the per-warp rings of neighbour-row bytes
   DropoutArgs drop;
 };
 
@@ -156,11 +167,10 @@ __device__ __forceinline__ float lds_f32(uint32_t a) {
 // Add the decoded elements of one lane's share of a neighbour row to its accumulators.
 // `table` = shared-window address of the decode table, lane_off = this lane's copy offset in a slab; aligned-table
 // kernels pass table = 0 and the (64 KB aligned) address inside lane_off.
-template <int BITS, int VEC, int DEC, typename AccT>
+template <int BITS, int VEC, int DEC, bool ALIGNED, typename AccT>
 __device__ __forceinline__ void sq_accumulate(AccT& acc, const VecLoad<VEC>& data, uint32_t table, uint32_t lane_off, int code_kind,
                                               float scale, float emin, float mean) {
   constexpr int NW = VEC / 4;
-  constexpr bool ALIGNED = SqCta<BITS, DEC>::kAligned;
 #pragma unroll
   for (int w = 0; w < NW; ++w) {
     const uint32_t word = data.w[w];
@@ -208,9 +218,10 @@ __device__ __forceinline__ void sq_accumulate(AccT& acc, const VecLoad<VEC>& dat
 // U = neighbours held in registers per destination row (rows with more take extra, unpipelined rounds).
 // PEER: the table is row-sharded over the GPUs of one NVSwitch box and every shard is mapped into this process;
 // a neighbour's row is read from its owner's HBM with an ordinary load over NVLink (no collective, no staging copy).
-template <int BITS, int VEC, int U, typename IdxT, int DEC, bool PEER = false>
-__global__ void __launch_bounds__(SqCta<BITS, DEC>::kThreads, SqCta<BITS, DEC>::kCtasPerSm) sq_spmm_kernel(const SqParams p) {
-  constexpr bool ALIGNED = SqCta<BITS, DEC>::kAligned;
+template <int BITS, int VEC, int U, typename IdxT, int DEC, bool PEER = false, bool ASYNC = false>
+__global__ void __launch_bounds__(SqCta<BITS, DEC, ASYNC>::kThreads, SqCta<BITS, DEC, ASYNC>::kCtasPerSm)
+sq_spmm_kernel(const SqParams p) {
+  constexpr bool ALIGNED = SqCta<BITS, DEC, ASYNC>::kAligned;
   constexpr int EPL = BITS == 16 ? VEC / 2 : VEC * 8 / BITS;  // output columns per lane
   constexpr bool PACKED = DEC == DEC_LUT && BITS <= 4;
   extern __shared__ __align__(16) unsigned char smem_dyn[];
@@ -236,6 +247,80 @@ __global__ void __launch_bounds__(SqCta<BITS, DEC>::kThreads, SqCta<BITS, DEC>::
   const float mean = __ldg(p.codebooks + cb_row * kCodebookDim + 4);
   const float scale = sq_scale<BITS>(emin, emax);
 
+  // ---- Pipeline state and priming.  The chain indptr -> neighbour ids -> code rows of the first rows is three dependent
+  //      global-load latencies; for 2- and 8-bit codes it is issued BEFORE the decode table is built, so that it overlaps
+  //      the construction (measured on B200, same box: 8 bit 51.9 -> 49.5 us, 2 bit 43.0 -> 42.0 us; 1 bit 38.9 -> 43.0
+  //      and 4 bit 42.6 -> 43.4 the other way, so those prime after the build).
+  constexpr bool PRIME_EARLY = BITS == 2 || BITS == 8;
+  const IdxT* __restrict__ indptr = reinterpret_cast<const IdxT*>(p.indptr);
+  const IdxT* __restrict__ indices = reinterpret_cast<const IdxT*>(p.indices);
+  const int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int64_t stride = (((int64_t)gridDim.x * blockDim.x) >> 5) * rows_per_warp;
+  const uint8_t* __restrict__ my_codes = p.codes + byte0;
+  // address of this lane's slice of source row `id`
+  auto row_ptr = [&](uint32_t id) -> const uint8_t* {
+    if (!PEER) return my_codes + (uint64_t)id * p.row_bytes;
+    const uint32_t owner = (uint32_t)__umul64hi((unsigned long long)id, p.shard_magic);
+    const uint32_t local = id - owner * p.rows_per_shard;
+    return p.shard[owner] + byte0 + (uint64_t)local * p.row_bytes;
+  };
+
+  // ---- three-deep software pipeline over the rows d, d+stride, d+2*stride, ... of this lane group.
+  // Rows are counted in 32 bits (the host checks n_dst < 2^31).
+  const int n_dst = (int)p.n_dst;
+  const int istride = (int)stride;
+  int d = (int)(warp * rows_per_warp) + sub;
+  const IdxT* idsA = indices;  // first neighbour id of rows i, i+1, i+2
+  const IdxT* idsB = indices;
+  const IdxT* idsC = indices;
+  int degA = 0, degB = 0, degC = 0;
+  // One set of id registers is enough: a stage first issues the row loads that consume them, then
+  // overwrites them with the ids of the row after (the hardware scoreboard orders the two).
+  uint32_t nidx[U];
+  VecLoad<VEC> data[ASYNC ? 1 : 2][ASYNC ? 1 : U];
+  // ASYNC: shared-window address of this lane's bytes of neighbour slot 0, stage 0, in its warp's ring
+  constexpr uint32_t kSlotBytes = 32 * VEC, kStageBytes = U * kSlotBytes;
+  const uint32_t ring = ASYNC ? (uint32_t)__cvta_generic_to_shared(smem_raw + p.ring_offset) + (threadIdx.x >> 5) * (2 * kStageBytes) +
+                                    (uint32_t)lane * VEC
+                              : 0u;
+  // fetch (or zero) this lane's bytes of neighbour slot u of the row whose ids are in nidx, into `stage`
+  auto fetch_async = [&](int stage, int u, bool have) {
+    const uint32_t dst = ring + (uint32_t)stage * kStageBytes + (uint32_t)u * kSlotBytes;
+    if (have) {
+      if (VEC == 8) cp_async_bytes8(dst, row_ptr(nidx[u]));
+      else cp_async_bytes4(dst, row_ptr(nidx[u]));
+    } else if (VEC == 8) {
+      asm volatile("st.shared.b64 [%0], %1;" ::"r"(dst), "l"(0ull) : "memory");
+    } else {
+      asm volatile("st.shared.b32 [%0], %1;" ::"r"(dst), "r"(0u) : "memory");
+    }
+  };
+  auto prime = [&]() {
+    if (d < n_dst && lane_active) { int64_t b = (int64_t)indptr[d]; degA = (int)((int64_t)indptr[d + 1] - b); idsA = indices + b; }
+    if (d + istride < n_dst && lane_active) {
+      int64_t b = (int64_t)indptr[d + istride]; degB = (int)((int64_t)indptr[d + istride + 1] - b); idsB = indices + b;
+    }
+    if (d + 2 * istride < n_dst && lane_active) {
+      int64_t b = (int64_t)indptr[d + 2 * istride]; degC = (int)((int64_t)indptr[d + 2 * istride + 1] - b); idsC = indices + b;
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) nidx[u] = u < degA ? (uint32_t)idsA[u] : 0u;
+    if (ASYNC) {
+#pragma unroll
+      for (int u = 0; u < U; ++u) fetch_async(0, u, u < degA);
+      asm volatile("cp.async.commit_group;" ::: "memory");
+    } else {
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+#pragma unroll
+        for (int w = 0; w < VEC / 4; ++w) data[0][u].w[w] = 0u;
+        if (u < degA) data[0][u].load(row_ptr(nidx[u]));
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) nidx[u] = u < degB ? (uint32_t)idsB[u] : 0u;
+  };
+  if (PRIME_EARLY) prime();
   uint32_t lane_off = 0;
   if (DEC == DEC_LUT) {
     // Copy c of a slab serves the lanes with lane % COPIES == c, whose lane_g is c % G.
@@ -283,49 +368,7 @@ __global__ void __launch_bounds__(SqCta<BITS, DEC>::kThreads, SqCta<BITS, DEC>::
   // the division without the per-element range check.
   const bool div_safe = __all_sync(0xffffffffu, BITS == 1 ? (mean > 1e-20f && mean < 1e20f) : (emin > -80.0f && emax < 80.0f));
 
-  const IdxT* __restrict__ indptr = reinterpret_cast<const IdxT*>(p.indptr);
-  const IdxT* __restrict__ indices = reinterpret_cast<const IdxT*>(p.indices);
-  const int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-  const int64_t stride = (((int64_t)gridDim.x * blockDim.x) >> 5) * rows_per_warp;
-  const uint8_t* __restrict__ my_codes = p.codes + byte0;
-  // address of this lane's slice of source row `id`
-  auto row_ptr = [&](uint32_t id) -> const uint8_t* {
-    if (!PEER) return my_codes + (uint64_t)id * p.row_bytes;
-    const uint32_t owner = (uint32_t)__umul64hi((unsigned long long)id, p.shard_magic);
-    const uint32_t local = id - owner * p.rows_per_shard;
-    return p.shard[owner] + byte0 + (uint64_t)local * p.row_bytes;
-  };
-
-  // ---- three-deep software pipeline over the rows d, d+stride, d+2*stride, ... of this lane group.
-  // Rows are counted in 32 bits (the host checks n_dst < 2^31).
-  const int n_dst = (int)p.n_dst;
-  const int istride = (int)stride;
-  int d = (int)(warp * rows_per_warp) + sub;
-  const IdxT* idsA = indices;  // first neighbour id of rows i, i+1, i+2
-  const IdxT* idsB = indices;
-  const IdxT* idsC = indices;
-  int degA = 0, degB = 0, degC = 0;
-  if (d < n_dst && lane_active) { int64_t b = (int64_t)indptr[d]; degA = (int)((int64_t)indptr[d + 1] - b); idsA = indices + b; }
-  if (d + istride < n_dst && lane_active) {
-    int64_t b = (int64_t)indptr[d + istride]; degB = (int)((int64_t)indptr[d + istride + 1] - b); idsB = indices + b;
-  }
-  if (d + 2 * istride < n_dst && lane_active) {
-    int64_t b = (int64_t)indptr[d + 2 * istride]; degC = (int)((int64_t)indptr[d + 2 * istride + 1] - b); idsC = indices + b;
-  }
-  // One set of id registers is enough: a stage first issues the row loads that consume them, then
-  // overwrites them with the ids of the row after (the hardware scoreboard orders the two).
-  uint32_t nidx[U];
-  VecLoad<VEC> data[2][U];
-#pragma unroll
-  for (int u = 0; u < U; ++u) nidx[u] = u < degA ? (uint32_t)idsA[u] : 0u;
-#pragma unroll
-  for (int u = 0; u < U; ++u) {
-#pragma unroll
-    for (int w = 0; w < VEC / 4; ++w) data[0][u].w[w] = 0u;
-    if (u < degA) data[0][u].load(row_ptr(nidx[u]));
-  }
-#pragma unroll
-  for (int u = 0; u < U; ++u) nidx[u] = u < degB ? (uint32_t)idsB[u] : 0u;
+  if (!PRIME_EARLY) prime();
   // Neighbour slots beyond a row's degree read slab 0 of a zero-filled copy of the table geometry
   // (their data word is kept 0), so the decode loop needs no divergent branch: adding +0 changes nothing.
   const uint32_t lane_off_zero = lane_off + Lut<BITS>::TABLE_BYTES;
@@ -335,11 +378,17 @@ __global__ void __launch_bounds__(SqCta<BITS, DEC>::kThreads, SqCta<BITS, DEC>::
     for (int P = 0; P < 2; ++P) {
       if (row_base < n_dst) {  // warp uniform
         // (1) code rows of the next destination row -> data[P^1]
+        if (ASYNC) {
 #pragma unroll
-        for (int u = 0; u < U; ++u) {
+          for (int u = 0; u < U; ++u) fetch_async(P ^ 1, u, u < degB);
+          asm volatile("cp.async.commit_group;" ::: "memory");
+        } else {
 #pragma unroll
-          for (int w = 0; w < VEC / 4; ++w) data[P ^ 1][u].w[w] = 0u;
-          if (u < degB) data[P ^ 1][u].load(row_ptr(nidx[u]));
+          for (int u = 0; u < U; ++u) {
+#pragma unroll
+            for (int w = 0; w < VEC / 4; ++w) data[P ^ 1][u].w[w] = 0u;
+            if (u < degB) data[P ^ 1][u].load(row_ptr(nidx[u]));
+          }
         }
         // (2) neighbour ids of the row after it
 #pragma unroll
@@ -357,13 +406,21 @@ __global__ void __launch_bounds__(SqCta<BITS, DEC>::kThreads, SqCta<BITS, DEC>::
         Acc<EPL, PACKED> acc;
         acc.clear();
         const int umax = __reduce_max_sync(0xffffffffu, degA < U ? degA : U);  // slots any row of the warp uses
+        if (ASYNC) asm volatile("cp.async.wait_group 1;" ::: "memory");  // everything but the copies issued in (1) has landed
 #pragma unroll
         for (int u = 0; u < U; ++u) {
           if (u < umax) {  // warp uniform
+            VecLoad<VEC> landed;
+            if (ASYNC) {  // this lane reads back exactly the bytes it copied (or zeroed)
+              const uint32_t src = ring + (uint32_t)P * kStageBytes + (uint32_t)u * kSlotBytes;
+              if (VEC == 8) asm volatile("ld.shared.v2.b32 {%0, %1}, [%2];" : "=r"(landed.w[0]), "=r"(landed.w[VEC / 4 - 1]) : "r"(src));
+              else asm volatile("ld.shared.b32 %0, [%1];" : "=r"(landed.w[0]) : "r"(src));
+            }
+            const VecLoad<VEC>& row = ASYNC ? landed : data[ASYNC ? 0 : P][ASYNC ? 0 : u];
             if (DEC == DEC_LUT) {
-              sq_accumulate<BITS, VEC, DEC>(acc, data[P][u], table, u < degA ? lane_off : lane_off_zero, p.code_kind, scale, emin, mean);
+              sq_accumulate<BITS, VEC, DEC, ALIGNED>(acc, row, table, u < degA ? lane_off : lane_off_zero, p.code_kind, scale, emin, mean);
             } else if (u < degA) {
-              sq_accumulate<BITS, VEC, DEC>(acc, data[P][u], table, lane_off, p.code_kind, scale, emin, mean);
+              sq_accumulate<BITS, VEC, DEC, ALIGNED>(acc, row, table, lane_off, p.code_kind, scale, emin, mean);
             }
           }
         }
@@ -375,7 +432,7 @@ __global__ void __launch_bounds__(SqCta<BITS, DEC>::kThreads, SqCta<BITS, DEC>::
             if (k + u < degA) extra[u].load(row_ptr((uint32_t)idsA[k + u]));
 #pragma unroll
           for (int u = 0; u < 4; ++u)
-            if (k + u < degA) sq_accumulate<BITS, VEC, DEC>(acc, extra[u], table, lane_off, p.code_kind, scale, emin, mean);
+            if (k + u < degA) sq_accumulate<BITS, VEC, DEC, ALIGNED>(acc, extra[u], table, lane_off, p.code_kind, scale, emin, mean);
         }
 
         // (5) mean / dropout / store
@@ -385,7 +442,10 @@ __global__ void __launch_bounds__(SqCta<BITS, DEC>::kThreads, SqCta<BITS, DEC>::
           constexpr int LQ = Q >= 8 ? 3 : Q == 4 ? 2 : Q == 2 ? 1 : 0;  // low chunk-index bits that only depend on q
           const int NC = p.feat_dim >> 2;                               // chunks per output row
           const int NCP = Q << p.logG;                                  // row stride of the staging area (>= NC)
-          float4* stage = reinterpret_cast<float4*>(smem_raw + p.stage_offset) + (threadIdx.x >> 5) * (32 * Q);
+          // ASYNC kernels stage in the ring stage that was just decoded (it is free until the copies of the row after next)
+          float4* stage = ASYNC ? reinterpret_cast<float4*>(smem_raw + p.ring_offset + (threadIdx.x >> 5) * (2 * kStageBytes) + P * kStageBytes)
+                                : reinterpret_cast<float4*>(smem_raw + p.stage_offset) + (threadIdx.x >> 5) * (32 * Q);
+          static_assert(!ASYNC || 32 * EPL * 4 <= (int)kStageBytes, "a ring stage must hold a warp's output rows");
           // chunk c of a row is kept at c ^ m, m = the lane bits that the low bits of c do not already spread
           // over the banks; m only touches the q part of the index, so a lane stays inside its own Q chunks
           if (have_row) {
@@ -500,9 +560,9 @@ __global__ void __launch_bounds__(256) sq_spmm_generic_kernel(const void* __rest
 
 static int ilog2(int v) { int l = 0; while ((1 << l) < v) ++l; return l; }
 
-template <int BITS, int VEC, int U, typename IdxT, int DEC, bool PEER = false>
+template <int BITS, int VEC, int U, typename IdxT, int DEC, bool PEER = false, bool ASYNC = false>
 static int launch_fast(SqParams p, bool vec_store, cudaStream_t st) {
-  auto kern = sq_spmm_kernel<BITS, VEC, U, IdxT, DEC, PEER>;
+  auto kern = sq_spmm_kernel<BITS, VEC, U, IdxT, DEC, PEER, ASYNC>;
   constexpr int EPL = BITS == 16 ? VEC / 2 : VEC * 8 / BITS;
   // decode table (64 KB) + the decoded code values of each distinct codebook row
   size_t smem = 0;
@@ -511,16 +571,18 @@ static int launch_fast(SqParams p, bool vec_store, cudaStream_t st) {
     int n_rows = (1 << p.logG) < L::COPIES ? (1 << p.logG) : L::COPIES;
     smem = L::TABLE_BYTES + 256 + (size_t)n_rows * L::NCODE * sizeof(float);
   }
-  constexpr int kThreads = SqCta<BITS, DEC>::kThreads;
+  constexpr int kThreads = SqCta<BITS, DEC, ASYNC>::kThreads;
   constexpr int kWarpsPerCta = kThreads / 32;
   // staging area for coalesced output: warps x 32 lanes x EPL floats
   p.staged = 0;
   p.stage_offset = (int)smem;
   if (vec_store && EPL >= 4) {
     p.staged = 1;
-    smem += (size_t)kWarpsPerCta * 32 * EPL * sizeof(float);
+    if (!ASYNC) smem += (size_t)kWarpsPerCta * 32 * EPL * sizeof(float);  // (ASYNC kernels stage inside their rings)
   }
-  if (SqCta<BITS, DEC>::kAligned) smem += 65536;  // slack for the 64 KB alignment of the table inside the shared window
+  p.ring_offset = (int)smem;
+  if (ASYNC) smem += (size_t)kWarpsPerCta * 2 * U * 32 * VEC;  // two stages of U neighbour rows per warp
+  if (SqCta<BITS, DEC, ASYNC>::kAligned) smem += 65536;  // slack for the 64 KB alignment of the table inside the shared window
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return set_error(F2C_ERR_CUDA, "sq_decompress_spmm_csr: %s", cudaGetErrorString(e));
@@ -553,10 +615,16 @@ static int pick_u(const SqParams& p, bool vec_store, cudaStream_t st) {
   return launch_fast<BITS, VEC, 8, IdxT, DEC>(p, vec_store, st);
 }
 
+int g_tune_async = 0;  // f2c_set_tuning key 5: 1 = cp.async ring kernels for 4- and 8-bit table decode
+
 template <int BITS, typename IdxT>
 static int dispatch_fast(const SqParams& p, int vec, bool lut, bool vec_store, cudaStream_t st) {
   constexpr bool CAN_LUT = BITS <= 8;
   constexpr bool CAN_8 = BITS > 2;  // 1/2-bit: 4 bytes per lane already are 32 / 16 columns
+  if constexpr (BITS == 4 || BITS == 8) if (lut && vec == 8 && g_tune_async != 0) {
+    if (g_tune_u > 0 && g_tune_u < 12) return launch_fast<BITS, 8, 8, IdxT, DEC_LUT, false, true>(p, vec_store, st);
+    return launch_fast<BITS, 8, 12, IdxT, DEC_LUT, false, true>(p, vec_store, st);
+  }
   if constexpr (CAN_LUT) if (lut) {
     if constexpr (CAN_8) if (vec == 8) return pick_u<BITS, 8, IdxT, DEC_LUT>(p, vec_store, st);
     return pick_u<BITS, 4, IdxT, DEC_LUT>(p, vec_store, st);
@@ -733,7 +801,7 @@ extern "C" int f2c_sq_spmm_csr_peer(const void* const* shard_ptrs_host, int worl
 
 // Experiment knobs of the fused SQ kernel (no counterpart in the reference).  key 0: bytes per lane per
 // row load (4/8), 1: neighbours held in registers per row (8/12/16), 2: table decode on/off, 3: CTAs per
-// SM, 4: pipelined VQ / two-level kernel on (1) / off (0).  value 0 (key 2: -1, key 4: 1) restores the built-in choice.
+// SM, 4: pipelined VQ / two-level kernel on (1) / off (0), 5: cp.async ring variant of the 4- / 8-bit kernels on (1) / off (0).  value 0 (key 2: -1, key 4: 1) restores the built-in choice.
 extern "C" int f2c_set_tuning(int key, int value) {
   switch (key) {
     case 0: g_tune_vec = value; break;
@@ -741,6 +809,7 @@ extern "C" int f2c_set_tuning(int key, int value) {
     case 2: g_tune_lut = value; break;
     case 3: g_tune_ctas_per_sm = value; break;
     case 4: g_tune_vq_fast = value; break;
+    case 5: g_tune_async = value; break;
     case 10: g_kmeans_force_exact = value; break;
     default: return set_error(F2C_ERR_INVALID, "set_tuning: unknown key %d", key);
   }

@@ -367,8 +367,8 @@ class KMeans:
 
 def set_tuning(key, value):
     """Experiment knobs: key in {"vec", "inflight", "lut", "ctas_per_sm"} (fused SQ kernel), "vq_fast" (1/0: pipelined
-    VQ / two-level kernel or the general one), "kmeans_exact" (1: exact fp32 scorer, -1: tensor-core scorer, 0: heuristic)."""
-    check(lib.f2c_set_tuning({"vec": 0, "inflight": 1, "lut": 2, "ctas_per_sm": 3, "vq_fast": 4, "kmeans_exact": 10}[key], int(value)))
+    VQ / two-level kernel or the general one), "sq_async" (1/0: cp.async ring variant of the 4- / 8-bit fused SQ kernels), "kmeans_exact" (1: exact fp32 scorer, -1: tensor-core scorer, 0: heuristic)."""
+    check(lib.f2c_set_tuning({"vec": 0, "inflight": 1, "lut": 2, "ctas_per_sm": 3, "vq_fast": 4, "sq_async": 5, "kmeans_exact": 10}[key], int(value)))
 
 
 # ------------------------------------------------------------------ neighbour sampling

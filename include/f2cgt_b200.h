@@ -186,6 +186,8 @@ int f2c_kmeans_assign_static(const float* x, const float* centers, int64_t* labe
 /* Experiment knobs (no counterpart in the reference).  Fused SQ kernel - key 0: bytes per lane per row load
  * (4/8), 1: neighbours held in registers per row (8/12/16), 2: table decode on/off, 3: CTAs per SM; value 0
  * (key 2: -1) restores the built-in choice.  Key 4: pipelined VQ / two-level kernel on (1, default) or off (0).
+ * Key 5: 4- / 8-bit fused SQ kernels that stage neighbour rows in a shared-memory ring with cp.async instead of
+ * registers, on (1) or off (0, default: measured slower).
  * Key 10: k-means scorer, 1 exact fp32, -1 tensor cores, 0 heuristic. */
 int f2c_set_tuning(int key, int value);
 

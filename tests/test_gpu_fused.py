@@ -90,8 +90,13 @@ def test_fused_sq_every_tuning_variant_is_bit_identical(capi, oracle, bits):
                 for lut in (0, 1):
                     ops.set_tuning("vec", vec), ops.set_tuning("inflight", inflight), ops.set_tuning("lut", lut)
                     assert torch.equal(capi.sq_decompress_spmm_csr(*args), base), (vec, inflight, lut)
+        # the cp.async ring variant (neighbour rows staged in shared memory instead of registers), 8 and 12 rows per stage
+        ops.set_tuning("vec", 0), ops.set_tuning("lut", -1)
+        for inflight in (8, 12, 16):
+            ops.set_tuning("inflight", inflight), ops.set_tuning("sq_async", 1)
+            assert torch.equal(capi.sq_decompress_spmm_csr(*args), base), ("async", inflight)
     finally:
-        ops.set_tuning("vec", 0), ops.set_tuning("inflight", 0), ops.set_tuning("lut", -1)
+        ops.set_tuning("vec", 0), ops.set_tuning("inflight", 0), ops.set_tuning("lut", -1), ops.set_tuning("sq_async", 0)
 
 
 @pytest.mark.parametrize("bits", [4, 16])
