@@ -223,12 +223,13 @@ __global__ void __launch_bounds__(kSqLutThreads) sq_decompress_lut_kernel(
 #pragma unroll
     for (int q = 0; q < EPT / 4; ++q) stg_cs_f4(o + 4 * q, make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]));
   };
-  for (; row + 3 * step < rows; row += 4 * step, cp += 4 * cstep, op += 4 * ostep) {
-    uint32_t raw[4];
+  constexpr int kInFlight = 8;  // rows in flight per thread
+  for (; row + (kInFlight - 1) * step < rows; row += kInFlight * step, cp += kInFlight * cstep, op += kInFlight * ostep) {
+    uint32_t raw[kInFlight];
 #pragma unroll
-    for (int u = 0; u < 4; ++u) raw[u] = fetch(cp + u * cstep);
+    for (int u = 0; u < kInFlight; ++u) raw[u] = fetch(cp + u * cstep);
 #pragma unroll
-    for (int u = 0; u < 4; ++u) emit(raw[u], op + u * ostep);
+    for (int u = 0; u < kInFlight; ++u) emit(raw[u], op + u * ostep);
   }
   for (; row < rows; row += step, cp += cstep, op += ostep) emit(fetch(cp), op);
 }

@@ -59,7 +59,7 @@ __global__ void __launch_bounds__(256) vq_decompress_scalar_kernel(const void* _
 // Streaming variant for the common shapes (uint8 codes, fp32 codebooks that fit in shared memory, vec_per_row
 // dividing the CTA size): the codebooks are staged once per CTA of a persistent grid, a thread keeps one float4
 // column position for its whole life (so its subspace and offset are computed once, and row advance is an add),
-// and four rows are in flight per thread.  Subspaces narrower than 32 columns are interleaved inside 128-byte
+// and eight rows are in flight per thread.  Subspaces narrower than 32 columns are interleaved inside 128-byte
 // lines, so that the eight lanes of a quarter-warp read eight different 16-byte bank groups whatever the codes.
 constexpr int kVqStreamThreads = 1024;
 constexpr size_t kVqStreamSmem = 200 * 1024;
@@ -97,12 +97,13 @@ __global__ void __launch_bounds__(kVqStreamThreads, 1) vq_decompress_stream_kern
   float* op = out + row * feat_dim + j;
   const int64_t cstep = step * n_cb, ostep = step * feat_dim;
   const uint32_t kmax = (uint32_t)K - 1u;
-  for (; row + 3 * step < rows; row += 4 * step, cp += 4 * cstep, op += 4 * ostep) {
-    uint32_t c[4];
+  constexpr int kInFlight = 8;  // rows in flight per thread
+  for (; row + (kInFlight - 1) * step < rows; row += kInFlight * step, cp += kInFlight * cstep, op += kInFlight * ostep) {
+    uint32_t c[kInFlight];
 #pragma unroll
-    for (int u = 0; u < 4; ++u) c[u] = min((uint32_t)__ldg(cp + u * cstep), kmax);
+    for (int u = 0; u < kInFlight; ++u) c[u] = min((uint32_t)__ldg(cp + u * cstep), kmax);
 #pragma unroll
-    for (int u = 0; u < 4; ++u) {
+    for (int u = 0; u < kInFlight; ++u) {
       float4 v;
       asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(lane_base + c[u] * (uint32_t)stride));
       stg_cs_f4(op + u * ostep, v);
