@@ -162,6 +162,7 @@ struct Top2 {
 
 // Shared memory: [B tile][A tile group 0][A tile group 1][scratch 256 floats][exchange 2 x 128 x 16 B][2 mbarriers]
 // [tmem slot][2 fail flags]
+template <bool BF16>
 __global__ void __launch_bounds__(kCtaThreads, 1) kmeans_tc_kernel(const Params p) {
   extern __shared__ __align__(128) unsigned char smem[];
   const int tid = threadIdx.x;
@@ -171,7 +172,7 @@ __global__ void __launch_bounds__(kCtaThreads, 1) kmeans_tc_kernel(const Params 
   const int half = lt >> 7;          // which half of the row's K chunks it loads and which half of the centres it scans
   const int lane_quarter = (lt >> 5) & 3;
   // 16-byte K chunks per operand row (the last two carry the norm term): 4 tf32 or 8 bf16 values per chunk
-  const int kc_x = p.bf16 ? 3 * p.dp / 8 : p.terms * p.dp / 4;
+  const int kc_x = BF16 ? 3 * p.dp / 8 : p.terms * p.dp / 4;
   const int kc = kc_x + 2;
   const uint32_t lbo_b = kMaxN * 16, lbo_a = kTileM * 16, sbo = 128;
   unsigned char* b_tile = smem;
@@ -202,7 +203,7 @@ __global__ void __launch_bounds__(kCtaThreads, 1) kmeans_tc_kernel(const Params 
       for (int t = 0; t < p.d; ++t) { const float v = __ldg(p.y + (int64_t)c * p.d + t); nrm = fmaf(v, v, nrm); }
     // cosine: rows are scaled to unit length (zero rows stay zero); L2: rows as they are
     const float row_scale = p.metric == F2C_COSINE ? (nrm > 0.0f ? 1.0f / sqrtf(nrm) : 0.0f) : 1.0f;
-    if (p.bf16) {
+    if (BF16) {
       const int C = p.dp / 8;
       for (int cq = 0; cq < C; ++cq) {
         float v[8];
@@ -218,7 +219,7 @@ __global__ void __launch_bounds__(kCtaThreads, 1) kmeans_tc_kernel(const Params 
         *reinterpret_cast<uint4*>(b_tile + (size_t)(2 * C + cq) * lbo_b + c * 16) = c2;
       }
     }
-    for (int gq = 0; gq < (p.bf16 ? 0 : G); ++gq) {
+    for (int gq = 0; gq < (BF16 ? 0 : G); ++gq) {
       float v[4];
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
@@ -237,7 +238,7 @@ __global__ void __launch_bounds__(kCtaThreads, 1) kmeans_tc_kernel(const Params 
     }
     // norm term: -|y_c|^2 / 2 split in two TF32 values (L2), 0 (cosine), a value that never wins (padding)
     float h = c < p.k ? (p.metric == F2C_L2 ? -0.5f * nrm : 0.0f) : -1e30f;
-    if (p.bf16) {  // three bf16 pieces of h against three ones on the point side
+    if (BF16) {  // three bf16 pieces of h against three ones on the point side
       const __nv_bfloat16 h1 = __float2bfloat16_rn(h);
       const __nv_bfloat16 h2 = __float2bfloat16_rn(h - __bfloat162float(h1));
       const __nv_bfloat16 h3 = __float2bfloat16_rn(h - __bfloat162float(h1) - __bfloat162float(h2));
@@ -262,7 +263,7 @@ __global__ void __launch_bounds__(kCtaThreads, 1) kmeans_tc_kernel(const Params 
   cmax = sqrtf(cmax);
 
   // instruction descriptor: fp32 accumulate; A and B formats tf32 (2, kind::tf32) or bf16 (1, kind::f16); N / 8; M / 16
-  const uint32_t fmt = p.bf16 ? 1u : 2u;
+  const uint32_t fmt = BF16 ? 1u : 2u;
   const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(p.n_pad >> 3) << 17) | ((uint32_t)(kTileM >> 4) << 24);
   const int ksteps = kc / 2;  // one MMA consumes 8 tf32 = two 16-byte chunks of K
   const uint32_t mbar_addr = smem_u32(mbar + g);
@@ -279,7 +280,7 @@ __global__ void __launch_bounds__(kCtaThreads, 1) kmeans_tc_kernel(const Params 
     const int G = p.dp / 4;
 #pragma unroll
     for (int q = 0; q < kMaxChunks; ++q) {
-      const int gq = p.bf16 ? 2 * (half + 2 * (q >> 1)) + (q & 1) : half + 2 * q;
+      const int gq = BF16 ? 2 * (half + 2 * (q >> 1)) + (q & 1) : half + 2 * q;
       xv[q] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
       if (gq < G && tile_ < n_tiles && i_ < p.n) {
         if (p.vec4 && 4 * gq + 3 < p.d) {
@@ -303,7 +304,7 @@ __global__ void __launch_bounds__(kCtaThreads, 1) kmeans_tc_kernel(const Params 
     float xx = 0.0f;
     {
       const int G = p.dp / 4;
-      if (p.bf16) {
+      if (BF16) {
         const int C = p.dp / 8;
 #pragma unroll
         for (int q2 = 0; q2 < kMaxChunks / 2; ++q2) {
@@ -322,7 +323,7 @@ __global__ void __launch_bounds__(kCtaThreads, 1) kmeans_tc_kernel(const Params 
         }
       }
 #pragma unroll
-      for (int q = 0; q < (p.bf16 ? 0 : kMaxChunks); ++q) {
+      for (int q = 0; q < (BF16 ? 0 : kMaxChunks); ++q) {
         const int gq = half + 2 * q;
         if (gq < G) {
           const float v[4] = {xv[q].x, xv[q].y, xv[q].z, xv[q].w};
@@ -341,7 +342,7 @@ __global__ void __launch_bounds__(kCtaThreads, 1) kmeans_tc_kernel(const Params 
       // norm-term columns: ones against the pieces of -|y|^2 / 2 (two tf32 ones, or three bf16 ones = 0x3F80 each)
       *reinterpret_cast<uint4*>(a_tile + (size_t)(kc_x + half) * lbo_a + pt * 16) =
           half != 0 ? make_uint4(0u, 0u, 0u, 0u)
-                    : (p.bf16 ? make_uint4(0x3F803F80u, 0x00003F80u, 0u, 0u) : make_uint4(0x3F800000u, 0x3F800000u, 0u, 0u));
+                    : (BF16 ? make_uint4(0x3F803F80u, 0x00003F80u, 0u, 0u) : make_uint4(0x3F800000u, 0x3F800000u, 0u, 0u));
     }
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -354,7 +355,7 @@ __global__ void __launch_bounds__(kCtaThreads, 1) kmeans_tc_kernel(const Params 
       for (int s_ = 0; s_ < ksteps; ++s_) {
         const uint64_t a_desc = make_desc(a_addr + (uint32_t)s_ * 2u * lbo_a, lbo_a, sbo);
         const uint64_t b_desc = make_desc(b_addr + (uint32_t)s_ * 2u * lbo_b, lbo_b, sbo);
-        if (p.bf16) mma_bf16(tmem_base, a_desc, b_desc, idesc, s_ > 0 ? 1u : 0u);
+        if (BF16) mma_bf16(tmem_base, a_desc, b_desc, idesc, s_ > 0 ? 1u : 0u);
         else mma_tf32(tmem_base, a_desc, b_desc, idesc, s_ > 0 ? 1u : 0u);
       }
       asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(mbar_addr) : "memory");
@@ -466,12 +467,13 @@ int kmeans_assign_tc(const float* x, const float* y, int64_t* labels, int64_t n,
   const int kc = (p.bf16 ? 3 * p.dp / 8 : p.terms * p.dp / 4) + 2;
   size_t smem = (size_t)kc * (tc::kMaxN + 2 * tc::kTileM) * 16 + tc::kMaxN * 4 + 2 * tc::kTileM * 16 + 64;
   if (smem < 120 * 1024) smem = 120 * 1024;  // one CTA per SM: a second one would only wait for the TMEM columns
-  e = cudaFuncSetAttribute(tc::kmeans_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  auto kern = p.bf16 ? tc::kmeans_tc_kernel<true> : tc::kmeans_tc_kernel<false>;
+  e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return set_error(F2C_ERR_CUDA, "kmeans_assign: %s", cudaGetErrorString(e));
   int64_t tiles = ceil_div(n, tc::kTileM);
   int64_t grid = ceil_div(tiles, 2);  // one CTA per SM (it owns all 512 TMEM columns), two tiles in flight per CTA
   if (grid > kSmCount) grid = kSmCount;
-  tc::kmeans_tc_kernel<<<(unsigned)grid, tc::kCtaThreads, smem, st>>>(p);
+  kern<<<(unsigned)grid, tc::kCtaThreads, smem, st>>>(p);
   int rc = check_launch("kmeans_assign (tensor cores)");
   if (rc) return rc;
   // undecided points: exact fp32 scorer over the device-side list
