@@ -161,7 +161,7 @@ struct Top2 {
 };
 
 // Shared memory: [B tile][A tile group 0][A tile group 1][scratch 256 floats][exchange 2 x 128 x 16 B][2 mbarriers]
-// [tmem slot][2 fail flags]
+// [tmem slot][2 fail flags][2 x 128 floats |x|^2]
 template <bool BF16>
 __global__ void __launch_bounds__(kCtaThreads, 1) kmeans_tc_kernel(const Params p) {
   extern __shared__ __align__(128) unsigned char smem[];
@@ -182,6 +182,7 @@ __global__ void __launch_bounds__(kCtaThreads, 1) kmeans_tc_kernel(const Params 
   uint64_t* mbar = reinterpret_cast<uint64_t*>(scratch + kMaxN + 2 * kTileM * 4);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(mbar + 2);
   volatile uint32_t* fail = tmem_slot + 1;
+  float* xx_s = reinterpret_cast<float*>(mbar + 8) + g * kTileM;  // |x|^2 of the tile's points (bf16 path)
 
   // ---- one-time setup: TMEM (all 512 columns: 256 per group), mbarriers, centre tile ----
   if (tid < 32) {
@@ -275,12 +276,19 @@ __global__ void __launch_bounds__(kCtaThreads, 1) kmeans_tc_kernel(const Params 
   // previous tile's MMA and epilogue: chunk q of the thread is 16-byte chunk half + 2q of the row (at most 8: d <= 64).
   constexpr int kMaxChunks = 8;
   float4 xv[kMaxChunks];
+  // bf16 path (rows of 132 to 256 bytes): the tile's rows are fetched and split by a different thread mapping than the
+  // one of the epilogue, so that a warp-wide load covers 8 rows x 128 contiguous bytes instead of 32 rows x 16 bytes
+  // (the load queue was the limiter): lane = (row pl of 8, 32-byte chunk cl of 4), warp wq of the group, item
+  // j = 0..3 -> row block 2 wq + (j >> 1), chunk cl + 4 (j & 1).  Shared-memory stores stay conflict-free (8 lanes =
+  // 8 consecutive rows of one chunk), |x|^2 goes through shared memory to the epilogue thread of the point.
+  const int wq = lt >> 5, pl = lt & 7, cl = (lt >> 3) & 3;
   auto fetch_row = [&](int64_t tile_) {
-    const int64_t i_ = tile_ * kTileM + pt;
+    const int64_t i_own = tile_ * kTileM + pt;
     const int G = p.dp / 4;
 #pragma unroll
     for (int q = 0; q < kMaxChunks; ++q) {
-      const int gq = BF16 ? 2 * (half + 2 * (q >> 1)) + (q & 1) : half + 2 * q;
+      const int gq = BF16 ? 2 * (cl + 4 * ((q >> 1) & 1)) + (q & 1) : half + 2 * q;
+      const int64_t i_ = BF16 ? tile_ * kTileM + (wq * 2 + (q >> 2)) * 8 + pl : i_own;
       xv[q] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
       if (gq < G && tile_ < n_tiles && i_ < p.n) {
         if (p.vec4 && 4 * gq + 3 < p.d) {
@@ -306,20 +314,29 @@ __global__ void __launch_bounds__(kCtaThreads, 1) kmeans_tc_kernel(const Params 
       const int G = p.dp / 4;
       if (BF16) {
         const int C = p.dp / 8;
+        float part[2] = {0.0f, 0.0f};  // this thread's share of |x|^2 of its two rows
 #pragma unroll
         for (int q2 = 0; q2 < kMaxChunks / 2; ++q2) {
-          const int cq = half + 2 * q2;  // bf16 chunk = float4 chunks 2 cq, 2 cq + 1 = xv[2 q2], xv[2 q2 + 1]
+          const int cq = cl + 4 * (q2 & 1);  // bf16 chunk = float4 chunks 2 cq, 2 cq + 1 = xv[2 q2], xv[2 q2 + 1]
+          const int ptl = (wq * 2 + (q2 >> 1)) * 8 + pl;
           if (cq < C) {
             const float v[8] = {xv[2 * q2].x, xv[2 * q2].y, xv[2 * q2].z, xv[2 * q2].w,
                                 xv[2 * q2 + 1].x, xv[2 * q2 + 1].y, xv[2 * q2 + 1].z, xv[2 * q2 + 1].w};
 #pragma unroll
-            for (int e = 0; e < 8; ++e) xx = fmaf(v[e], v[e], xx);
+            for (int e = 0; e < 8; ++e) part[q2 >> 1] = fmaf(v[e], v[e], part[q2 >> 1]);
             uint4 c1, c2;
             split8_bf16(v, c1, c2);  // A' = [x1 | x2 | x1]
-            *reinterpret_cast<uint4*>(a_tile + (size_t)(cq) * lbo_a + pt * 16) = c1;
-            *reinterpret_cast<uint4*>(a_tile + (size_t)(C + cq) * lbo_a + pt * 16) = c2;
-            *reinterpret_cast<uint4*>(a_tile + (size_t)(2 * C + cq) * lbo_a + pt * 16) = c1;
+            *reinterpret_cast<uint4*>(a_tile + (size_t)(cq) * lbo_a + ptl * 16) = c1;
+            *reinterpret_cast<uint4*>(a_tile + (size_t)(C + cq) * lbo_a + ptl * 16) = c2;
+            *reinterpret_cast<uint4*>(a_tile + (size_t)(2 * C + cq) * lbo_a + ptl * 16) = c1;
           }
+        }
+#pragma unroll
+        for (int b = 0; b < 2; ++b) {
+          float v = part[b];
+          v += __shfl_xor_sync(0xffffffffu, v, 8);
+          v += __shfl_xor_sync(0xffffffffu, v, 16);
+          if (cl == 0) xx_s[(wq * 2 + b) * 8 + pl] = v;
         }
       }
 #pragma unroll
@@ -348,6 +365,7 @@ __global__ void __launch_bounds__(kCtaThreads, 1) kmeans_tc_kernel(const Params 
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     group_sync(g);  // A tile complete; every warp of the group has finished reading the previous tile's accumulators
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    if (BF16) xx = half == 0 ? xx_s[pt] : 0.0f;  // read before the next tile's split overwrites it (two group syncs away)
 
     // ---- S = A' * B'^T into this group's TMEM columns ----
     if (lt == 0) {
@@ -465,7 +483,7 @@ int kmeans_assign_tc(const float* x, const float* y, int64_t* labels, int64_t n,
   cudaError_t e = cudaMemsetAsync(head, 0, 256, st);
   if (e != cudaSuccess) return set_error(F2C_ERR_CUDA, "kmeans_assign: %s", cudaGetErrorString(e));
   const int kc = (p.bf16 ? 3 * p.dp / 8 : p.terms * p.dp / 4) + 2;
-  size_t smem = (size_t)kc * (tc::kMaxN + 2 * tc::kTileM) * 16 + tc::kMaxN * 4 + 2 * tc::kTileM * 16 + 64;
+  size_t smem = (size_t)kc * (tc::kMaxN + 2 * tc::kTileM) * 16 + tc::kMaxN * 4 + 2 * tc::kTileM * 16 + 64 + 2 * tc::kTileM * 4;
   if (smem < 120 * 1024) smem = 120 * 1024;  // one CTA per SM: a second one would only wait for the TMEM columns
   auto kern = p.bf16 ? tc::kmeans_tc_kernel<true> : tc::kmeans_tc_kernel<false>;
   e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
