@@ -13,13 +13,16 @@ LIB_PATH = os.environ.get("F2CGT_B200_LIB") or os.path.join(_PKG, "libf2cgt_b200
 U8, I8, I16, I32, I64, F16, F32, F64 = range(8)
 MEAN, SUM = 0, 1
 L2, COSINE = 0, 1
+SCORER_EXACT, SCORER_TENSOR = 0x100, 0x200
+# f2c_kernel: kernel family of a fused aggregation call
+KERNELS = {"auto": 0, "stream": 1, "prefetch": 2, "general": 3, "prefetch_arith": 4}
 
 STATUS_NAMES = {1: "invalid argument", 2: "unsupported", 3: "CUDA error", 4: "size limit"}
 
 
 class Epilogue(C.Structure):
     _fields_ = [("p", C.c_float), ("training", C.c_int), ("scale", C.c_int), ("seed", C.c_uint64),
-                ("offset", C.c_uint64)]
+                ("offset", C.c_uint64), ("kernel", C.c_int)]
 
 
 class F2CError(RuntimeError):
@@ -62,11 +65,12 @@ SIGNATURES = {
     "f2c_kmeans_assign_workspace": [i64, i64, i64],
     "f2c_kmeans_assign": [p, p, p, i64, i64, i64, ci, p, p],
     "f2c_kmeans_assign_static": [p, p, p, i64, i64, i64, ci, p],
+    "f2c_kmeans_assign_static_status": [p, p, p],
+    "f2c_device_status": [p, p],
     "f2c_check_csc": [p, p, ci, i64, i64, p, p],
     "f2c_relabel_capacity": [i64],
     "f2c_relabel_mark": [p, ci, i64, p, p, i64, p, p, p],
     "f2c_relabel_assign": [p, ci, i64, p, p, i64, p, p, p, p, p],
-    "f2c_set_tuning": [ci, ci],
     "f2c_sample_degrees": [p, p, p, ci, i64, ci, p],
     "f2c_sample_neighbors": [p, p, p, p, p, ci, i64, ci, u64, u64, p],
     "f2c_last_error": [],

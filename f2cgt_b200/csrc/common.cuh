@@ -11,12 +11,14 @@
 
 namespace f2c {
 
-constexpr int kSmCount = 148;          // B200: 2 dies x 74 SMs
+constexpr int kSmCount = 148;          // B200: 2 dies x 74 SMs (sizing default; launches ask sm_count() for the device's own figure)
 constexpr int kCodebookDim = 5;        // [fmin, fmax, emin, emax, mean] (reference src/sq_quantization.cu:17)
 
 // ---- error plumbing (defined in api.cu) ----
 int set_error(int status, const char* fmt, ...);
 int check_launch(const char* what);
+int sm_count(int device);  // multiprocessors of `device` (queried once per device)
+int current_sm_count();     // the same for the current device
 
 #define F2C_REQUIRE(cond, status, ...)                 \
   do {                                                 \
@@ -152,6 +154,9 @@ static inline DropoutArgs make_dropout(const f2c_epilogue* ep) {
   a.offset = ep->offset;
   return a;
 }
+
+// Kernel family a caller asked for (f2c_epilogue::kernel); F2C_KERNEL_AUTO without an options struct.
+static inline int kernel_variant(const f2c_epilogue* ep) { return ep == nullptr ? F2C_KERNEL_AUTO : ep->kernel; }
 
 __device__ __forceinline__ float dropout_apply(float v, uint32_t draw, const DropoutArgs& a) {
   bool drop = a.drop_all || draw < a.threshold;

@@ -32,49 +32,29 @@
 //    corrections that reproduce the IEEE quotient, and written as whole 512-byte runs.
 //
 // Grid: persistent, exactly the resident CTA count; each CTA builds its table once.
-#include "common.cuh"
+#include <mutex>
+
+#include "sq_fused.cuh"
 
 namespace f2c {
 
 int validate_sq(const char* op, int code_dtype, int64_t n_codebooks, int64_t src_dim, int64_t feat_dim, int bits,
                 int64_t column_slice);
+// streamed kernel (fused_sq_stream.cu); *served = false when it does not take the shape
+int launch_sq_stream(int bits, int index_dtype, const void* codes, int code_dtype, const float* codebooks, int64_t n_cb,
+                     const void* indptr, const void* indices, float* out, int64_t n_dst, int64_t n_src, int64_t src_dim, int64_t D,
+                     int64_t cs, int reduce, const DropoutArgs& drop, cudaStream_t st, const void* const* shards, int world,
+                     int64_t rows_per_shard, bool* served);
 
-// experiment knobs (0 = built-in choice), set through f2c_set_tuning
-int g_tune_vec = 0, g_tune_u = 0, g_tune_lut = -1, g_tune_ctas_per_sm = 0;
-extern int g_kmeans_force_exact;
-extern int g_tune_vq_fast;
-
-template <int VEC> struct VecLoad;
-template <> struct VecLoad<4> {
-  uint32_t w[1];
-  __device__ __forceinline__ void load(const void* p) { w[0] = ldg_nc_u32(p); }
-};
-template <> struct VecLoad<8> {
-  uint32_t w[2];
-  __device__ __forceinline__ void load(const void* p) { uint2 v = ldg_nc_u64(p); w[0] = v.x; w[1] = v.y; }
-};
-
-enum { DEC_ARITH = 0, DEC_LUT = 1 };
 // Table kernels for 4- and 8-bit codes run as ONE 512-thread CTA per SM whose table starts on a 64 KB boundary of the
 // shared window: the base address then lives in the upper half of the byte permute's second source and a lookup
 // address costs one instruction.  Measured on B200 (config-2 block): 4 bit 47.1 -> 45.1 us, 8 bit 55.3 -> 51.9 us; the
 // 1- and 2-bit kernels (fewer lookups per byte of code, larger staging area) are faster as two 256-thread CTAs.
-// ASYNC kernels keep no neighbour rows in registers: every lane copies its bytes of the next destination row's neighbour
-// rows into a per-warp shared-memory ring with cp.async and reads them back when the row is decoded, which frees the
-// 32-48 prefetch registers per thread and lets 24 warps run per SM (one 768-thread CTA).
-template <int BITS, int DEC, bool ASYNC = false> struct SqCta {
-  static constexpr bool kAligned = !ASYNC && DEC == DEC_LUT && BITS >= 4;
-  static constexpr int kThreads = ASYNC ? 768 : kAligned ? 512 : 256;
-  static constexpr int kCtasPerSm = (ASYNC || kAligned) ? 1 : 2;
+template <int BITS, int DEC> struct SqCta {
+  static constexpr bool kAligned = DEC == DEC_LUT && BITS >= 4;
+  static constexpr int kThreads = kAligned ? 512 : 256;
+  static constexpr int kCtasPerSm = kAligned ? 1 : 2;
 };
-
-__device__ __forceinline__ void cp_async_bytes4(uint32_t dst, const void* src) {
-  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src) : "memory");
-}
-__device__ __forceinline__ void cp_async_bytes8(uint32_t dst, const void* src) {
-  asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(dst), "l"(src) : "memory");
-}
-enum { CODE_U8 = 0, CODE_I8 = 1, CODE_I16 = 2 };
 
 struct PeerInfo {
   const void* shard[8];
@@ -102,126 +82,16 @@ struct SqParams {
   unsigned long long shard_magic;  // floor(2^64 / rows_per_shard) + 1: exact 32-bit division by one multiply-high
   int staged;        // 1: rows leave through the shared-memory staging area (feat_dim % 4 == 0)
   int stage_offset;  // byte offset of that area in dynamic shared memory
-  int ring_offset;   // ASYNC kernels: byte offset of the per-warp rings of neighbour-row bytes
   DropoutArgs drop;
 };
-
-// Decode table geometry: 256 slabs of 256 bytes (64 KB).  A slab holds COPIES copies of the FLOATS
-// floats its byte encodes; one copy is one vector read (1-bit codes: two 16-byte halves kept 128 bytes
-// apart so that eight lanes reading a half touch eight different bank groups).
-template <int BITS> struct Lut {
-  static constexpr int B = (BITS == 1 || BITS == 2 || BITS == 4) ? BITS : 8;
-  static constexpr int FLOATS = 8 / B;                              // 8, 4, 2, 1
-  static constexpr int COPY_BYTES = FLOATS >= 4 ? 16 : FLOATS * 4;
-  static constexpr int HALVES = FLOATS == 8 ? 2 : 1;
-  static constexpr int COPIES = 256 / (COPY_BYTES * HALVES) > 32 ? 32 : 256 / (COPY_BYTES * HALVES);  // 8, 16, 32, 32
-  static constexpr int NCODE = 1 << B;
-  static constexpr int TABLE_BYTES = 256 * 256;
-  __device__ static __forceinline__ uint32_t lane_offset(int lane) { return (uint32_t)(lane & (COPIES - 1)) * COPY_BYTES; }
-};
-
-// Accumulators: fp32 pairs packed in 64-bit registers where the decode delivers pairs (table decode of
-// 1/2/4-bit codes), so that every add is one add.f32x2 on operands that are already pairs; scalar
-// fp32 registers otherwise.  Each half rounds to nearest exactly like a scalar add.
-template <int EPL, bool PACKED> struct Acc;
-template <int EPL> struct Acc<EPL, true> {
-  unsigned long long v[EPL / 2];
-  __device__ __forceinline__ void clear() {
-#pragma unroll
-    for (int i = 0; i < EPL / 2; ++i) v[i] = 0ull;
-  }
-  __device__ __forceinline__ void add_pair(int i, unsigned long long x) { asm("add.rn.f32x2 %0, %0, %1;" : "+l"(v[i]) : "l"(x)); }
-  __device__ __forceinline__ void add_one(int, float) {}
-  __device__ __forceinline__ float4 chunk(int q) const {
-    return make_float4(__uint_as_float((uint32_t)v[2 * q]), __uint_as_float((uint32_t)(v[2 * q] >> 32)),
-                       __uint_as_float((uint32_t)v[2 * q + 1]), __uint_as_float((uint32_t)(v[2 * q + 1] >> 32)));
-  }
-  __device__ __forceinline__ float get(int e) const { return __uint_as_float((uint32_t)(v[e >> 1] >> (32 * (e & 1)))); }
-};
-template <int EPL> struct Acc<EPL, false> {
-  float v[EPL];
-  __device__ __forceinline__ void clear() {
-#pragma unroll
-    for (int i = 0; i < EPL; ++i) v[i] = 0.0f;
-  }
-  __device__ __forceinline__ void add_pair(int, unsigned long long) {}
-  __device__ __forceinline__ void add_one(int i, float x) { v[i] += x; }
-  __device__ __forceinline__ float4 chunk(int q) const { return make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]); }
-  __device__ __forceinline__ float get(int e) const { return v[e]; }
-};
-
-__device__ __forceinline__ unsigned long long lds_b64(uint32_t a) {
-  unsigned long long v;
-  asm volatile("ld.shared.b64 %0, [%1];" : "=l"(v) : "r"(a));
-  return v;
-}
-__device__ __forceinline__ void lds_b64x2(uint32_t a, unsigned long long& x, unsigned long long& y) {
-  asm volatile("ld.shared.v2.b64 {%0, %1}, [%2];" : "=l"(x), "=l"(y) : "r"(a));
-}
-__device__ __forceinline__ float lds_f32(uint32_t a) {
-  float v;
-  asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(a));
-  return v;
-}
-
-// Add the decoded elements of one lane's share of a neighbour row to its accumulators.
-// `table` = shared-window address of the decode table, lane_off = this lane's copy offset in a slab; aligned-table
-// kernels pass table = 0 and the (64 KB aligned) address inside lane_off.
-template <int BITS, int VEC, int DEC, bool ALIGNED, typename AccT>
-__device__ __forceinline__ void sq_accumulate(AccT& acc, const VecLoad<VEC>& data, uint32_t table, uint32_t lane_off, int code_kind,
-                                              float scale, float emin, float mean) {
-  constexpr int NW = VEC / 4;
-#pragma unroll
-  for (int w = 0; w < NW; ++w) {
-    const uint32_t word = data.w[w];
-    if (DEC == DEC_LUT) {
-      using L = Lut<BITS>;
-#pragma unroll
-      for (int b = 0; b < 4; ++b) {
-        // result bytes [lane_off.b0, word.b_b, lane_off.b2, lane_off.b3]  ==  (byte << 8) | lane_off
-        const uint32_t e = (ALIGNED ? 0u : table) + __byte_perm(word, lane_off, 0x7604u | (uint32_t)(b << 4));
-        const int k = w * 4 + b;  // byte number inside the lane's slice
-        if (L::FLOATS == 1) {
-          acc.add_one(k, lds_f32(e));
-        } else if (L::FLOATS == 2) {
-          acc.add_pair(k, lds_b64(e));
-        } else {
-#pragma unroll
-          for (int h = 0; h < L::HALVES; ++h) {
-            unsigned long long x, y;
-            lds_b64x2(e + 128 * h, x, y);
-            acc.add_pair((k * L::HALVES + h) * 2, x);
-            acc.add_pair((k * L::HALVES + h) * 2 + 1, y);
-          }
-        }
-      }
-    } else if (BITS == 16) {
-      acc.add_one(w * 2 + 0, sq_decode<BITS>((float)(int16_t)(word & 0xFFFFu), scale, emin, mean));
-      acc.add_one(w * 2 + 1, sq_decode<BITS>((float)(int16_t)(word >> 16), scale, emin, mean));
-    } else if (BITS == 8) {
-#pragma unroll
-      for (int b = 0; b < 4; ++b) {
-        uint32_t byte = (word >> (8 * b)) & 0xFFu;
-        float c = code_kind == CODE_I8 ? (float)(int8_t)byte : (float)byte;
-        acc.add_one(w * 4 + b, sq_decode<BITS>(c, scale, emin, mean));
-      }
-    } else {  // 1-, 2- or 4-bit arithmetic decode
-      constexpr int B = (BITS == 1 || BITS == 2 || BITS == 4) ? BITS : 4;
-      constexpr int PER_WORD = 32 / B;
-#pragma unroll
-      for (int i = 0; i < PER_WORD; ++i)
-        acc.add_one(w * PER_WORD + i, sq_decode<BITS>((float)((word >> (B * i)) & ((1u << B) - 1u)), scale, emin, mean));
-    }
-  }
-}
 
 // U = neighbours held in registers per destination row (rows with more take extra, unpipelined rounds).
 // PEER: the table is row-sharded over the GPUs of one NVSwitch box and every shard is mapped into this process;
 // a neighbour's row is read from its owner's HBM with an ordinary load over NVLink (no collective, no staging copy).
-template <int BITS, int VEC, int U, typename IdxT, int DEC, bool PEER = false, bool ASYNC = false>
-__global__ void __launch_bounds__(SqCta<BITS, DEC, ASYNC>::kThreads, SqCta<BITS, DEC, ASYNC>::kCtasPerSm)
+template <int BITS, int VEC, int U, typename IdxT, int DEC, bool PEER = false>
+__global__ void __launch_bounds__(SqCta<BITS, DEC>::kThreads, SqCta<BITS, DEC>::kCtasPerSm)
 sq_spmm_kernel(const SqParams p) {
-  constexpr bool ALIGNED = SqCta<BITS, DEC, ASYNC>::kAligned;
+  constexpr bool ALIGNED = SqCta<BITS, DEC>::kAligned;
   constexpr int EPL = BITS == 16 ? VEC / 2 : VEC * 8 / BITS;  // output columns per lane
   constexpr bool PACKED = DEC == DEC_LUT && BITS <= 4;
   extern __shared__ __align__(16) unsigned char smem_dyn[];
@@ -277,24 +147,7 @@ sq_spmm_kernel(const SqParams p) {
   // One set of id registers is enough: a stage first issues the row loads that consume them, then
   // overwrites them with the ids of the row after (the hardware scoreboard orders the two).
   uint32_t nidx[U];
-  VecLoad<VEC> data[ASYNC ? 1 : 2][ASYNC ? 1 : U];
-  // ASYNC: shared-window address of this lane's bytes of neighbour slot 0, stage 0, in its warp's ring
-  constexpr uint32_t kSlotBytes = 32 * VEC, kStageBytes = U * kSlotBytes;
-  const uint32_t ring = ASYNC ? (uint32_t)__cvta_generic_to_shared(smem_raw + p.ring_offset) + (threadIdx.x >> 5) * (2 * kStageBytes) +
-                                    (uint32_t)lane * VEC
-                              : 0u;
-  // fetch (or zero) this lane's bytes of neighbour slot u of the row whose ids are in nidx, into `stage`
-  auto fetch_async = [&](int stage, int u, bool have) {
-    const uint32_t dst = ring + (uint32_t)stage * kStageBytes + (uint32_t)u * kSlotBytes;
-    if (have) {
-      if (VEC == 8) cp_async_bytes8(dst, row_ptr(nidx[u]));
-      else cp_async_bytes4(dst, row_ptr(nidx[u]));
-    } else if (VEC == 8) {
-      asm volatile("st.shared.b64 [%0], %1;" ::"r"(dst), "l"(0ull) : "memory");
-    } else {
-      asm volatile("st.shared.b32 [%0], %1;" ::"r"(dst), "r"(0u) : "memory");
-    }
-  };
+  VecLoad<VEC> data[2][U];
   auto prime = [&]() {
     if (d < n_dst && lane_active) { int64_t b = (int64_t)indptr[d]; degA = (int)((int64_t)indptr[d + 1] - b); idsA = indices + b; }
     if (d + istride < n_dst && lane_active) {
@@ -305,17 +158,10 @@ sq_spmm_kernel(const SqParams p) {
     }
 #pragma unroll
     for (int u = 0; u < U; ++u) nidx[u] = u < degA ? (uint32_t)idsA[u] : 0u;
-    if (ASYNC) {
 #pragma unroll
-      for (int u = 0; u < U; ++u) fetch_async(0, u, u < degA);
-      asm volatile("cp.async.commit_group;" ::: "memory");
-    } else {
-#pragma unroll
-      for (int u = 0; u < U; ++u) {
-#pragma unroll
-        for (int w = 0; w < VEC / 4; ++w) data[0][u].w[w] = 0u;
-        if (u < degA) data[0][u].load(row_ptr(nidx[u]));
-      }
+    for (int u = 0; u < U; ++u) {
+      data[0][u].zero();
+      if (u < degA) data[0][u].load(row_ptr(nidx[u]));
     }
 #pragma unroll
     for (int u = 0; u < U; ++u) nidx[u] = u < degB ? (uint32_t)idsB[u] : 0u;
@@ -323,41 +169,9 @@ sq_spmm_kernel(const SqParams p) {
   if (PRIME_EARLY) prime();
   uint32_t lane_off = 0;
   if (DEC == DEC_LUT) {
-    // Copy c of a slab serves the lanes with lane % COPIES == c, whose lane_g is c % G.
-    // Phase 1 decodes each code value once per distinct codebook row (2^B * min(G, COPIES) exp2f in all);
-    // phase 2 assembles the byte-indexed, bank-replicated table from those values, 16 bytes per store.
     using L = Lut<BITS>;
-    float* base = reinterpret_cast<float*>(smem_raw + L::TABLE_BYTES + 256);  // [n_rows][NCODE], after the zero slab
-    const int n_rows = G < L::COPIES ? G : L::COPIES;
-    for (int i = threadIdx.x; i < n_rows * L::NCODE; i += blockDim.x) {
-      int code = i & (L::NCODE - 1), g = i / L::NCODE;
-      int row = (g * EPL) / p.column_slice;
-      if (row >= p.n_cb) row = p.n_cb - 1;
-      float e0 = __ldg(p.codebooks + row * kCodebookDim + 2), e1 = __ldg(p.codebooks + row * kCodebookDim + 3);
-      float m = __ldg(p.codebooks + row * kCodebookDim + 4);
-      float c = (L::B == 8 && p.code_kind == CODE_I8) ? (float)(int8_t)code : (float)code;
-      base[i] = sq_decode<BITS>(c, sq_scale<BITS>(e0, e1), e0, m);
-    }
-    __syncthreads();
-    constexpr int SPAN = L::HALVES == 2 ? 128 : 256;
-    for (int i = threadIdx.x; i < 256 * 16; i += blockDim.x) {
-      const int byte = i >> 4, j = i & 15;
-      float v[4];
-#pragma unroll
-      for (int t = 0; t < 4; ++t) {
-        const int o = 16 * j + 4 * t;  // byte offset inside the slab
-        const int h = L::HALVES == 2 ? o / 128 : 0;
-        const int oo = o % SPAN;
-        const int copy = oo / L::COPY_BYTES;
-        const int f = (oo % L::COPY_BYTES) / 4 + 4 * h;
-        const int g = copy & (n_rows - 1);
-        v[t] = copy < L::COPIES ? base[g * L::NCODE + ((byte >> (L::B * f)) & (L::NCODE - 1))] : 0.0f;
-      }
-      *reinterpret_cast<float4*>(smem_raw + i * 16) = make_float4(v[0], v[1], v[2], v[3]);
-    }
-    // zero slab used by neighbour slots beyond a row's degree (its address is lane_off + TABLE_BYTES with byte 0)
-    for (int i = threadIdx.x; i < 64; i += blockDim.x) reinterpret_cast<float*>(smem_raw + L::TABLE_BYTES)[i] = 0.0f;
-    __syncthreads();
+    build_sq_table<BITS, EPL>(smem_raw, reinterpret_cast<float*>(smem_raw + L::TABLE_BYTES + 256), p.codebooks, p.n_cb, p.column_slice,
+                              G, p.code_kind, (int)threadIdx.x, (int)blockDim.x, [] { __syncthreads(); });
     lane_off = L::lane_offset(lane);
     if (ALIGNED) lane_off |= (uint32_t)__cvta_generic_to_shared(smem_raw);  // low 16 bits of the base are zero
   }
@@ -378,17 +192,10 @@ sq_spmm_kernel(const SqParams p) {
     for (int P = 0; P < 2; ++P) {
       if (row_base < n_dst) {  // warp uniform
         // (1) code rows of the next destination row -> data[P^1]
-        if (ASYNC) {
 #pragma unroll
-          for (int u = 0; u < U; ++u) fetch_async(P ^ 1, u, u < degB);
-          asm volatile("cp.async.commit_group;" ::: "memory");
-        } else {
-#pragma unroll
-          for (int u = 0; u < U; ++u) {
-#pragma unroll
-            for (int w = 0; w < VEC / 4; ++w) data[P ^ 1][u].w[w] = 0u;
-            if (u < degB) data[P ^ 1][u].load(row_ptr(nidx[u]));
-          }
+        for (int u = 0; u < U; ++u) {
+          data[P ^ 1][u].zero();
+          if (u < degB) data[P ^ 1][u].load(row_ptr(nidx[u]));
         }
         // (2) neighbour ids of the row after it
 #pragma unroll
@@ -406,17 +213,10 @@ sq_spmm_kernel(const SqParams p) {
         Acc<EPL, PACKED> acc;
         acc.clear();
         const int umax = __reduce_max_sync(0xffffffffu, degA < U ? degA : U);  // slots any row of the warp uses
-        if (ASYNC) asm volatile("cp.async.wait_group 1;" ::: "memory");  // everything but the copies issued in (1) has landed
 #pragma unroll
         for (int u = 0; u < U; ++u) {
           if (u < umax) {  // warp uniform
-            VecLoad<VEC> landed;
-            if (ASYNC) {  // this lane reads back exactly the bytes it copied (or zeroed)
-              const uint32_t src = ring + (uint32_t)P * kStageBytes + (uint32_t)u * kSlotBytes;
-              if (VEC == 8) asm volatile("ld.shared.v2.b32 {%0, %1}, [%2];" : "=r"(landed.w[0]), "=r"(landed.w[VEC / 4 - 1]) : "r"(src));
-              else asm volatile("ld.shared.b32 %0, [%1];" : "=r"(landed.w[0]) : "r"(src));
-            }
-            const VecLoad<VEC>& row = ASYNC ? landed : data[ASYNC ? 0 : P][ASYNC ? 0 : u];
+            const VecLoad<VEC>& row = data[P][u];
             if (DEC == DEC_LUT) {
               sq_accumulate<BITS, VEC, DEC, ALIGNED>(acc, row, table, u < degA ? lane_off : lane_off_zero, p.code_kind, scale, emin, mean);
             } else if (u < degA) {
@@ -438,51 +238,9 @@ sq_spmm_kernel(const SqParams p) {
         // (5) mean / dropout / store
         const bool have_row = d < n_dst && lane_active;
         if (p.staged) {
-          constexpr int Q = EPL / 4;                                    // chunks (float4) per lane
-          constexpr int LQ = Q >= 8 ? 3 : Q == 4 ? 2 : Q == 2 ? 1 : 0;  // low chunk-index bits that only depend on q
-          const int NC = p.feat_dim >> 2;                               // chunks per output row
-          const int NCP = Q << p.logG;                                  // row stride of the staging area (>= NC)
-          // ASYNC kernels stage in the ring stage that was just decoded (it is free until the copies of the row after next)
-          float4* stage = ASYNC ? reinterpret_cast<float4*>(smem_raw + p.ring_offset + (threadIdx.x >> 5) * (2 * kStageBytes) + P * kStageBytes)
-                                : reinterpret_cast<float4*>(smem_raw + p.stage_offset) + (threadIdx.x >> 5) * (32 * Q);
-          static_assert(!ASYNC || 32 * EPL * 4 <= (int)kStageBytes, "a ring stage must hold a warp's output rows");
-          // chunk c of a row is kept at c ^ m, m = the lane bits that the low bits of c do not already spread
-          // over the banks; m only touches the q part of the index, so a lane stays inside its own Q chunks
-          if (have_row) {
-            const int m = ((lane & 7) >> (3 - LQ)) & ((1 << LQ) - 1);
-#pragma unroll
-            for (int q = 0; q < Q; ++q) {
-              const int c4 = lane_g * Q + q;
-              if (c4 < NC) stage[sub * NCP + (c4 ^ m)] = acc.chunk(q);
-            }
-          }
-          // reciprocal of the row's degree, once per lane group (0 marks "do not divide")
-          float my_rcp = 0.0f;
-          if (p.reduce == F2C_MEAN && degA > 1) my_rcp = 1.0f / (float)degA;
-          __syncwarp();
-          for (int row = 0; row < rows_per_warp; ++row) {
-            const int64_t dr = row_base + row;
-            if (dr >= n_dst) break;
-            const float rcp = __shfl_sync(0xffffffffu, my_rcp, row << p.logG);
-            const float deg = (float)__shfl_sync(0xffffffffu, degA, row << p.logG);
-            for (int c = lane; c < NC; c += 32) {
-              const int writer = (row << p.logG) + c / Q;  // lane that produced chunk c
-              const int m = ((writer & 7) >> (3 - LQ)) & ((1 << LQ) - 1);
-              float4 v = stage[row * NCP + (c ^ m)];
-              if (rcp != 0.0f) {
-                if (div_safe) {
-                  v.x = div_exact_fast(v.x, deg, rcp); v.y = div_exact_fast(v.y, deg, rcp);
-                  v.z = div_exact_fast(v.z, deg, rcp); v.w = div_exact_fast(v.w, deg, rcp);
-                } else {
-                  v.x = div_exact(v.x, deg, rcp); v.y = div_exact(v.y, deg, rcp);
-                  v.z = div_exact(v.z, deg, rcp); v.w = div_exact(v.w, deg, rcp);
-                }
-              }
-              if (p.drop.enabled) v = dropout_apply4(v, (uint64_t)(dr * p.feat_dim + 4 * c), p.drop);
-              stg_cs_f4(p.out + dr * p.feat_dim + 4 * c, v);
-            }
-          }
-          __syncwarp();
+          float4* stage = reinterpret_cast<float4*>(smem_raw + p.stage_offset) + (threadIdx.x >> 5) * (32 * (EPL / 4));
+          sq_store_rows<EPL>(acc, stage, lane, p.logG, degA, have_row, (int64_t)row_base, (int64_t)(n_dst - row_base), p.feat_dim,
+                             p.reduce, div_safe, p.drop, p.out);
         } else if (have_row) {
           float* orow = p.out + (int64_t)d * p.feat_dim;
           const float deg = degA == 0 ? 1.0f : (float)degA;
@@ -560,9 +318,16 @@ __global__ void __launch_bounds__(256) sq_spmm_generic_kernel(const void* __rest
 
 static int ilog2(int v) { int l = 0; while ((1 << l) < v) ++l; return l; }
 
-template <int BITS, int VEC, int U, typename IdxT, int DEC, bool PEER = false, bool ASYNC = false>
+// Resident CTAs per SM of one kernel instance at one shared-memory footprint, queried once per device.
+struct ResidentCache {
+  std::mutex m;
+  int value[64] = {};
+  size_t smem[64] = {};
+};
+
+template <int BITS, int VEC, int U, typename IdxT, int DEC, bool PEER = false>
 static int launch_fast(SqParams p, bool vec_store, cudaStream_t st) {
-  auto kern = sq_spmm_kernel<BITS, VEC, U, IdxT, DEC, PEER, ASYNC>;
+  auto kern = sq_spmm_kernel<BITS, VEC, U, IdxT, DEC, PEER>;
   constexpr int EPL = BITS == 16 ? VEC / 2 : VEC * 8 / BITS;
   // decode table (64 KB) + the decoded code values of each distinct codebook row
   size_t smem = 0;
@@ -571,86 +336,91 @@ static int launch_fast(SqParams p, bool vec_store, cudaStream_t st) {
     int n_rows = (1 << p.logG) < L::COPIES ? (1 << p.logG) : L::COPIES;
     smem = L::TABLE_BYTES + 256 + (size_t)n_rows * L::NCODE * sizeof(float);
   }
-  constexpr int kThreads = SqCta<BITS, DEC, ASYNC>::kThreads;
+  constexpr int kThreads = SqCta<BITS, DEC>::kThreads;
   constexpr int kWarpsPerCta = kThreads / 32;
   // staging area for coalesced output: warps x 32 lanes x EPL floats
   p.staged = 0;
   p.stage_offset = (int)smem;
   if (vec_store && EPL >= 4) {
     p.staged = 1;
-    if (!ASYNC) smem += (size_t)kWarpsPerCta * 32 * EPL * sizeof(float);  // (ASYNC kernels stage inside their rings)
+    smem += (size_t)kWarpsPerCta * 32 * EPL * sizeof(float);
   }
-  p.ring_offset = (int)smem;
-  if (ASYNC) smem += (size_t)kWarpsPerCta * 2 * U * 32 * VEC;  // two stages of U neighbour rows per warp
-  if (SqCta<BITS, DEC, ASYNC>::kAligned) smem += 65536;  // slack for the 64 KB alignment of the table inside the shared window
+  if (SqCta<BITS, DEC>::kAligned) smem += 65536;  // slack for the 64 KB alignment of the table inside the shared window
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return set_error(F2C_ERR_CUDA, "sq_decompress_spmm_csr: %s", cudaGetErrorString(e));
   }
-  // persistent grid: exactly as many CTAs as the device keeps resident (queried when the footprint changes)
-  static int resident = 0;
-  static size_t resident_smem = ~(size_t)0;
-  if (resident == 0 || resident_smem != smem) {
-    int n = 0;
-    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kern, kThreads, smem) != cudaSuccess || n < 1) n = 1;
-    resident = n;
-    resident_smem = smem;
+  // persistent grid: exactly as many CTAs as the device keeps resident
+  static ResidentCache cache;
+  int dev = 0, resident = 1;
+  if (cudaGetDevice(&dev) != cudaSuccess) dev = 0;
+  const int sms = sm_count(dev);
+  {
+    std::lock_guard<std::mutex> lock(cache.m);
+    const int slot = dev & 63;
+    if (cache.value[slot] == 0 || cache.smem[slot] != smem) {
+      int n = 0;
+      if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kern, kThreads, smem) != cudaSuccess || n < 1) n = 1;
+      cache.value[slot] = n;
+      cache.smem[slot] = smem;
+    }
+    resident = cache.value[slot];
   }
-  int ctas_per_sm = g_tune_ctas_per_sm > 0 ? g_tune_ctas_per_sm : resident;
   int rows_per_cta = kWarpsPerCta * (32 >> p.logG);
   int64_t grid = ceil_div(p.n_dst, rows_per_cta);
-  if (grid > (int64_t)kSmCount * ctas_per_sm) grid = (int64_t)kSmCount * ctas_per_sm;
+  if (grid > (int64_t)sms * resident) grid = (int64_t)sms * resident;
   kern<<<(unsigned)grid, kThreads, smem, st>>>(p);
   return check_launch("sq_decompress_spmm_csr");
 }
-
-template <int BITS, int VEC, typename IdxT, int DEC>
-static int pick_u(const SqParams& p, bool vec_store, cudaStream_t st) {
-  // neighbours held in registers per destination row; measured on B200 (config-2 block, fan-out 12): 8 is fastest
-  // for 2- and 4-bit codes (4 bit: 42-43 us against 46 with 12 - the four remaining neighbours take the unpipelined
-  // round, but 16 fewer live registers help more; 2 bit: a tie; 4 per row is slower again), 12 for 1- and 8-bit codes
-  int u = g_tune_u > 0 ? g_tune_u : (BITS == 2 || BITS == 4 ? 8 : 12);
-  if (u >= 16) return launch_fast<BITS, VEC, 16, IdxT, DEC>(p, vec_store, st);
-  if (u >= 12) return launch_fast<BITS, VEC, 12, IdxT, DEC>(p, vec_store, st);
-  return launch_fast<BITS, VEC, 8, IdxT, DEC>(p, vec_store, st);
-}
-
-int g_tune_async = 0;  // f2c_set_tuning key 5: 1 = cp.async ring kernels for 4- and 8-bit table decode
 
 template <int BITS, typename IdxT>
 static int dispatch_fast(const SqParams& p, int vec, bool lut, bool vec_store, cudaStream_t st) {
   constexpr bool CAN_LUT = BITS <= 8;
   constexpr bool CAN_8 = BITS > 2;  // 1/2-bit: 4 bytes per lane already are 32 / 16 columns
-  if constexpr (BITS == 4 || BITS == 8) if (lut && vec == 8 && g_tune_async != 0) {
-    if (g_tune_u > 0 && g_tune_u < 12) return launch_fast<BITS, 8, 8, IdxT, DEC_LUT, false, true>(p, vec_store, st);
-    return launch_fast<BITS, 8, 12, IdxT, DEC_LUT, false, true>(p, vec_store, st);
-  }
+  // neighbours held in registers per destination row; measured on B200 (config-2 block, fan-out 12): 8 is fastest
+  // for 2- and 4-bit codes (4 bit: 42-43 us against 46 with 12 - the four remaining neighbours take the unpipelined
+  // round, but 16 fewer live registers help more; 2 bit: a tie; 4 per row is slower again), 12 for 1- and 8-bit codes
+  constexpr int U = (BITS == 2 || BITS == 4) ? 8 : 12;
   if constexpr (CAN_LUT) if (lut) {
-    if constexpr (CAN_8) if (vec == 8) return pick_u<BITS, 8, IdxT, DEC_LUT>(p, vec_store, st);
-    return pick_u<BITS, 4, IdxT, DEC_LUT>(p, vec_store, st);
+    if constexpr (CAN_8) if (vec == 8) return launch_fast<BITS, 8, U, IdxT, DEC_LUT>(p, vec_store, st);
+    return launch_fast<BITS, 4, U, IdxT, DEC_LUT>(p, vec_store, st);
   }
-  if constexpr (CAN_8) if (vec == 8) return pick_u<BITS, 8, IdxT, DEC_ARITH>(p, vec_store, st);
-  return pick_u<BITS, 4, IdxT, DEC_ARITH>(p, vec_store, st);
+  if constexpr (CAN_8) if (vec == 8) return launch_fast<BITS, 8, U, IdxT, DEC_ARITH>(p, vec_store, st);
+  return launch_fast<BITS, 4, U, IdxT, DEC_ARITH>(p, vec_store, st);
 }
 
 template <int BITS, typename IdxT>
 static int launch_sq_spmm(const void* codes, int code_dtype, const float* codebooks, int64_t n_cb, const void* indptr,
                           const void* indices, float* out, int64_t n_dst, int64_t n_src, int64_t src_dim, int64_t D, int64_t cs,
-                          int reduce, const DropoutArgs& drop, cudaStream_t st, const PeerInfo* peer = nullptr) {
+                          int reduce, const DropoutArgs& drop, int variant, cudaStream_t st, const PeerInfo* peer = nullptr) {
   if (n_dst == 0 || D == 0) return F2C_OK;
+  const char* op = peer ? "sq_decompress_spmm_csr_peer" : "sq_decompress_spmm_csr";
+  // ---- streamed kernel (producer warps + shared-memory ring).  Measured on B200 (2,449,029-row table, outermost block
+  //      of 1024 seeds x fan-out 12,12,12, cold L2): 2-bit codes 36.9 us against 41.9 us for the register-prefetch kernel;
+  //      1 bit 41-43 against 41, 4 bit 49.5 against 43.7, 8 bit 61.4 against 49.2 - staging the rows costs shared-memory
+  //      wavefronts (7.0 M against 4.5 M at 4 bits) that the table decode needs itself, so only the 2-bit shape, whose
+  //      rows are cheap to stage and whose prefetch kernel is the most latency-bound, gains.
+  const bool stream_by_default = BITS == 2 && peer == nullptr;
+  if ((variant == F2C_KERNEL_AUTO && stream_by_default) || variant == F2C_KERNEL_STREAM) {
+    bool served = false;
+    int rc = launch_sq_stream(BITS, sizeof(IdxT) == 4 ? F2C_I32 : F2C_I64, codes, code_dtype, codebooks, n_cb, indptr, indices, out, n_dst,
+                              n_src, src_dim, D, cs, reduce, drop, st, peer ? peer->shard : nullptr, peer ? peer->world : 0,
+                              peer ? peer->rows_per_shard : 0, &served);
+    if (served || rc) return rc;
+    if (variant == F2C_KERNEL_STREAM) return set_error(F2C_ERR_UNSUPPORTED, "%s: shape not served by the streamed kernel", op);
+  }
   const int code_bytes = dtype_size(code_dtype);
   const int64_t row_bytes = src_dim * code_bytes;
-  // ---- can the vector kernel serve this shape? ----
+  // ---- can the register-prefetch kernel serve this shape? ----
   // bytes per lane per row: at most two words (two register sets of U rows are live) and at most 32 columns;
   // measured on B200: 8 bytes for 4/8/16-bit codes, 4 bytes for 1/2-bit codes
   constexpr int VMAX = BITS <= 2 ? 4 : 8;
   int vec = 0;
   for (int v = VMAX; v >= 4; v >>= 1)
     if (row_bytes % v == 0 && aligned(codes, v) && row_bytes <= 32 * v) { vec = v; break; }
-  if (g_tune_vec > 0 && vec > g_tune_vec && row_bytes <= 32 * g_tune_vec) vec = g_tune_vec;
   const bool natural_dtype = BITS < 8 || (BITS == 8 && code_bytes == 1) || (BITS == 16 && code_bytes == 2);
   // the vector kernel keeps neighbour ids in 32-bit registers
-  bool fast = vec != 0 && natural_dtype && n_src < (1ll << 32) && n_dst < (1ll << 30);
+  bool fast = vec != 0 && natural_dtype && n_src < (1ll << 32) && n_dst < (1ll << 30) && variant != F2C_KERNEL_GENERAL;
   int epl = 0, G = 0;
   if (fast) {
     epl = BITS == 16 ? vec / 2 : vec * 8 / BITS;
@@ -665,29 +435,30 @@ static int launch_sq_spmm(const void* codes, int code_dtype, const float* codebo
     p.reduce = reduce; p.staged = 0; p.stage_offset = 0; p.drop = drop;
     // table copies are shared by lanes l and l + COPIES: they must own the same columns
     int copies = BITS >= 4 ? 32 : BITS == 2 ? 16 : 8;
-    bool lut = (n_cb == 1 || copies % G == 0) && g_tune_lut != 0;
+    bool lut = (n_cb == 1 || copies % G == 0) && variant != F2C_KERNEL_PREFETCH_ARITH;
     if (peer != nullptr) {
       for (int r = 0; r < 8; ++r) p.shard[r] = (const uint8_t*)peer->shard[r < peer->world ? r : 0];
       p.rows_per_shard = (uint32_t)peer->rows_per_shard;
       p.shard_magic = ~0ull / (unsigned long long)peer->rows_per_shard + 1ull;
       constexpr int DEC = BITS <= 8 ? DEC_LUT : DEC_ARITH;
       if (vec != VMAX || (BITS <= 8 && !lut))
-        return set_error(F2C_ERR_UNSUPPORTED, "sq_decompress_spmm_csr_peer: shape or codebook layout not served by the peer kernel");
+        return set_error(F2C_ERR_UNSUPPORTED, "%s: shape or codebook layout not served by the peer kernel", op);
       return launch_fast<BITS, VMAX, 12, IdxT, DEC, true>(p, D % 4 == 0 && aligned(out, 16), st);
     }
     return dispatch_fast<BITS, IdxT>(p, vec, lut, D % 4 == 0 && aligned(out, 16), st);
   }
-  if (peer != nullptr)
-    return set_error(F2C_ERR_UNSUPPORTED, "sq_decompress_spmm_csr_peer: shape not served by the peer kernel");
+  if (peer != nullptr) return set_error(F2C_ERR_UNSUPPORTED, "%s: shape not served by the peer kernel", op);
+  if (variant == F2C_KERNEL_PREFETCH || variant == F2C_KERNEL_PREFETCH_ARITH)
+    return set_error(F2C_ERR_UNSUPPORTED, "%s: shape not served by the register-prefetch kernel", op);
   int64_t blocks = ceil_div(n_dst, 8);
-  if (blocks > kSmCount * 32) blocks = kSmCount * 32;
+  if (blocks > current_sm_count() * 32) blocks = current_sm_count() * 32;
 #define F2C_GEN(T) sq_spmm_generic_kernel<BITS, T, IdxT><<<(unsigned)blocks, 256, 0, st>>>( \
       codes, codebooks, (const IdxT*)indptr, (const IdxT*)indices, out, n_dst, src_dim, (int)D, (int)cs, reduce, drop)
   if (code_dtype == F2C_I8) F2C_GEN(int8_t);
   else if (code_dtype == F2C_U8) F2C_GEN(uint8_t);
   else F2C_GEN(int16_t);
 #undef F2C_GEN
-  return check_launch("sq_decompress_spmm_csr");
+  return check_launch(op);
 }
 
 }  // namespace f2c
@@ -710,13 +481,14 @@ extern "C" int f2c_sq_spmm_csr(const void* codes, int code_dtype, const float* c
               "%s: column_slice (%lld) must be a multiple of %d for %d-bit codes", op, (long long)column_slice, 8 / bits, bits);
   F2C_REQUIRE(n_dst * feat_dim == 0 || (indptr && out && codebooks), F2C_ERR_INVALID, "%s: null pointer", op);
   DropoutArgs drop = make_dropout(epilogue);
+  const int variant = kernel_variant(epilogue);
   cudaStream_t st = (cudaStream_t)stream;
 #define F2C_SQ(B)                                                                                                   \
   return index_dtype == F2C_I32                                                                                     \
              ? launch_sq_spmm<B, int32_t>(codes, code_dtype, codebooks, n_codebooks, indptr, indices, out, n_dst,   \
-                                          n_src, src_dim, feat_dim, column_slice, reduce, drop, st)                \
+                                          n_src, src_dim, feat_dim, column_slice, reduce, drop, variant, st)                \
              : launch_sq_spmm<B, int64_t>(codes, code_dtype, codebooks, n_codebooks, indptr, indices, out, n_dst,   \
-                                          n_src, src_dim, feat_dim, column_slice, reduce, drop, st)
+                                          n_src, src_dim, feat_dim, column_slice, reduce, drop, variant, st)
   switch (bits) {
     case 1: F2C_SQ(1);
     case 2: F2C_SQ(2);
@@ -782,13 +554,14 @@ extern "C" int f2c_sq_spmm_csr_peer(const void* const* shard_ptrs_host, int worl
   peer.world = world;
   peer.rows_per_shard = rows_per_shard;
   DropoutArgs drop = make_dropout(epilogue);
+  const int variant = kernel_variant(epilogue);
   cudaStream_t st = (cudaStream_t)stream;
 #define F2C_SQP(B)                                                                                                       \
   return index_dtype == F2C_I32                                                                                          \
              ? launch_sq_spmm<B, int32_t>(peer.shard[0], code_dtype, codebooks, n_codebooks, indptr, indices, out, n_dst, \
-                                          n_src, src_dim, feat_dim, column_slice, reduce, drop, st, &peer)              \
+                                          n_src, src_dim, feat_dim, column_slice, reduce, drop, variant, st, &peer)              \
              : launch_sq_spmm<B, int64_t>(peer.shard[0], code_dtype, codebooks, n_codebooks, indptr, indices, out, n_dst, \
-                                          n_src, src_dim, feat_dim, column_slice, reduce, drop, st, &peer)
+                                          n_src, src_dim, feat_dim, column_slice, reduce, drop, variant, st, &peer)
   switch (bits) {
     case 1: F2C_SQP(1);
     case 2: F2C_SQP(2);
@@ -797,21 +570,4 @@ extern "C" int f2c_sq_spmm_csr_peer(const void* const* shard_ptrs_host, int worl
     default: F2C_SQP(16);
   }
 #undef F2C_SQP
-}
-
-// Experiment knobs of the fused SQ kernel (no counterpart in the reference).  key 0: bytes per lane per
-// row load (4/8), 1: neighbours held in registers per row (8/12/16), 2: table decode on/off, 3: CTAs per
-// SM, 4: pipelined VQ / two-level kernel on (1) / off (0), 5: cp.async ring variant of the 4- / 8-bit kernels on (1) / off (0).  value 0 (key 2: -1, key 4: 1) restores the built-in choice.
-extern "C" int f2c_set_tuning(int key, int value) {
-  switch (key) {
-    case 0: g_tune_vec = value; break;
-    case 1: g_tune_u = value; break;
-    case 2: g_tune_lut = value; break;
-    case 3: g_tune_ctas_per_sm = value; break;
-    case 4: g_tune_vq_fast = value; break;
-    case 5: g_tune_async = value; break;
-    case 10: g_kmeans_force_exact = value; break;
-    default: return set_error(F2C_ERR_INVALID, "set_tuning: unknown key %d", key);
-  }
-  return F2C_OK;
 }

@@ -336,12 +336,14 @@ static int launch_rows(const VqParams& p, int roww, dim3 grid, size_t smem, cuda
 
 }  // namespace vqf
 
-int g_tune_vq_fast = 1;  // 0 sends every shape to the general kernels (experiments and tests)
+int launch_vq_stream(VqParams& p, int hot_bits, int index_dtype, cudaStream_t st, const char* op, bool* served);
 
-int launch_vq_fast(VqParams& p, int hot_bits, int index_dtype, cudaStream_t st, const char* op, bool* served) {
+int launch_vq_fast(VqParams& p, int hot_bits, int index_dtype, int variant, cudaStream_t st, const char* op, bool* served) {
   using namespace vqf;
   *served = false;
-  if (!g_tune_vq_fast) return F2C_OK;
+  // The streamed kernels are selectable but not the default here: on B200 (same block as above) VQ 16 x 8 ties (41-43 us),
+  // VQ 4 x 32 is 45-49 us against 35 us and the two-level op 130-140 us against 64 us for this file's kernel.
+  if (variant == F2C_KERNEL_STREAM) return launch_vq_stream(p, hot_bits, index_dtype, st, op, served);
   const int cs = p.cs;
   const int64_t row_bytes = p.n_cb;  // uint8 codes
   if (p.code_kind != 0 || p.K > 256 || p.n_dst >= (1ll << 30)) return F2C_OK;
@@ -370,7 +372,7 @@ int launch_vq_fast(VqParams& p, int hot_bits, int index_dtype, cudaStream_t st, 
   p.fast_stride = stride;
   p.fast_cb_bytes = (int)cb_bytes(per_part);
   const int parts = (int)ceil_div(p.n_cb, per_part);
-  int64_t grid_x = kSmCount / parts;
+  int64_t grid_x = current_sm_count() / parts;
   if (grid_x < 1) grid_x = 1;
   const int64_t need = ceil_div(p.n_dst, kWarps);
   if (grid_x > need) grid_x = need;

@@ -211,7 +211,7 @@ static int launch_vq(VqParams& p, cudaStream_t st, const char* op) {
   int64_t rows_per_cta = kVqThreads / 32;
   int64_t grid_x = ceil_div(p.n_dst, rows_per_cta);
   int ctas_per_sm = 1;  // 1024 threads at <= 64 registers fill the register file
-  int64_t cap = (int64_t)kSmCount * ctas_per_sm / parts;
+  int64_t cap = (int64_t)current_sm_count() * ctas_per_sm / parts;
   if (cap < 1) cap = 1;
   if (grid_x > cap) grid_x = cap;
   dim3 grid((unsigned)grid_x, (unsigned)parts);
@@ -251,14 +251,18 @@ extern "C" int f2c_vq_spmm_csr(const void* codes, int code_dtype, const float* c
   bool fast = column_slice % 4 == 0 && aligned(codebooks, 16);
   if (!fast) {
     int64_t blocks = ceil_div(n_dst, 8);
-    if (blocks > kSmCount * 32) blocks = kSmCount * 32;
+    if (blocks > current_sm_count() * 32) blocks = current_sm_count() * 32;
     if (index_dtype == F2C_I32) vq_spmm_generic_kernel<int32_t><<<(unsigned)blocks, 256, 0, st>>>(p);
     else vq_spmm_generic_kernel<int64_t><<<(unsigned)blocks, 256, 0, st>>>(p);
     return check_launch(op);
   }
+  const int variant = kernel_variant(epilogue);
   bool served = false;
-  rc = launch_vq_fast(p, 0, index_dtype, st, op, &served);
-  if (served || rc) return rc;
+  if (variant != F2C_KERNEL_GENERAL) {
+    rc = launch_vq_fast(p, 0, index_dtype, variant, st, op, &served);
+    if (served || rc) return rc;
+    if (variant != F2C_KERNEL_AUTO) return set_error(F2C_ERR_UNSUPPORTED, "%s: shape not served by the requested kernel family", op);
+  }
   return index_dtype == F2C_I32 ? launch_vq<0, int32_t>(p, st, op) : launch_vq<0, int64_t>(p, st, op);
 }
 
@@ -296,9 +300,13 @@ extern "C" int f2c_hybrid_spmm_csr(const void* sq_codes, int sq_dtype, const flo
   p.sq_codes = (const uint8_t*)sq_codes; p.sq_codebooks = sq_codebooks; p.slot = slot; p.sq_row_bytes = sq_row_bytes;
   p.sq_cs = (int)sq_column_slice; p.sq_n_cb = (int)sq_n_codebooks; p.sq_signed = sq_dtype == F2C_I8;
   cudaStream_t st = (cudaStream_t)stream;
+  const int variant = kernel_variant(epilogue);
   bool served = false;
-  rc = launch_vq_fast(p, bits, index_dtype, st, op, &served);
-  if (served || rc) return rc;
+  if (variant != F2C_KERNEL_GENERAL) {
+    rc = launch_vq_fast(p, bits, index_dtype, variant, st, op, &served);
+    if (served || rc) return rc;
+    if (variant != F2C_KERNEL_AUTO) return set_error(F2C_ERR_UNSUPPORTED, "%s: shape not served by the requested kernel family", op);
+  }
 #define F2C_HY(B) \
   return index_dtype == F2C_I32 ? launch_vq<B, int32_t>(p, st, op) : launch_vq<B, int64_t>(p, st, op)
   switch (bits) {

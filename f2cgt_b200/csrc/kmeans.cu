@@ -141,7 +141,7 @@ static int launch_thread_assign(const float* x, const float* y, int64_t* labels,
   while ((size_t)kc * (DMAX + 1) * sizeof(float) > budget) kc = (kc + 1) / 2;
   size_t smem = (size_t)kc * (DMAX + 1) * sizeof(float);
   unsigned grid = (unsigned)ceil_div(n, 256);
-  if (count_dev != nullptr && grid > 2u * kSmCount) grid = 2u * kSmCount;  // the list is short: a small grid walks it
+  if (count_dev != nullptr && grid > 2u * current_sm_count()) grid = 2u * current_sm_count();  // the list is short: a small grid walks it
   cudaError_t e;
   if (metric == F2C_COSINE) {
     auto kern = kmeans_thread_kernel<DMAX, F2C_COSINE>;
@@ -167,7 +167,7 @@ int kmeans_assign_exact(const float* x, const float* y, int64_t* labels, const i
   if (d <= 128) return launch_thread_assign<128>(x, y, labels, subset, n, k, d, metric, st);
   if (subset != nullptr) return set_error(F2C_ERR_UNSUPPORTED, "kmeans_assign: subset re-scoring needs d <= 128");
   int64_t blocks = ceil_div(n, 8);
-  if (blocks > kSmCount * 32) blocks = kSmCount * 32;
+  if (blocks > current_sm_count() * 32) blocks = current_sm_count() * 32;
   if (metric == F2C_COSINE)
     kmeans_warp_kernel<F2C_COSINE, false, true><<<(unsigned)blocks, 256, 0, st>>>(x, y, nullptr, labels, n, (int)k, (int)d);
   else
@@ -191,7 +191,6 @@ bool kmeans_tc_supported(int64_t n, int64_t k, int64_t d);
 int64_t kmeans_tc_workspace(int64_t n);
 int kmeans_assign_tc(const float* x, const float* y, int64_t* labels, int64_t n, int64_t k, int64_t d, int metric, void* workspace,
                      cudaStream_t st);
-int g_kmeans_force_exact = 0;  // experiment / test switch (f2c_set_tuning key 10)
 
 static int validate_km(const char* op, int64_t n, int64_t k, int64_t d, int metric) {
   F2C_REQUIRE(n >= 0 && k >= 1 && d >= 1, F2C_ERR_INVALID, "%s: bad shape n=%lld k=%lld d=%lld", op, (long long)n, (long long)k,
@@ -212,7 +211,7 @@ extern "C" int f2c_pairwise_distance(const float* x, const float* y, float* dist
   if (n == 0) return F2C_OK;
   F2C_REQUIRE(x && y && dist, F2C_ERR_INVALID, "pairwise_distance: null pointer");
   int64_t blocks = ceil_div(n, 8);
-  if (blocks > kSmCount * 32) blocks = kSmCount * 32;
+  if (blocks > current_sm_count() * 32) blocks = current_sm_count() * 32;
   cudaStream_t st = (cudaStream_t)stream;
   if (metric == F2C_COSINE)
     kmeans_warp_kernel<F2C_COSINE, true, false><<<(unsigned)blocks, 256, 0, st>>>(x, y, dist, nullptr, n, (int)k, (int)d);
@@ -227,6 +226,8 @@ extern "C" int64_t f2c_kmeans_assign_workspace(int64_t n, int64_t k, int64_t d) 
 
 extern "C" int f2c_kmeans_assign(const float* x, const float* centers, int64_t* labels, int64_t n, int64_t k, int64_t d,
                                  int metric, void* workspace, void* stream) {
+  const int scorer = metric & (F2C_SCORER_EXACT | F2C_SCORER_TENSOR);  // per-call choice of the scorer (tests, benchmarks)
+  metric &= ~(F2C_SCORER_EXACT | F2C_SCORER_TENSOR);
   int rc = validate_km("kmeans_assign", n, k, d, metric);
   if (rc) return rc;
   if (n == 0) return F2C_OK;
@@ -234,8 +235,8 @@ extern "C" int f2c_kmeans_assign(const float* x, const float* centers, int64_t* 
   // tensor-core path when a scratch buffer is supplied and the shape fits; the exact fp32 scorer otherwise
   // (measured on B200 with 256 centres: the tensor-core path is faster from d = 8 up for both metrics; below that
   //  the CUDA-core scorer reads so little per point that the 128-point tiles only add latency)
-  const bool prefer_tc = d >= 8 || g_kmeans_force_exact == -1;
-  if (workspace != nullptr && kmeans_tc_supported(n, k, d) && prefer_tc && g_kmeans_force_exact != 1 && aligned(workspace, 16))
+  const bool prefer_tc = d >= 8 || scorer == F2C_SCORER_TENSOR;
+  if (workspace != nullptr && kmeans_tc_supported(n, k, d) && prefer_tc && scorer != F2C_SCORER_EXACT && aligned(workspace, 16))
     return kmeans_assign_tc(x, centers, labels, n, k, d, metric, workspace, (cudaStream_t)stream);
   return kmeans_assign_exact(x, centers, labels, nullptr, n, k, d, metric, (cudaStream_t)stream);
 }

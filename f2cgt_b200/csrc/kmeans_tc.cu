@@ -490,7 +490,7 @@ int kmeans_assign_tc(const float* x, const float* y, int64_t* labels, int64_t n,
   if (e != cudaSuccess) return set_error(F2C_ERR_CUDA, "kmeans_assign: %s", cudaGetErrorString(e));
   int64_t tiles = ceil_div(n, tc::kTileM);
   int64_t grid = ceil_div(tiles, 2);  // one CTA per SM (it owns all 512 TMEM columns), two tiles in flight per CTA
-  if (grid > kSmCount) grid = kSmCount;
+  if (grid > current_sm_count()) grid = current_sm_count();
   kern<<<(unsigned)grid, tc::kCtaThreads, smem, st>>>(p);
   int rc = check_launch("kmeans_assign (tensor cores)");
   if (rc) return rc;
@@ -518,6 +518,24 @@ int kmeans_assign_tc(const float* x, const float* y, int64_t* labels, int64_t n,
 namespace tc {
 constexpr int64_t kStaticMaxPoints = 1 << 20;
 static __device__ __align__(256) unsigned char g_static_scratch[256 + 4 * kStaticMaxPoints];
+
+// Device address of the scratch array on the current device, looked up once per device (with that device current).
+static int static_scratch(const char* op, void** scratch) {
+  static std::mutex mu;
+  static void* scratch_of_device[64] = {nullptr};
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= 64) return set_error(F2C_ERR_CUDA, "%s: cudaGetDevice: %s", op, cudaGetErrorString(e));
+  std::lock_guard<std::mutex> lock(mu);
+  if (scratch_of_device[dev] == nullptr) {
+    void* ptr = nullptr;
+    e = cudaGetSymbolAddress(&ptr, g_static_scratch);
+    if (e != cudaSuccess || ptr == nullptr) return set_error(F2C_ERR_CUDA, "%s: cudaGetSymbolAddress: %s", op, cudaGetErrorString(e));
+    scratch_of_device[dev] = ptr;
+  }
+  *scratch = scratch_of_device[dev];
+  return F2C_OK;
+}
 }  // namespace tc
 }  // namespace f2c
 
@@ -535,24 +553,30 @@ extern "C" int f2c_kmeans_assign_static(const float* x, const float* centers, in
   if (n == 0) return F2C_OK;
   F2C_REQUIRE(x && centers && labels, F2C_ERR_INVALID, "%s: null pointer", op);
 
-  // device address of the scratch array, looked up once per device (with that device current)
-  static std::mutex mu;
-  static void* scratch_of_device[64] = {nullptr};
-  int dev = -1;
-  cudaError_t e = cudaGetDevice(&dev);
-  if (e != cudaSuccess || dev < 0 || dev >= 64) return set_error(F2C_ERR_CUDA, "%s: cudaGetDevice: %s", op, cudaGetErrorString(e));
   void* scratch = nullptr;
-  {
-    std::lock_guard<std::mutex> lock(mu);
-    if (scratch_of_device[dev] == nullptr) {
-      void* ptr = nullptr;
-      e = cudaGetSymbolAddress(&ptr, tc::g_static_scratch);
-      if (e != cudaSuccess || ptr == nullptr) return set_error(F2C_ERR_CUDA, "%s: cudaGetSymbolAddress: %s", op, cudaGetErrorString(e));
-      scratch_of_device[dev] = ptr;
-    }
-    scratch = scratch_of_device[dev];
-  }
+  int rc = tc::static_scratch(op, &scratch);
+  if (rc) return rc;
   // same kernels as kmeans_assign; the header (count, error code) is cleared inside
   return kmeans_assign_tc(x, centers, labels, n, k, d, metric, scratch, (cudaStream_t)stream);
 }
 
+// What the last f2c_kmeans_assign_static call on the current device left in the header of the built-in array: the
+// number of points the tensor-core pass handed to the exact scorer, and the code the kernel writes when one of its
+// bounded barrier waits ran out (0 = none; labels of the unfinished tiles are then unwritten).  Waits for `stream`,
+// copies the eight header bytes to the host, allocates nothing.  Returns F2C_ERR_CUDA when the code is non-zero.
+extern "C" int f2c_kmeans_assign_static_status(int32_t* undecided_host, int32_t* error_host, void* stream) {
+  using namespace f2c;
+  const char* op = "kmeans_assign_static_status";
+  void* scratch = nullptr;
+  int rc = tc::static_scratch(op, &scratch);
+  if (rc) return rc;
+  cudaError_t e = cudaStreamSynchronize((cudaStream_t)stream);
+  if (e != cudaSuccess) return set_error(F2C_ERR_CUDA, "%s: %s", op, cudaGetErrorString(e));
+  int32_t head[2] = {0, 0};
+  e = cudaMemcpy(head, scratch, sizeof(head), cudaMemcpyDeviceToHost);
+  if (e != cudaSuccess) return set_error(F2C_ERR_CUDA, "%s: %s", op, cudaGetErrorString(e));
+  if (undecided_host) *undecided_host = head[0];
+  if (error_host) *error_host = head[1];
+  if (head[1] != 0) return set_error(F2C_ERR_CUDA, "%s: the tensor-core kernel gave up on a bounded wait (code %d)", op, head[1]);
+  return F2C_OK;
+}

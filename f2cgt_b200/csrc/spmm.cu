@@ -84,7 +84,7 @@ static int launch_spmm(const void* feat, const void* indptr, const void* indices
   if (n_dst == 0 || D == 0) return F2C_OK;
   constexpr int VEC = 16 / (int)sizeof(T);
   int64_t blocks = ceil_div(n_dst, 8);  // 8 warps per block, one row per warp per pass
-  if (blocks > kSmCount * 64) blocks = kSmCount * 64;
+  if (blocks > current_sm_count() * 64) blocks = current_sm_count() * 64;
   bool vec = D % VEC == 0 && aligned(feat, 16) && aligned(out, 16);
   if (vec)
     spmm_csr_kernel<T, IdxT, VEC><<<(unsigned)blocks, 256, 0, st>>>((const T*)feat, (T*)out, (const IdxT*)indptr,
@@ -144,7 +144,7 @@ extern "C" int f2c_check_csc(const void* indptr, const void* indices, int index_
   cudaStream_t st = (cudaStream_t)stream;
   cudaError_t e = cudaMemsetAsync(flag_device, 0, sizeof(int32_t), st);
   if (e != cudaSuccess) return set_error(F2C_ERR_CUDA, "check_csc: %s", cudaGetErrorString(e));
-  unsigned grid = (unsigned)kSmCount * 8;
+  unsigned grid = (unsigned)current_sm_count() * 8;
   if (index_dtype == F2C_I32)
     check_csc_kernel<int32_t><<<grid, 256, 0, st>>>((const int32_t*)indptr, (const int32_t*)indices, n_dst, n_src, flag_device);
   else

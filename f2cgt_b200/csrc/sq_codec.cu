@@ -258,7 +258,7 @@ static bool try_decompress_lut(const void* codes, float* out, const float* cb, i
   }
   const int rows_per_cta = kSqLutThreads / (int)cpr;
   int64_t grid = ceil_div(rows, rows_per_cta);
-  const int64_t cap = (int64_t)kSmCount * (smem > 32 * 1024 ? 3 : 6);
+  const int64_t cap = (int64_t)current_sm_count() * (smem > 32 * 1024 ? 3 : 6);
   if (grid > cap) grid = cap;
   kern<<<(unsigned)grid, kSqLutThreads, smem, st>>>((const uint8_t*)codes, out, cb, rows, src_dim, (int)D, (int)cpr, (int)cs,
                                                     (int)n_cb, log_copies, std::is_signed<CodeT>::value ? 1 : 0);

@@ -132,7 +132,7 @@ static bool try_vq_decompress_stream(const void* codes, const float* cbs, float*
   }
   const int rows_per_cta = kVqStreamThreads / (int)(D / 4);
   int64_t grid = ceil_div(rows, rows_per_cta);
-  if (grid > kSmCount) grid = kSmCount;
+  if (grid > current_sm_count()) grid = current_sm_count();
   vq_decompress_stream_kernel<<<(unsigned)grid, kVqStreamThreads, smem, st>>>(
       (const uint8_t*)codes, cbs, out, rows, (int)(D / 4), (int)n_cb, (int)K, (int)cs, (int)D, spq, stride);
   return true;

@@ -30,7 +30,8 @@ struct VqParams {
   int fast_cb_bytes;  // staged bytes per column part
 };
 
-// Pipelined kernel for the common shapes; sets *served = false (and launches nothing) when the shape is not one of them.
-int launch_vq_fast(VqParams& p, int hot_bits, int index_dtype, cudaStream_t st, const char* op, bool* served);
+// Streamed (fused_vq_stream.cu) or register-prefetch (fused_vq_fast.cu) kernel for the common shapes, by `variant`
+// (an f2c_kernel value); sets *served = false (and launches nothing) when the shape is not one of theirs.
+int launch_vq_fast(VqParams& p, int hot_bits, int index_dtype, int variant, cudaStream_t st, const char* op, bool* served);
 
 }  // namespace f2c

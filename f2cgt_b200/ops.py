@@ -61,12 +61,39 @@ class _on:
         return self.g.__exit__(*a)
 
 
-def _epilogue(dropout):
-    """dropout = None or dict(p=..., seed=..., offset=0, training=True, scale=False)."""
-    if dropout is None:
+def _epilogue(dropout, kernel="auto"):
+    """Per-call options: dropout = None or dict(p=..., seed=..., offset=0, training=True, scale=False); kernel = one of
+    ``_lib.KERNELS`` ("auto" lets the library choose; the others pin a kernel family - same bits, for tests and timing)."""
+    if dropout is None and kernel == "auto":
         return None
+    if dropout is None:
+        return Epilogue(0.0, 0, 0, 0, 0, _lib.KERNELS[kernel])
     return Epilogue(float(dropout["p"]), int(dropout.get("training", True)), int(dropout.get("scale", False)),
-                    int(dropout.get("seed", 0)) & 0xFFFFFFFFFFFFFFFF, int(dropout.get("offset", 0)))
+                    int(dropout.get("seed", 0)) & 0xFFFFFFFFFFFFFFFF, int(dropout.get("offset", 0)), _lib.KERNELS[kernel])
+
+
+def _check_block(check, indptr, indices, n_src):
+    """check=True: verify the CSC block on the device first (indptr non-decreasing from 0, every index in [0, n_src));
+    the fused kernels trust ``indices`` like the reference does, so a debugging caller can ask."""
+    if not check:
+        return
+    flag = torch.zeros(1, dtype=torch.int32, device=indptr.device)
+    with _on(indptr):
+        _lib.check(lib.f2c_check_csc(_ptr(indptr), _ptr(indices), _DT[indptr.dtype], indptr.numel() - 1, int(n_src), _ptr(flag),
+                                     _stream(indptr)))
+    code = int(flag.item())
+    if code != 0:
+        raise RuntimeError(f"invalid CSC block (code {code}): indptr must be non-decreasing from 0 and every index in [0, {n_src})")
+
+
+def device_status(device=None):
+    """0, or the code of a bounded wait that ran out inside a kernel since the last query (synchronises the current stream)."""
+    import ctypes
+    code = ctypes.c_int32(0)
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    with torch.cuda.device(dev):
+        check(lib.f2c_device_status(ctypes.byref(code), torch.cuda.current_stream(dev).cuda_stream))
+    return int(code.value)
 
 
 # ------------------------------------------------------------------ bit packing
@@ -167,24 +194,26 @@ def spmm_csr(feat, indptr, indices, reduce="mean"):
 
 
 def sq_decompress_spmm_csr(compress_feat, codebooks, indptr, indices, target_bit, column_slice, feat_dim, reduce="mean",
-                           dropout=None):
+                           dropout=None, kernel="auto", check=False):
     """src/fusion_spmm.cu:240-272.  Fused SQ decode + mean aggregation -> float32 [n_dst, feat_dim]."""
     _chk(compress_feat, "compress_feat", (torch.uint8, torch.int8, torch.int16))
     _chk(codebooks, "codebooks", (torch.float32,))
     n_dst = _csc(indptr, indices)
     if compress_feat.dim() != 2:
         raise RuntimeError("compress_feat must be 2-D")
+    _check_block(check, indptr, indices, compress_feat.shape[0])
     out = torch.empty((n_dst, feat_dim), dtype=torch.float32, device=compress_feat.device)
-    ep = _epilogue(dropout)
+    ep = _epilogue(dropout, kernel)
     with _on(compress_feat):
-        check(lib.f2c_sq_spmm_csr(_ptr(compress_feat), _DT[compress_feat.dtype], _ptr(codebooks), codebooks.shape[0],
+        _lib.check(lib.f2c_sq_spmm_csr(_ptr(compress_feat), _DT[compress_feat.dtype], _ptr(codebooks), codebooks.shape[0],
                                   _ptr(indptr), _ptr(indices), _DT[indptr.dtype], _ptr(out), n_dst, compress_feat.shape[0],
-                                  compress_feat.shape[1], feat_dim, target_bit, column_slice, _REDUCE[reduce], ep, _stream(compress_feat)))
+                                       compress_feat.shape[1], feat_dim, target_bit, column_slice, _REDUCE[reduce], ep,
+                                       _stream(compress_feat)))
     return out
 
 
 def sq_decompress_spmm_csr_peer(peer_table, codebooks, indptr, indices, target_bit, column_slice, feat_dim, reduce="mean",
-                                dropout=None):
+                                dropout=None, kernel="auto"):
     """``sq_decompress_spmm_csr`` over a row-sharded table (``f2cgt_b200.shard.PeerTable``): indices are global row ids,
     remote rows are read by the kernel itself over NVLink."""
     import ctypes
@@ -194,7 +223,7 @@ def sq_decompress_spmm_csr_peer(peer_table, codebooks, indptr, indices, target_b
     if len(peer_table.pointers) != peer_table.world:
         raise RuntimeError("the peer table is closed")
     ptrs = (ctypes.c_void_p * peer_table.world)(*peer_table.pointers)
-    ep = _epilogue(dropout)
+    ep = _epilogue(dropout, kernel)
     with _on(indptr):
         check(lib.f2c_sq_spmm_csr_peer(ptrs, peer_table.world, peer_table.rpr, _DT[peer_table.dtype], _ptr(codebooks),
                                        codebooks.shape[0], _ptr(indptr), _ptr(indices), _DT[indptr.dtype], _ptr(out), n_dst,
@@ -203,7 +232,8 @@ def sq_decompress_spmm_csr_peer(peer_table, codebooks, indptr, indices, target_b
     return out
 
 
-def vq_decompress_spmm_csr(compress_feat, codebooks, indptr, indices, feat_dim, reduce="mean", dropout=None):
+def vq_decompress_spmm_csr(compress_feat, codebooks, indptr, indices, feat_dim, reduce="mean", dropout=None, kernel="auto",
+                           check=False):
     """src/fusion_spmm.cu:107-141.  Fused VQ decode + mean aggregation -> float32 [n_dst, feat_dim]."""
     _chk(compress_feat, "compress_feat", (torch.uint8, torch.int8, torch.int16))
     _chk(codebooks, "codebooks", (torch.float32,))
@@ -211,10 +241,11 @@ def vq_decompress_spmm_csr(compress_feat, codebooks, indptr, indices, feat_dim, 
     if compress_feat.dim() != 2 or codebooks.dim() != 3 or compress_feat.shape[1] != codebooks.shape[0]:
         raise RuntimeError("compress_feat must be [rows, n_codebooks] and codebooks [n_codebooks, length, column_slice]")
     n_cb, K, cs = codebooks.shape
+    _check_block(check, indptr, indices, compress_feat.shape[0])
     out = torch.empty((n_dst, feat_dim), dtype=torch.float32, device=compress_feat.device)
-    ep = _epilogue(dropout)
+    ep = _epilogue(dropout, kernel)
     with _on(compress_feat):
-        check(lib.f2c_vq_spmm_csr(_ptr(compress_feat), _DT[compress_feat.dtype], _ptr(codebooks), _ptr(indptr), _ptr(indices),
+        _lib.check(lib.f2c_vq_spmm_csr(_ptr(compress_feat), _DT[compress_feat.dtype], _ptr(codebooks), _ptr(indptr), _ptr(indices),
                                   _DT[indptr.dtype], _ptr(out), n_dst, n_cb, K, cs, feat_dim, _REDUCE[reduce], ep,
                                   _stream(compress_feat)))
     return out
@@ -238,7 +269,7 @@ def fusion_decompress(sq_data, sq_codebooks, target_bits, column_slice, vq_data,
 
 
 def two_level_decompress_spmm_csr(sq_data, sq_codebooks, target_bits, column_slice, vq_data, vq_codebooks, slot, indptr,
-                                  indices, feat_dim, reduce="mean", dropout=None):
+                                  indices, feat_dim, reduce="mean", dropout=None, kernel="auto", check=False):
     """Two-level aggregation in one launch.  Source row s is decoded from row ``slot[s]`` of the SQ table
     when ``slot[s] >= 0`` (int32), from row s of the VQ table otherwise; then the reference mean."""
     _chk(sq_data, "sq_data", (torch.uint8, torch.int8, torch.int16))
@@ -248,10 +279,11 @@ def two_level_decompress_spmm_csr(sq_data, sq_codebooks, target_bits, column_sli
     _chk(slot, "slot", (torch.int32,))
     n_dst = _csc(indptr, indices)
     n_cb, K, cs = vq_codebooks.shape
+    _check_block(check, indptr, indices, vq_data.shape[0])
     out = torch.empty((n_dst, feat_dim), dtype=torch.float32, device=vq_data.device)
-    ep = _epilogue(dropout)
+    ep = _epilogue(dropout, kernel)
     with _on(vq_data):
-        check(lib.f2c_hybrid_spmm_csr(_ptr(sq_data), _DT[sq_data.dtype], _ptr(sq_codebooks), sq_codebooks.shape[0],
+        _lib.check(lib.f2c_hybrid_spmm_csr(_ptr(sq_data), _DT[sq_data.dtype], _ptr(sq_codebooks), sq_codebooks.shape[0],
                                       target_bits, column_slice, sq_data.shape[1], _ptr(vq_data), _DT[vq_data.dtype],
                                       _ptr(vq_codebooks), n_cb, K, cs, _ptr(slot), _ptr(indptr), _ptr(indices),
                                       _DT[indptr.dtype], _ptr(out), n_dst, feat_dim, _REDUCE[reduce], ep, _stream(vq_data)))
@@ -286,8 +318,9 @@ def pairwise_distance(x, y, metric):
     return dist
 
 
-def kmeans_assign(x, centers, metric):
-    """labels[i] = first argmin_c dist(x_i, centers_c), int64 (src/kmeans.cu:77-98)."""
+def kmeans_assign(x, centers, metric, scorer="auto"):
+    """labels[i] = first argmin_c dist(x_i, centers_c), int64 (src/kmeans.cu:77-98).  scorer = "auto" | "exact" (fp32 FMA) |
+    "tensor" (tcgen05 + exact re-score of undecided points): same labels, pinned per call for tests and timing."""
     _chk(x, "data", (torch.float32,))
     _chk(centers, "centers", (torch.float32,))
     if x.dim() != 2 or centers.dim() != 2 or x.shape[1] != centers.shape[1]:
@@ -300,7 +333,8 @@ def kmeans_assign(x, centers, metric):
     if ws is not None:
         ws[:256].zero_()  # header: [undecided count, error code]; the library clears it again when it uses the scratch
     with _on(x):
-        check(lib.f2c_kmeans_assign(_ptr(x), _ptr(centers), _ptr(labels), n, k, d, _metric(metric), _ptr(ws) if ws is not None else 0,
+        flags = {"auto": 0, "exact": _lib.SCORER_EXACT, "tensor": _lib.SCORER_TENSOR}[scorer]
+        check(lib.f2c_kmeans_assign(_ptr(x), _ptr(centers), _ptr(labels), n, k, d, _metric(metric) | flags, _ptr(ws) if ws is not None else 0,
                                     _stream(x)))
     if ws is not None:
         # word 1 of the scratch header is set when the tensor-core kernel gave up on a bounded wait
@@ -363,12 +397,6 @@ class KMeans:
 
     def get_centers(self):
         return self.cluster_centers
-
-
-def set_tuning(key, value):
-    """Experiment knobs: key in {"vec", "inflight", "lut", "ctas_per_sm"} (fused SQ kernel), "vq_fast" (1/0: pipelined
-    VQ / two-level kernel or the general one), "sq_async" (1/0: cp.async ring variant of the 4- / 8-bit fused SQ kernels), "kmeans_exact" (1: exact fp32 scorer, -1: tensor-core scorer, 0: heuristic)."""
-    check(lib.f2c_set_tuning({"vec": 0, "inflight": 1, "lut": 2, "ctas_per_sm": 3, "vq_fast": 4, "sq_async": 5, "kmeans_exact": 10}[key], int(value)))
 
 
 # ------------------------------------------------------------------ neighbour sampling

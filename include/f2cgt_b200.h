@@ -34,6 +34,10 @@ typedef enum {
 
 typedef enum { F2C_MEAN = 0, F2C_SUM = 1 } f2c_reduce;   /* the reference only has mean */
 typedef enum { F2C_L2 = 0, F2C_COSINE = 1 } f2c_metric;  /* src/kmeans.cu:16-22,107-112 */
+/* f2c_kmeans_assign only: OR one of these into `metric` to pin the scorer for this call (tests, benchmarks);
+ * without one the library picks by shape.  Both give the same labels. */
+#define F2C_SCORER_EXACT 0x100   /* fp32 FMA scorer */
+#define F2C_SCORER_TENSOR 0x200  /* tcgen05 scorer + exact re-score of undecided points (needs a workspace) */
 
 typedef enum {
   F2C_OK = 0,
@@ -43,18 +47,36 @@ typedef enum {
   F2C_ERR_LIMIT = 4         /* a stated size limit of the entry point was exceeded */
 } f2c_status;
 
-/* Optional epilogue fused into the aggregation kernels: dropout on the aggregated output.
- * Equivalent to calling f2c_dropout on the output with the same arguments.  NULL = no epilogue. */
+/* Kernel family of a fused aggregation call.  Every family computes the same bits (same decode expression, CSC
+ * summation order, one division); AUTO picks the fastest one that takes the shape, the others exist so that tests and
+ * benchmarks can pin one.  A pinned family that does not take the shape returns F2C_ERR_UNSUPPORTED. */
+typedef enum {
+  F2C_KERNEL_AUTO = 0,
+  F2C_KERNEL_STREAM = 1,          /* producer warp streams neighbour data into a shared-memory ring (cp.async) */
+  F2C_KERNEL_PREFETCH = 2,        /* neighbour data prefetched into registers, software-pipelined over rows */
+  F2C_KERNEL_GENERAL = 3,         /* any shape: warp per destination row, arithmetic decode */
+  F2C_KERNEL_PREFETCH_ARITH = 4   /* fused SQ only: the register-prefetch kernel with exp2f decode instead of the table */
+} f2c_kernel;
+
+/* Optional per-call options of the aggregation kernels: dropout fused on the aggregated output (equivalent to calling
+ * f2c_dropout on the output with the same arguments) and the kernel family.  NULL = no dropout, F2C_KERNEL_AUTO. */
 typedef struct {
   float p;          /* drop probability */
   int training;     /* 0 = identity */
   int scale;        /* 0 = survivors unchanged (reference, src/fusion_dropout.cu:16); 1 = times 1/(1-p) */
   uint64_t seed;    /* Philox key */
   uint64_t offset;  /* Philox stream offset (counter words 2,3) */
+  int kernel;       /* f2c_kernel */
 } f2c_epilogue;
 
 const char* f2c_last_error(void);
 int f2c_version(void);
+
+/* Kernels of this library never spin without a limit: a wait that runs out (a producer warp or a tensor-core
+ * barrier that does not answer within ~0.2 s) makes the kernel return early and raises a per-device word.
+ * f2c_device_status synchronises `stream`, copies that word of the current device to *code_host (0 = no wait ever
+ * ran out since the last query) and clears it.  Allocates nothing.  No counterpart in the reference. */
+int f2c_device_status(int32_t* code_host, void* stream);
 
 /* packbits(unpack, target_bits)  -  src/packbits.cu:44-64 (kernel :6-42).
  * unpack [rows, unpack_dim] u8 -> pack [rows, ceil(unpack_dim*bits/8)] u8; bits in {1,2,4}. */
@@ -179,18 +201,16 @@ int f2c_kmeans_assign(const float* x, const float* centers, int64_t* labels, int
  * (a synchronising runtime query).  All calls on a device share the array: calls that overlap on the GPU race. */
 int f2c_kmeans_assign_static(const float* x, const float* centers, int64_t* labels, int64_t n, int64_t k, int64_t d,
                              int metric, void* stream);
+/* Companion of f2c_kmeans_assign_static (no counterpart in the reference either): its caller cannot read the
+ * built-in array, so this copies the array's 8-byte header to the host after `stream` has drained - the number of
+ * points the exact scorer had to settle and the code the kernel writes when one of its bounded waits ran out
+ * (then some labels are unwritten).  Returns F2C_ERR_CUDA when that code is non-zero.  Allocates nothing.
+ * (f2c_kmeans_assign reports the same two words as int32 words 0 and 1 of the caller's workspace.) */
+int f2c_kmeans_assign_static_status(int32_t* undecided_host, int32_t* error_host, void* stream);
 
 /* Debug helper (no counterpart: the reference never checks that indices < compress_feat.size(0)).
  * Writes 0 to *flag_device if indptr is non-decreasing from 0.. and every index is in [0, n_src),
  * else a non-zero code.  Asynchronous; the caller reads the flag. */
-/* Experiment knobs (no counterpart in the reference).  Fused SQ kernel - key 0: bytes per lane per row load
- * (4/8), 1: neighbours held in registers per row (8/12/16), 2: table decode on/off, 3: CTAs per SM; value 0
- * (key 2: -1) restores the built-in choice.  Key 4: pipelined VQ / two-level kernel on (1, default) or off (0).
- * Key 5: 4- / 8-bit fused SQ kernels that stage neighbour rows in a shared-memory ring with cp.async instead of
- * registers, on (1) or off (0, default: measured slower).
- * Key 10: k-means scorer, 1 exact fp32, -1 tensor cores, 0 heuristic. */
-int f2c_set_tuning(int key, int value);
-
 int f2c_check_csc(const void* indptr, const void* indices, int index_dtype, int64_t n_dst, int64_t n_src,
                   int32_t* flag_device, void* stream);
 

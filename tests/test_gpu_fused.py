@@ -76,27 +76,78 @@ def test_fused_sq_equals_unfused_and_oracle(capi, oracle, bits, D, cs):
         assert torch.equal(again, fused)
 
 
-@pytest.mark.parametrize("bits", [2, 4, 8])
-def test_fused_sq_every_tuning_variant_is_bit_identical(capi, oracle, bits):
-    rng = np.random.default_rng(bits)
-    _, cb, stored = sq_table(oracle, rng, 400, 128, bits, 64)
-    indptr, indices = random_csc(rng, 333, 400, max_deg=25)
-    args = (dev(stored), dev(cb), dev(indptr), dev(indices), bits, 64, 128)
-    from f2cgt_b200 import ops
-    base = capi.sq_decompress_spmm_csr(*args)
+def _served(fn):
+    """Result of a call that pins a kernel family, or None when that family does not take the shape."""
     try:
-        for vec in (4, 8, 16):
-            for inflight in (4, 8):
-                for lut in (0, 1):
-                    ops.set_tuning("vec", vec), ops.set_tuning("inflight", inflight), ops.set_tuning("lut", lut)
-                    assert torch.equal(capi.sq_decompress_spmm_csr(*args), base), (vec, inflight, lut)
-        # the cp.async ring variant (neighbour rows staged in shared memory instead of registers), 8 and 12 rows per stage
-        ops.set_tuning("vec", 0), ops.set_tuning("lut", -1)
-        for inflight in (8, 12, 16):
-            ops.set_tuning("inflight", inflight), ops.set_tuning("sq_async", 1)
-            assert torch.equal(capi.sq_decompress_spmm_csr(*args), base), ("async", inflight)
-    finally:
-        ops.set_tuning("vec", 0), ops.set_tuning("inflight", 0), ops.set_tuning("lut", -1), ops.set_tuning("sq_async", 0)
+        return fn()
+    except RuntimeError as e:
+        if "not served" in str(e):
+            return None
+        raise
+
+
+@pytest.mark.parametrize("bits", [1, 2, 4, 8])
+@pytest.mark.parametrize("D,cs", [(128, 64), (128, 128), (256, 256), (96, 96), (64, 16), (32, 8)])
+def test_fused_sq_every_kernel_family_is_bit_identical(capi, oracle, bits, D, cs):
+    """Streamed, register-prefetch (table and exp2f decode) and general kernels: same bits, any degree mix
+    (empty rows, rows longer than the streamed kernel's ring groups, ragged last group)."""
+    rng = np.random.default_rng(bits + D)
+    _, cb, stored = sq_table(oracle, rng, 400, D, bits, cs)
+    deg = rng.integers(0, 26, 333)
+    deg[::7] = 0
+    deg[5::41] = rng.integers(60, 400, len(deg[5::41]))
+    indptr = np.concatenate([[0], np.cumsum(deg)]).astype(np.int64)
+    indices = rng.integers(0, 400, int(indptr[-1])).astype(np.int64)
+    for idx in (np.int64, np.int32):
+        args = (dev(stored), dev(cb), dev(indptr.astype(idx)), dev(indices.astype(idx)), bits, cs, D)
+        base = capi.sq_decompress_spmm_csr(*args, kernel="general")
+        ran = []
+        for kernel in ("stream", "prefetch", "prefetch_arith", "auto"):
+            for kw in (dict(), dict(reduce="sum"), dict(dropout=dict(p=0.3, seed=5, offset=1, training=True))):
+                got = _served(lambda: capi.sq_decompress_spmm_csr(*args, kernel=kernel, **kw))
+                if got is not None:
+                    assert torch.equal(got, capi.sq_decompress_spmm_csr(*args, kernel="general", **kw)), (kernel, kw, idx)
+                    ran.append(kernel)
+        if D * bits % 128 == 0 and D * bits <= 8 * 256 and cs % (64 // bits if bits > 2 else 32 // bits) == 0:
+            assert "stream" in ran, "the streamed kernel must take whole 16-byte rows whose lanes see one codebook row"
+        assert torch.equal(capi.sq_decompress_spmm_csr(*args), base)
+    from f2cgt_b200 import ops
+    assert ops.device_status() == 0
+
+
+@pytest.mark.parametrize("kind", ["sq1", "sq4", "sq8", "vq", "two_level"])
+def test_streamed_kernels_over_several_chunks(capi, oracle, kind):
+    """More destination rows than one pass of the grid's indptr slices (148 CTAs x 1024 rows), a table small enough
+    that the general kernel is a cheap comparator: chunk boundaries, ring wrap-around, the drain between chunks."""
+    rng = np.random.default_rng(11)
+    n_src, n_dst, D = 3000, 320_000, 128
+    deg = rng.integers(0, 14, n_dst)
+    deg[::1000] = 70
+    indptr = np.concatenate([[0], np.cumsum(deg)]).astype(np.int64)
+    indices = rng.integers(0, n_src, int(indptr[-1])).astype(np.int64)
+    ip, ix = dev(indptr), dev(indices)
+    if kind.startswith("sq"):
+        bits = int(kind[2:])
+        _, cb, stored = sq_table(oracle, rng, n_src, D, bits, 128)
+        a = capi.sq_decompress_spmm_csr(dev(stored), dev(cb), ip, ix, bits, 128, D, kernel="stream")
+        b = capi.sq_decompress_spmm_csr(dev(stored), dev(cb), ip, ix, bits, 128, D, kernel="prefetch")
+    else:
+        cbs = dev(rng.standard_normal((4, 256, 32)).astype(np.float32))
+        codes = dev(rng.integers(0, 256, (n_src, 4)).astype(np.uint8))
+        if kind == "vq":
+            a = capi.vq_decompress_spmm_csr(codes, cbs, ip, ix, D, kernel="stream")
+            b = capi.vq_decompress_spmm_csr(codes, cbs, ip, ix, D, kernel="prefetch")
+        else:
+            _, cb, sq = sq_table(oracle, rng, 600, D, 8, 128)
+            slot = np.full(n_src, -1, np.int32)
+            hot = rng.choice(n_src, 600, replace=False)
+            slot[hot] = rng.permutation(600).astype(np.int32)
+            t = (dev(sq), dev(cb), 8, 128, codes, cbs, dev(slot), ip, ix, D)
+            a = capi.two_level_decompress_spmm_csr(*t, kernel="stream")
+            b = capi.two_level_decompress_spmm_csr(*t, kernel="prefetch")
+    assert torch.equal(a, b)
+    from f2cgt_b200 import ops
+    assert ops.device_status() == 0
 
 
 @pytest.mark.parametrize("bits", [4, 16])
@@ -191,9 +242,9 @@ def test_two_level_is_composition(capi, oracle, bits, D, n_cb, cs):
                                          (16, 256, 4, 64), (4, 256, 64, 256), (8, 256, 32, 256), (4, 37, 128, 512)])
 @pytest.mark.parametrize("hot_bits,hot_cs", [(0, 0), (8, 0), (8, 32), (4, 0), (4, 64)])
 def test_pipelined_vq_kernel_equals_general_kernel(capi, oracle, n_cb, K, cs, D, hot_bits, hot_cs):
-    """The pipelined kernel (shared-memory codebooks, table decode of hot rows) against the general one and the oracle:
-    rows with 0, 1..16, 17..32 and more than 32 neighbours, codes >= K, ragged feat_dim, several column parts."""
-    from f2cgt_b200 import ops
+    """The streamed and register-prefetch kernels (shared-memory codebooks, table decode of hot rows) against the
+    general one and the oracle: rows with 0, 1..16, 17..32 and more than 32 neighbours, codes >= K, ragged feat_dim,
+    several column parts."""
     rng = np.random.default_rng(n_cb * 7 + cs + hot_bits)
     n_src, n_hot, n_dst = 700, 90, 333
     cbs = rng.standard_normal((n_cb, K, cs)).astype(np.float32)
@@ -209,21 +260,19 @@ def test_pipelined_vq_kernel_equals_general_kernel(capi, oracle, n_cb, K, cs, D,
     drop = dict(p=0.3, seed=5, offset=1, training=True)
 
     def both(fn):
-        ops.set_tuning("vq_fast", 1)
-        a = fn()
-        ops.set_tuning("vq_fast", 0)
-        try:
-            b = fn()
-        finally:
-            ops.set_tuning("vq_fast", 1)
-        return a, b
+        """(kernel-family results that took the shape, general-kernel result)"""
+        fast = [r for r in (_served(lambda k=k: fn(k)) for k in ("stream", "prefetch", "auto")) if r is not None]
+        assert len(fast) >= 2  # "auto" always runs; the prefetch kernel takes every shape of this test
+        if K == 256:
+            assert len(fast) == 3, "the streamed kernel must take 256-centroid codebooks"
+        return fast, fn("general")
 
     for idx in (np.int64, np.int32):
         ip, ix = dev(indptr.astype(idx)), dev(indices.astype(idx))
         if hot_bits == 0:
             for kw in (dict(), dict(reduce="sum"), dict(dropout=drop)):
-                a, b = both(lambda: capi.vq_decompress_spmm_csr(dev(codes), dev(cbs), ip, ix, D, **kw))
-                assert torch.equal(a, b), kw
+                fast, b = both(lambda k: capi.vq_decompress_spmm_csr(dev(codes), dev(cbs), ip, ix, D, kernel=k, **kw))
+                assert all(torch.equal(a, b) for a in fast), kw
             want = oracle.vq_decompress_spmm_csr(np.minimum(codes, K - 1).astype(np.uint8), cbs, indptr, indices, D, "mean")
             assert np.array_equal(host(capi.vq_decompress_spmm_csr(dev(codes), dev(cbs), ip, ix, D)), want)
         else:
@@ -236,9 +285,9 @@ def test_pipelined_vq_kernel_equals_general_kernel(capi, oracle, n_cb, K, cs, D,
                 hot = rng.choice(n_src, n_hot, replace=False)
                 slot[hot] = rng.permutation(n_hot).astype(np.int32)
                 for kw in (dict(), dict(reduce="sum"), dict(dropout=drop)):
-                    a, b = both(lambda: capi.two_level_decompress_spmm_csr(dev(sq), dev(cb), hot_bits, hcs, dev(codes), dev(cbs),
-                                                                           dev(slot), ip, ix, D, **kw))
-                    assert torch.equal(a, b), (kw, signed)
+                    fast, b = both(lambda k: capi.two_level_decompress_spmm_csr(dev(sq), dev(cb), hot_bits, hcs, dev(codes), dev(cbs),
+                                                                                dev(slot), ip, ix, D, kernel=k, **kw))
+                    assert all(torch.equal(a, b) for a in fast), (kw, signed)
 
 
 @pytest.mark.parametrize("kind", ["sq", "vq", "two_level"])

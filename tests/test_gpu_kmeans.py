@@ -96,16 +96,28 @@ def test_tensor_core_assignment_equals_exact_fp32_kernel(capi, oracle, metric, n
     if k >= 8:
         c2[k // 2] = c2[1]         # an exact duplicate centre: the lower index must win
     for centers in (c, c2):
-        try:
-            ops.set_tuning("kmeans_exact", -1)  # force the tensor-core path whatever the shape heuristic says
-            tc = capi.kmeans_assign(x, centers, metric)
-            undecided = ops.kmeans_assign.last_undecided
-            ops.set_tuning("kmeans_exact", 1)
-            exact = capi.kmeans_assign(x, centers, metric)
-        finally:
-            ops.set_tuning("kmeans_exact", 0)
+        tc = ops.kmeans_assign(x, centers, metric, scorer="tensor")  # the tensor-core path whatever the shape heuristic says
+        undecided = ops.kmeans_assign.last_undecided
+        exact = ops.kmeans_assign(x, centers, metric, scorer="exact")
         assert torch.equal(tc, exact), (metric, n, k, d, int((tc != exact).sum()))
         # the split product (3 x tf32 up to d = 32, 3 x bf16 up to d = 64) decides almost everything itself
         # (a duplicated centre makes every point that prefers it an exact tie: about 1/k of the points)
         assert undecided <= (0.02 if d <= 32 else 0.05) * n + 8 + (3.0 * n / k if centers is c2 else 0)
-    assert labels_match(oracle, x.cpu().numpy(), c.cpu().numpy(), metric, tc.cpu().numpy()) or True
+        if centers is c:
+            assert labels_match(oracle, x.cpu().numpy(), c.cpu().numpy(), metric, tc.cpu().numpy())
+
+
+@pytest.mark.parametrize("d", [8, 32, 64])
+def test_tensor_core_assignment_at_table_scale(capi, d):
+    """The sizes the k-means profile times: 2,449,029 sub-vectors against 256 centres (one VQ subspace of the
+    2.4 M-row table), tensor-core labels == exact-scorer labels point for point, both metrics."""
+    from f2cgt_b200 import ops
+    n, k = 2_449_029, 256
+    g = torch.Generator(device="cuda").manual_seed(d)
+    x = torch.randn(n, d, device="cuda", generator=g)
+    c = torch.randn(k, d, device="cuda", generator=g)
+    for metric in ("l2", "cosine"):
+        tc = ops.kmeans_assign(x, c, metric, scorer="tensor")
+        assert ops.kmeans_assign.last_undecided <= (0.02 if d <= 32 else 0.05) * n
+        exact = ops.kmeans_assign(x, c, metric, scorer="exact")
+        assert torch.equal(tc, exact), (metric, d, int((tc != exact).sum()))

@@ -24,11 +24,17 @@ def _regular(lib, x, c, metric):
 
 
 def _static(lib, x, c, metric):
+    import ctypes
     n, d = x.shape
     labels = torch.full((n,), -1, dtype=torch.int64, device="cuda")
     rc = lib.f2c_kmeans_assign_static(x.data_ptr(), c.data_ptr(), labels.data_ptr(), n, c.shape[0], d, metric, 0)
     assert rc == 0, lib.f2c_last_error()
-    torch.cuda.synchronize()
+    # the caller cannot read the built-in array; the status call copies its header out after the stream has drained
+    undecided, error = ctypes.c_int32(-1), ctypes.c_int32(-1)
+    rc = lib.f2c_kmeans_assign_static_status(ctypes.byref(undecided), ctypes.byref(error), 0)
+    assert rc == 0, lib.f2c_last_error()
+    assert error.value == 0, "a bounded wait of the tensor-core kernel ran out"
+    assert undecided.value >= 1, "the duplicated centre must leave exact ties to the exact scorer"
     return labels
 
 
