@@ -2,19 +2,21 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
 
-Workload (N = 1): the packed low-bit SQ configuration - a 2,449,029 x 128 feature table stored as 1-,
-2- and 4-bit log-domain SQ codes of N(0,1) features, a synthetic power-law graph (Zipf 2.1 degrees,
-mean 50), minibatches of 1024 seeds with fan-out 12,12,12.  One STEP aggregates the outermost block
-(the one the fused first GraphSAGE layer sees: ~10^5 destination rows, ~10^6 edges) of one minibatch
-with the fused kernel once per code width (three launches), gathering rows straight from the HBM-
-resident table by global id.  Successive steps use different pre-sampled minibatches and L2 is
-flushed between steps (outside the step's event pair).
+Workload (both arms, identical inputs): the packed low-bit SQ configuration - a 2,449,029 x 128 feature table stored
+as 1-, 2- and 4-bit log-domain SQ codes of N(0,1) features, a synthetic power-law graph (Zipf 2.1 degrees, mean 50),
+six minibatches of 1024 seeds with fan-out 12,12,12.  Graph, tables and the six outermost blocks (the ones the fused
+first GraphSAGE layer sees: ~7 * 10^4 destination rows, ~8 * 10^5 edges) come from ONE seeded CPU generator
+(`cpu_workload`, cached on disk between the two arms); the GPU arm uploads them.  One STEP aggregates one block with
+the fused kernel once per code width (three launches), gathering rows straight from the HBM-resident table by
+global id.  Successive steps rotate through the six blocks and L2 is flushed between steps (outside the event pair).
 
-Prints ONE JSON line (rank 0).  `value` = sampled edges aggregated per second by the whole job with
-all inputs resident in HBM; `e2e` = the same work called through the public module with the block's
-CSC in pinned host memory and the aggregated rows read back to the host inside the timed region.
-`--impl reference` times the reference's PyTorch CPU path (oracle/torch_cpu_path.py) on the same
-configuration on the host cores.
+Prints ONE JSON line (rank 0).  `value` = sampled edges aggregated per second by the whole job with all inputs
+resident in HBM; at N > 1 the table is ROW-SHARDED over the GPUs (1/N of the rows each) and the kernel reads remote
+rows over NVLink, the replicated and the NCCL all-to-all placements are timed beside it.  `e2e` = the same work called
+through the public module with the block's CSC in pinned host memory and the aggregated rows read back to the host
+inside the timed region.  `epoch` = GraphSAGE training (3 layers, two-level table) seconds per epoch, replicated and
+sharded table.  `--impl reference` times the reference's PyTorch CPU path (oracle/torch_cpu_path.py) on the same
+blocks and tables on the host cores.
 """
 import argparse
 import json
@@ -37,9 +39,12 @@ BITS = (1, 2, 4)
 COLUMN_SLICE = 128
 N_MINIBATCHES = 6
 METRIC = "fused_sq_decompress_spmm_sampled_edges_per_s"
-# dram__bytes_read.sum + dram__bytes_write.sum per launch on this block, from one ncu capture per width
-# (profiles/sq_spmm_bench_block.md); below the algorithmic bytes because the output is still dirty in L2 at kernel end
-NCU_DRAM_TRAFFIC_BYTES = {1: 34.9e6, 2: 43.1e6, 4: 48.5e6}
+WORKLOAD = ("SQ 1/2/4-bit packed table 2449029x128 (N(0,1) features), power-law graph (Zipf 2.1, mean degree 50), "
+            "6 minibatches of 1024 seeds x fan-out 12,12,12, outermost block, all three widths per step; graph, tables and "
+            "blocks from one seeded CPU generator")
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the 4-bit kernel on a block of this generator, from an ncu
+# capture (not measured in this run); below the algorithmic bytes because the output is still dirty in L2 at kernel end
+NCU_DRAM_TRAFFIC_BYTES_SQ4 = 49.8e6
 
 
 def algorithmic_bytes(n_edges, n_dst, row_bytes, idx_bytes, feat_dim, codebook_bytes):
@@ -99,33 +104,123 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
+# --------------------------------------------------------------------------------------------- shared workload
+def cpu_workload(need_graph=False):
+    """Graph, SQ tables (1/2/4 bits) and the six outermost blocks, generated on the CPU from seed 0 with torch's CPU
+    generator, the oracle's compressor and the oracle's neighbour sampler.  Both arms call this; the result is cached
+    on disk (plain .npy files) so that the second arm on a box only reads it back.  Returns numpy arrays."""
+    import numpy as np
+    cache = os.environ.get("F2CGT_BENCH_CACHE", "/tmp/f2cgt_b200_bench_workload_v3")
+    done = os.path.join(cache, "done")
+    names = [f"codes{b}" for b in BITS] + ["codebook"] + [f"blk{i}_{k}" for i in range(N_MINIBATCHES) for k in ("indptr", "indices")]
+
+    def load(with_graph):
+        w = {n: np.load(os.path.join(cache, n + ".npy"), mmap_mode="r") for n in names}
+        if with_graph:
+            w["graph_indptr"] = np.load(os.path.join(cache, "graph_indptr.npy"), mmap_mode="r")
+            w["graph_indices"] = np.load(os.path.join(cache, "graph_indices.npy"), mmap_mode="r")
+        return w
+
+    if os.path.exists(done):
+        try:
+            return load(need_graph)
+        except Exception:  # noqa: BLE001
+            pass
+    import torch
+    from oracle import oracle as O
+    torch.set_num_threads(os.cpu_count() or 1)
+    g = torch.Generator(); g.manual_seed(0)
+    u = torch.rand(NUM_NODES, generator=g, dtype=torch.float64).clamp_min(1e-12)
+    raw = u.pow(-1.0 / (ZIPF - 1.0)).clamp_max(NUM_NODES // 20)
+    deg = torch.floor(raw * (AVG_DEGREE / float(raw.mean()))).to(torch.int64)
+    indptr = torch.zeros(NUM_NODES + 1, dtype=torch.int64)
+    torch.cumsum(deg, 0, out=indptr[1:])
+    nnz = int(indptr[-1])
+    indices = torch.empty(nnz, dtype=torch.int64)
+    for s in range(0, nnz, 1 << 25):
+        e = min(s + (1 << 25), nnz)
+        indices[s:e] = torch.searchsorted(indptr, torch.randint(0, nnz, (e - s,), generator=g), right=True) - 1
+    ip_np, ix_np = indptr.numpy(), indices.numpy()
+    # tables: codes of N(0,1) features, encoded chunk-wise with the oracle's compressor
+    sample = torch.randn((250_000, FEAT_DIM), generator=g).numpy()
+    cb = O.sq_codebooks(sample, COLUMN_SLICE)
+    tables = {b: [] for b in BITS}
+    for s in range(0, NUM_NODES, 1 << 18):
+        x = torch.randn((min(1 << 18, NUM_NODES - s), FEAT_DIM), generator=g).numpy()
+        for b in BITS:
+            tables[b].append(O.sq_codes_to_storage(O.sq_compress(x, cb, b, COLUMN_SLICE), b))
+    w = {f"codes{b}": np.concatenate(v).view(np.uint8) for b, v in tables.items()}
+    w["codebook"] = cb
+    # minibatch blocks with the oracle's sampler: hops in reversed(fan_out) order, frontier = [frontier, new nodes]
+    for mb in range(N_MINIBATCHES):
+        frontier = torch.randperm(NUM_NODES, generator=g)[:BATCH].numpy()
+        for hop, pick in enumerate(reversed(FAN_OUT)):
+            sip, six = O.sample_neighbors(ip_np, ix_np, frontier, pick, mb, hop)
+            if hop == len(FAN_OUT) - 1:
+                w[f"blk{mb}_indptr"], w[f"blk{mb}_indices"] = sip, six
+            else:
+                fresh = np.setdiff1d(np.unique(six), frontier)
+                frontier = np.concatenate([frontier, fresh])
+    try:
+        os.makedirs(cache, exist_ok=True)
+        for n in names:
+            np.save(os.path.join(cache, n + ".npy"), np.ascontiguousarray(w[n]))
+        np.save(os.path.join(cache, "graph_indptr.npy"), ip_np)
+        np.save(os.path.join(cache, "graph_indices.npy"), ix_np)
+        open(done, "w").write("ok")
+    except OSError:
+        pass  # no cache: the next arm generates again
+    if need_graph:
+        w["graph_indptr"], w["graph_indices"] = ip_np, ix_np
+    return w
+
+
+def shared_config(w):
+    n_edges = statistics.mean(int(w[f"blk{i}_indices"].shape[0]) for i in range(N_MINIBATCHES))
+    n_dst = statistics.mean(int(w[f"blk{i}_indptr"].shape[0]) - 1 for i in range(N_MINIBATCHES))
+    return {"workload": WORKLOAD, "edges_per_block": int(n_edges), "dst_rows_per_block": int(n_dst), "index_dtype": "int64",
+            "minibatches_rotated": N_MINIBATCHES}
+
+
 # --------------------------------------------------------------------------------------------- ours
-def build_workload(device, rank, world):
+def build_workload(device, rank, world, dist):
+    """Tables and blocks on the device.  Rank 0 holds the CPU generator's six blocks; at N > 1 every other rank draws
+    its own six minibatches from the same (uploaded) graph with the GPU sampler (data parallel: own seeds per rank)."""
+    import numpy as np
     import torch
     from f2cgt_b200 import synth
-    indptr, indices = synth.power_law_graph(NUM_NODES, AVG_DEGREE, ZIPF, seed=0, device=device)
-    tables = {}
-    for bits in BITS:
-        tables[bits] = synth.sq_table_from_normal(NUM_NODES, FEAT_DIM, bits, COLUMN_SLICE, seed=0, device=device)
-    g = torch.Generator(device=device)
-    g.manual_seed(1000 + rank)  # every rank draws its own seed minibatches (data parallel)
-    blocks = []
-    for b in range(N_MINIBATCHES):
-        seeds = torch.randperm(NUM_NODES, generator=g, device=device)[:BATCH]
-        blk = synth.sample_blocks(indptr, indices, seeds, FAN_OUT, rng_seed=rank * 1000 + b)[0]
-        blocks.append((blk["indptr"].contiguous(), blk["indices_global"].contiguous()))
-        if world > 1:  # what the sharded modes need: the block's distinct source rows and block-local ids
-            BLOCK_EXTRA.append((blk["src_nodes"].contiguous(), blk["indices_local"].contiguous()))
-    del indptr, indices
-    torch.cuda.empty_cache()
-    return tables, blocks
-
-
-BLOCK_EXTRA = []
+    if world > 1:
+        if rank == 0:
+            cpu_workload(need_graph=True)  # fill the cache once; the other ranks read it after the barrier
+        dist.barrier()
+    w = cpu_workload(need_graph=world > 1 and rank != 0)
+    cb = torch.from_numpy(np.array(w["codebook"])).to(device)
+    tables = {b: (torch.from_numpy(np.array(w[f"codes{b}"])).to(device).view(torch.int8), cb) for b in BITS}
+    blocks, extra = [], []
+    if rank == 0:
+        for i in range(N_MINIBATCHES):
+            blocks.append((torch.from_numpy(np.array(w[f"blk{i}_indptr"])).to(device), torch.from_numpy(np.array(w[f"blk{i}_indices"])).to(device)))
+    else:
+        indptr = torch.from_numpy(np.array(w["graph_indptr"])).to(device)
+        indices = torch.from_numpy(np.array(w["graph_indices"])).to(device)
+        g = torch.Generator(device=device)
+        g.manual_seed(1000 + rank)
+        for b in range(N_MINIBATCHES):
+            seeds = torch.randperm(NUM_NODES, generator=g, device=device)[:BATCH]
+            blk = synth.sample_blocks(indptr, indices, seeds, FAN_OUT, rng_seed=rank * 1000 + b)[0]
+            blocks.append((blk["indptr"].contiguous(), blk["indices_global"].contiguous()))
+        del indptr, indices
+        torch.cuda.empty_cache()
+    if world > 1:  # what the all-to-all placement needs: the block's distinct source rows and block-local ids
+        from f2cgt_b200 import ops
+        for ip, ix in blocks:
+            src, (local,) = ops.tensor_relabel([ix])
+            extra.append((src.contiguous(), local.contiguous()))
+    return w, tables, blocks, extra
 
 
 def time_steps(step_fn, blocks, steps, warmup, flush, torch):
-    """Per-step CUDA events on the current stream; returns (list of step ms, edges done)."""
+    """Per-step CUDA events on the current stream; returns (sum of step ms, edges done)."""
     for w in range(warmup):
         step_fn(w % len(blocks))
         flush.sum()
@@ -141,16 +236,16 @@ def time_steps(step_fn, blocks, steps, warmup, flush, torch):
         torch.cuda.synchronize()
         ms.append(a.elapsed_time(b))
         edges += blocks[s % len(blocks)][1].numel() * len(BITS)
-    return ms, edges
+    return sum(ms), edges
 
 
-def multi_gpu_modes(args, capi, tables, blocks, flush, device, rank, world, torch, dist):
-    """Row-sharded table at N > 1: NCCL all-to-all fetch (what the task statement describes) and direct peer loads."""
+def sharded_placements(args, capi, tables, blocks, extra, flush, device, rank, world, torch, dist):
+    """Row-sharded table at N > 1: the fused kernel reading remote rows over NVLink (peer mappings), and the NCCL
+    all-to-all fetch followed by the kernel on block-local rows.  Each is checked once against the replicated table."""
     from f2cgt_b200 import ops, shard
     out = {}
     lo, hi = shard.shard_bounds(NUM_NODES, world, rank)
     shards = {b: tables[b][0][lo:hi].contiguous() for b in BITS}
-    # --- peer loads: every rank maps the other shards (CUDA IPC) and the kernel reads remote rows itself
     try:
         peers = {b: shard.PeerTable(shards[b], NUM_NODES) for b in BITS}
 
@@ -158,35 +253,84 @@ def multi_gpu_modes(args, capi, tables, blocks, flush, device, rank, world, torc
             ip, ix = blocks[i]
             for b in BITS:
                 ops.sq_decompress_spmm_csr_peer(peers[b], tables[b][1], ip, ix, b, COLUMN_SLICE, FEAT_DIM)
-        ms, edges = time_steps(step_peer, blocks, args.steps, args.warmup, flush, torch)
-        out["sharded_peer_loads"] = (sum(ms), edges)
-        # one-off check against the replicated table
+        out["sharded_peer_loads"] = time_steps(step_peer, blocks, args.steps, args.warmup, flush, torch)
         ip, ix = blocks[0]
-        a = ops.sq_decompress_spmm_csr_peer(peers[4], tables[4][1], ip, ix, 4, COLUMN_SLICE, FEAT_DIM)
-        bref = capi.sq_decompress_spmm_csr(tables[4][0], tables[4][1], ip, ix, 4, COLUMN_SLICE, FEAT_DIM)
-        assert torch.equal(a, bref), "peer-load result differs from the replicated table"
+        for b in BITS:
+            a = ops.sq_decompress_spmm_csr_peer(peers[b], tables[b][1], ip, ix, b, COLUMN_SLICE, FEAT_DIM)
+            ref = capi.sq_decompress_spmm_csr(tables[b][0], tables[b][1], ip, ix, b, COLUMN_SLICE, FEAT_DIM)
+            assert torch.equal(a, ref), f"peer-load result differs from the replicated table at {b} bits"
     except Exception as e:  # noqa: BLE001
         out["sharded_peer_loads_error"] = repr(e)[:300]
-    # --- NCCL all-to-all: owners gather rows, rows are exchanged, the kernel runs on block-local rows
     try:
         st = {b: shard.ShardedTable(shards[b], NUM_NODES) for b in BITS}
-        plans = [st[BITS[0]].plan(src) for src, _ in BLOCK_EXTRA]  # id exchange happens when the block is sampled
+        plans = [st[BITS[0]].plan(src) for src, _ in extra]  # the id exchange happens when the block is sampled
 
         def step_a2a(i):
             ip, _ = blocks[i]
-            _, ix_local = BLOCK_EXTRA[i]
+            _, ix_local = extra[i]
             for b in BITS:
                 rows = st[b].fetch_rows(plans[i])
                 capi.sq_decompress_spmm_csr(rows, tables[b][1], ip, ix_local, b, COLUMN_SLICE, FEAT_DIM)
-        ms, edges = time_steps(step_a2a, blocks, args.steps, args.warmup, flush, torch)
-        out["sharded_nccl_all_to_all"] = (sum(ms), edges)
+        out["sharded_nccl_all_to_all"] = time_steps(step_a2a, blocks, args.steps, args.warmup, flush, torch)
         rows = st[4].fetch_rows(plans[0])
-        a = capi.sq_decompress_spmm_csr(rows, tables[4][1], blocks[0][0], BLOCK_EXTRA[0][1], 4, COLUMN_SLICE, FEAT_DIM)
-        bref = capi.sq_decompress_spmm_csr(tables[4][0], tables[4][1], blocks[0][0], blocks[0][1], 4, COLUMN_SLICE, FEAT_DIM)
-        assert torch.equal(a, bref), "all-to-all result differs from the replicated table"
+        a = capi.sq_decompress_spmm_csr(rows, tables[4][1], blocks[0][0], extra[0][1], 4, COLUMN_SLICE, FEAT_DIM)
+        ref = capi.sq_decompress_spmm_csr(tables[4][0], tables[4][1], blocks[0][0], blocks[0][1], 4, COLUMN_SLICE, FEAT_DIM)
+        assert torch.equal(a, ref), "all-to-all result differs from the replicated table"
     except Exception as e:  # noqa: BLE001
         out["sharded_nccl_all_to_all_error"] = repr(e)[:300]
     return out
+
+
+def parity_check(capi, tables, blocks, torch):
+    """Block 0 of the timed workload (global-id gathers into the 2.45 M-row table, ~0.8 M power-law edges): every width
+    against the reference's own CUDA kernel when its build is present, else against decode-then-aggregate of the block's
+    distinct source rows with this library's unfused operators (the reference's own test property)."""
+    from f2cgt_b200 import ops
+    out = {}
+    ip, ix = blocks[0]
+    try:
+        from oracle import build_ref
+        ref = build_ref.load()
+    except Exception:  # noqa: BLE001
+        ref = None
+    src, (local,) = ops.tensor_relabel([ix])
+    for bits in BITS:
+        codes, cb = tables[bits]
+        got = capi.sq_decompress_spmm_csr(codes, cb, ip, ix, bits, COLUMN_SLICE, FEAT_DIM)
+        unfused = capi.spmm_csr(capi.sq_decompress(codes[src].contiguous(), cb, bits, COLUMN_SLICE, FEAT_DIM), ip, local)
+        ok = torch.equal(got, unfused)
+        how = "bit-exact vs decode-then-aggregate"
+        if ref is not None:
+            want = ref.sq_decompress_spmm_csr(codes, cb, ip, ix, bits, COLUMN_SLICE, FEAT_DIM)
+            torch.cuda.synchronize()
+            ok = ok and torch.equal(got, want)
+            how = "bit-exact vs the reference's CUDA kernel and vs decode-then-aggregate"
+        out[f"sq{bits}"] = how if ok else "MISMATCH"
+    return out
+
+
+def two_level_parity(torch):
+    """The two-level single launch on a block of the same shape against its composition (decode every source row by its
+    own codec with the unfused operators, then the plain mean): bit-equal."""
+    from f2cgt_b200 import ops, synth
+    dev = torch.device("cuda", torch.cuda.current_device())
+    n = 200_000
+    indptr, indices = synth.power_law_graph(n, 50, 2.1, seed=3, device=dev)
+    g = torch.Generator(device=dev); g.manual_seed(7)
+    seeds = torch.randperm(n, generator=g, device=dev)[:1024]
+    blk = synth.sample_blocks(indptr, indices, seeds, FAN_OUT, rng_seed=3)[0]
+    ip, ix = blk["indptr"].contiguous(), blk["indices_global"].contiguous()
+    vq = torch.randint(0, 256, (n, 4), generator=g, dtype=torch.uint8, device=dev)
+    cbs = torch.randn(4, 256, 32, generator=g, device=dev)
+    deg = indptr[1:] - indptr[:-1]
+    hot = torch.topk(deg, n // 20).indices
+    slot = torch.full((n,), -1, dtype=torch.int32, device=dev)
+    slot[hot] = torch.arange(hot.numel(), dtype=torch.int32, device=dev)
+    sq_hot, sq_cb = synth.sq_table_from_normal(hot.numel(), FEAT_DIM, 8, FEAT_DIM, seed=1, device=dev)
+    got = ops.two_level_decompress_spmm_csr(sq_hot, sq_cb, 8, FEAT_DIM, vq, cbs, slot, ip, ix, FEAT_DIM)
+    full = ops.vq_decompress(vq, cbs, FEAT_DIM)
+    full[hot] = ops.sq_decompress(sq_hot, sq_cb, 8, FEAT_DIM, FEAT_DIM)
+    return "bit-exact vs composition of the unfused decoders + spmm_csr" if torch.equal(got, ops.spmm_csr(full, ip, ix)) else "MISMATCH"
 
 
 def run_ours(args):
@@ -201,20 +345,18 @@ def run_ours(args):
     device = torch.device("cuda", local_rank)
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
-    tables, blocks = build_workload(device, rank, world)
+    w, tables, blocks, extra = build_workload(device, rank, world, dist)
     flush = torch.zeros(64 << 20, dtype=torch.float32, device=device)  # 256 MiB, read (not written) to evict L2
 
-    def step_device(blk, out_sink=None):
-        ip, ix = blk
-        outs = []
+    def step_device(i):
+        ip, ix = blocks[i]
         for bits in BITS:
             codes, cb = tables[bits]
-            outs.append(capi.sq_decompress_spmm_csr(codes, cb, ip, ix, bits, COLUMN_SLICE, FEAT_DIM))
-        return outs
+            capi.sq_decompress_spmm_csr(codes, cb, ip, ix, bits, COLUMN_SLICE, FEAT_DIM)
 
-    # ---- device-resident timing: per-step and per-kernel CUDA events on the launching (current) stream
-    for w in range(args.warmup):
-        step_device(blocks[w % len(blocks)])
+    # ---- replicated table, device-resident: per-step and per-kernel CUDA events on the launching (current) stream
+    for wu in range(args.warmup):
+        step_device(wu % len(blocks))
         flush.sum()
     torch.cuda.synchronize()
     if world > 1:
@@ -246,7 +388,6 @@ def run_ours(args):
     if world > 1:
         dist.barrier()
     wall = time.perf_counter() - wall0
-    clocks = sampler.stop() if rank == 0 else None
     total_ms = sum(step_ms)
 
     # ---- end to end through the public module with HOST buffers: pinned CSC in, aggregated rows out
@@ -267,8 +408,8 @@ def run_ours(args):
         torch.cuda.synchronize()
         return (hip.numel() + hix.numel()) * 8, n_dst * FEAT_DIM * 4 * len(BITS), hix.numel() * len(BITS)
 
-    for w in range(2):
-        step_e2e(host_blocks[w % len(host_blocks)])
+    for wu in range(2):
+        step_e2e(host_blocks[wu % len(host_blocks)])
     if world > 1:
         dist.barrier()
     torch.cuda.synchronize()
@@ -279,32 +420,65 @@ def run_ours(args):
         h2d += a; d2h += b; e2e_edges += c
     torch.cuda.synchronize()
     e2e_s = time.perf_counter() - t0
+    clocks = sampler.stop() if rank == 0 else None
 
     # ---- aggregate over ranks: max time, summed edges
-    stats = torch.tensor([total_ms, e2e_s, float(edges_done), float(e2e_edges)], dtype=torch.float64, device=device)
-    modes = {}
+    def reduce_rate(ms, edges):
+        if world == 1:
+            return edges / (ms * 1e-3)
+        t = torch.tensor([ms], dtype=torch.float64, device=device)
+        e = torch.tensor([float(edges)], dtype=torch.float64, device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX); dist.all_reduce(e, op=dist.ReduceOp.SUM)
+        return float(e[0]) / (float(t[0]) * 1e-3)
+
+    placements = {"replicated": reduce_rate(total_ms, edges_done)}
+    e2e_rate = reduce_rate(e2e_s * 1e3, e2e_edges)
+    value, value_ms, placement_of_value = placements["replicated"], total_ms, "replicated (one GPU holds the whole table)"
     if world > 1:
-        mx = stats.clone(); dist.all_reduce(mx, op=dist.ReduceOp.MAX)
-        sm = stats.clone(); dist.all_reduce(sm, op=dist.ReduceOp.SUM)
-        total_ms, e2e_s = float(mx[0]), float(mx[1])
-        edges_all, e2e_edges_all = float(sm[2]), float(sm[3])
-        modes["replicated"] = edges_all / (total_ms * 1e-3)
-        raw = multi_gpu_modes(args, capi, tables, blocks, flush, device, rank, world, torch, dist)
+        raw = sharded_placements(args, capi, tables, blocks, extra, flush, device, rank, world, torch, dist)
         for name in ("sharded_peer_loads", "sharded_nccl_all_to_all"):
             ok = torch.tensor([1.0 if name in raw else 0.0], dtype=torch.float64, device=device)
             dist.all_reduce(ok, op=dist.ReduceOp.MIN)
             if float(ok[0]) == 1.0:
-                t = torch.tensor([raw[name][0]], dtype=torch.float64, device=device)
-                e = torch.tensor([float(raw[name][1])], dtype=torch.float64, device=device)
-                dist.all_reduce(t, op=dist.ReduceOp.MAX); dist.all_reduce(e, op=dist.ReduceOp.SUM)
-                modes[name] = float(e[0]) / (float(t[0]) * 1e-3)
+                placements[name] = reduce_rate(*raw[name])
             elif rank == 0 and name + "_error" in raw:
-                modes[name + "_error"] = raw[name + "_error"]
-    else:
-        edges_all, e2e_edges_all = float(edges_done), float(e2e_edges)
+                placements[name + "_error"] = raw[name + "_error"]
+        if "sharded_peer_loads" in placements:  # the headline at N > 1: the table really partitioned, 1/N of the rows per GPU
+            value = placements["sharded_peer_loads"]
+            tmax = torch.tensor([raw["sharded_peer_loads"][0]], dtype=torch.float64, device=device)
+            dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
+            value_ms = float(tmax[0])
+            placement_of_value = "row-sharded over the GPUs, the fused kernel reads remote rows over NVLink (peer mappings, no collective)"
+        elif "sharded_nccl_all_to_all" in placements:
+            value = placements["sharded_nccl_all_to_all"]
+            tmax = torch.tensor([raw["sharded_nccl_all_to_all"][0]], dtype=torch.float64, device=device)
+            dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
+            value_ms = float(tmax[0])
+            placement_of_value = "row-sharded over the GPUs, rows fetched with an NCCL all-to-all before the fused kernel"
+
+    # ---- GraphSAGE epoch (second half of the metric): replicated and sharded table, same process group
+    epoch = []
+    if not args.no_epoch:
+        from f2cgt_b200 import train_graphsage
+        del flush
+        torch.cuda.empty_cache()
+        for table in ("replicated", "sharded"):
+            if table == "sharded" and world == 1:
+                continue
+            try:
+                rec = train_graphsage.train("small", table, rank, world, local_rank, epochs=2, min_timed_steps=100)
+                epoch.append({"table": table, "ms_per_step": rec["ms_per_step"], "s_per_epoch": rec["value"], "steps": rec["steps_per_epoch_per_gpu"],
+                              "timed_steps": rec["timed_steps_per_gpu"], "breakdown_ms": rec["breakdown_ms"],
+                              "graph": "2,449,029 nodes, mean degree 50 (the 111 M-node graph of the two-level configuration is not built here)",
+                              "codecs": "two-level: hot 5 % SQ 8 bits + VQ 4 x 32 (ratio 128), D = 128, 172 classes, 122,880 training ids "
+                                        "split over the ranks, batch 1024, fan-out 12,12,12, dropout 0.5, bf16 autocast"})
+            except Exception as e:  # noqa: BLE001
+                epoch.append({"table": table, "error": repr(e)[:300]})
+        flush = torch.zeros(64 << 20, dtype=torch.float32, device=device)
 
     if rank == 0:
         peak, peak_kind = measured_peak()
+        cfg = shared_config(w)
         n_edges = statistics.mean(ix.numel() for _, ix in blocks)
         n_dst = statistics.mean(ip.numel() - 1 for ip, _ in blocks)
         variants = {}
@@ -315,32 +489,43 @@ def run_ours(args):
             variants[f"sq{bits}"] = {"ms": round(ms, 5), "edges_per_s": n_edges / (ms * 1e-3), "algorithmic_bytes": int(byts),
                                      "gbs": byts / (ms * 1e-3) / 1e9, "frac_of_peak": byts / (ms * 1e-3) / 1e9 / peak}
         dom = variants["sq4"]
+        parity = parity_check(capi, tables, blocks, torch)
+        try:
+            parity["two_level_sq8_vq4x32"] = two_level_parity(torch)
+        except Exception as e:  # noqa: BLE001
+            parity["two_level_sq8_vq4x32"] = "not run: " + repr(e)[:120]
+        from f2cgt_b200 import ops
+        parity["device_status"] = ops.device_status()
         line = {
-            "metric": METRIC, "value": edges_all / (total_ms * 1e-3), "unit": "edges/s", "n_gpus": world, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": total_ms / args.steps, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": "u8 codes -> f32", "data": "synthetic",
-            "config": {"workload": "SQ 1/2/4-bit packed table 2449029x128 (N(0,1) features), power-law graph (Zipf 2.1, mean degree 50), "
-                                   "1024 seeds x fan-out 12,12,12, outermost block, one fused launch per width per step",
-                       "edges_per_block": int(n_edges), "dst_rows_per_block": int(n_dst), "index_dtype": "int64",
-                       "gather": "global ids into the HBM-resident table", "minibatches_rotated": len(blocks),
-                       "l2": "256 MiB read sweep between steps (outside the step's event pair) evicts L2; tables 39/78/157 MB",
-                       "table": "replicated per GPU (157 MB at 4 bits); the row-sharded placements are timed beside it at N>1 "
-                                "and reported in table_placements_edges_per_s", "timing": "CUDA events on the launching stream, max over ranks"},
-            "roofline": {"bound": "hbm", "kernel": "sq_spmm_kernel<4-bit>", "achieved": dom["gbs"], "peak": peak, "unit": "GB/s",
-                         "frac": dom["frac_of_peak"], "traffic": NCU_DRAM_TRAFFIC_BYTES[4], "traffic_unit": "bytes/launch (ncu dram read+write, profiles/sq_spmm_bench_block.md)", "algorithmic_bytes": dom["algorithmic_bytes"], "peak_source": f"MEASURED_PEAKS.json hbm_gbs ({peak_kind})"},
+            "metric": METRIC, "value": value, "unit": "edges/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": value_ms / args.steps, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "u8 codes -> f32", "data": "synthetic", "config": cfg,
+            "arm_details": {
+                "gather": "global ids into the HBM-resident table", "table_placement_of_value": placement_of_value,
+                "l2": "256 MiB read sweep between steps (outside the step's event pair) evicts L2; tables 39/78/157 MB",
+                "timing": "CUDA events on the launching stream, max over ranks; one fused launch per width per step",
+                "kernels": "sq_spmm_kernel<1>, sq_stream_kernel<2>, sq_spmm_kernel<4> (library's choice per width)"},
+            "roofline": {"bound": "hbm", "kernel": "sq_spmm_kernel<4-bit> (replicated table, one GPU)", "achieved": dom["gbs"], "peak": peak,
+                         "unit": "GB/s", "frac": dom["frac_of_peak"], "traffic": NCU_DRAM_TRAFFIC_BYTES_SQ4,
+                         "traffic_unit": "bytes/launch: ncu dram read+write of one 4-bit launch on a block of this generator, from an "
+                                         "earlier capture, not measured in this run", "algorithmic_bytes": dom["algorithmic_bytes"],
+                         "peak_source": f"MEASURED_PEAKS.json hbm_gbs ({peak_kind})"},
             "variants": variants,
-            "e2e": {"value": e2e_edges_all / e2e_s, "unit": "edges/s", "h2d_bytes_per_step": h2d // e2e_steps,
+            "e2e": {"value": e2e_rate, "unit": "edges/s", "h2d_bytes_per_step": h2d // e2e_steps,
                     "d2h_bytes_per_step": d2h // e2e_steps, "steps": e2e_steps,
-                    "what": "pinned-host CSC -> device, 3 fused launches via F2CGTLib, aggregated rows -> pinned host"},
-            "gpu_launches": args.steps * len(BITS), "table_placements_edges_per_s": modes,
-            "clocks": clocks, "wall_s_timed_region": wall,
+                    "what": "pinned-host CSC -> device, 3 fused launches via F2CGTLib (replicated table), aggregated rows -> pinned host"},
+            "gpu_launches": args.steps * len(BITS), "table_placements_edges_per_s": placements, "parity_check": parity,
+            "epoch": epoch, "clocks": clocks, "wall_s_timed_region": wall,
         }
         if world == 1 and not args.no_cpu_baseline:
-            line["cpu_baseline"] = cpu_leg(blocks[0], steps=1, warmup=1, tables_dev=tables)
+            line["cpu_baseline"] = cpu_leg(w, steps=1, warmup=1)
         if world == 1:
-            line["reference_cuda_kernels"] = reference_cuda_leg(tables, blocks)
+            line["reference_cuda_kernels"] = reference_cuda_leg(tables, blocks, flush)
             line["other_fused_kernels"] = other_kernels_leg()
         emit(line)
+        if any(v == "MISMATCH" for v in parity.values()):
+            sys.stderr.write("bench.py: parity check failed\n")
+            sys.exit(1)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
@@ -360,9 +545,11 @@ def other_kernels_leg():
         return {"unavailable": repr(e)[:200]}
 
 
-def reference_cuda_leg(tables, blocks):
-    """The reference's own CUDA kernel for the same op on the same GPU (extension built from its sources
-    by oracle/build_ref.py), for context; absent when that extension was not built."""
+def reference_cuda_leg(tables, blocks, flush):
+    """The reference's own CUDA kernel for the same op on the same GPU and block (extension built from its sources by
+    oracle/build_ref.py), timed like ours: CUDA events on the stream it launches on (the legacy default stream, which
+    is torch's current stream here), cold L2, launch path hidden behind a parked GPU; its output allocation
+    (torch::zeros, a memset on the same stream) is part of its operator and inside the events."""
     import torch
     try:
         from oracle import build_ref
@@ -373,28 +560,47 @@ def reference_cuda_leg(tables, blocks):
     ip, ix = blocks[0]
     for bits in BITS:
         codes, cb = tables[bits]
-        for _ in range(2):
+        for _ in range(2):  # also pre-touches the caching allocator for the output shape
             ref.sq_decompress_spmm_csr(codes, cb, ip, ix, bits, COLUMN_SLICE, FEAT_DIM)
+            flush.sum()
         torch.cuda.synchronize()
-        t0 = time.perf_counter()
+        ms = []
         for _ in range(5):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda._sleep(250_000)
+            a.record()
             ref.sq_decompress_spmm_csr(codes, cb, ip, ix, bits, COLUMN_SLICE, FEAT_DIM)
-        torch.cuda.synchronize()
-        out[f"sq{bits}_ms"] = (time.perf_counter() - t0) / 5 * 1e3
-    out["note"] = "warm L2, includes its torch::zeros output allocation, legacy default stream"
+            b.record()
+            flush.sum()
+            torch.cuda.synchronize()
+            ms.append(a.elapsed_time(b))
+        out[f"sq{bits}_ms"] = statistics.median(ms)
+    out["note"] = "CUDA events on its (legacy default) stream, cold L2, block 0, includes its zero-fill of the output"
     return out
 
 
 # --------------------------------------------------------------------------------------------- CPU
-def cpu_leg(block, steps, warmup, tables_dev=None, tables_host=None):
-    """Reference PyTorch CPU path on blocks[0] of one minibatch, all three widths per step."""
+def cpu_tables(w):
+    import numpy as np
+    import torch
+    cb = torch.from_numpy(np.array(w["codebook"]))
+    return {b: (torch.from_numpy(np.array(w[f"codes{b}"])), cb) for b in BITS}
+
+
+def cpu_blocks(w):
+    import numpy as np
+    import torch
+    return [(torch.from_numpy(np.array(w[f"blk{i}_indptr"])), torch.from_numpy(np.array(w[f"blk{i}_indices"]))) for i in range(N_MINIBATCHES)]
+
+
+def cpu_leg(w, steps, warmup):
+    """Reference PyTorch CPU path on block 0, all three widths per step."""
     import torch
     from oracle import torch_cpu_path as T
     cores = os.cpu_count() or 1
     torch.set_num_threads(cores)
-    ip, ix = block[0].cpu(), block[1].cpu()
-    if tables_host is None:
-        tables_host = {b: (t[0].cpu().view(torch.uint8), t[1].cpu()) for b, t in tables_dev.items()}
+    tables_host = cpu_tables(w)
+    ip, ix = cpu_blocks(w)[0]
     times = []
     for s in range(warmup + steps):
         t0 = time.perf_counter()
@@ -405,55 +611,23 @@ def cpu_leg(block, steps, warmup, tables_dev=None, tables_host=None):
             times.append(time.perf_counter() - t0)
     sec = statistics.mean(times)
     return {"value": ix.numel() * len(BITS) / sec, "unit": "edges/s", "cores": cores, "kind": "port",
-            "sample": f"one full step (blocks[0] of one minibatch, {ix.numel()} edges, widths 1/2/4), {steps} timed after {warmup} warm-up",
+            "sample": f"one full step (block 0, {ix.numel()} edges, widths 1/2/4), {steps} timed after {warmup} warm-up",
             "seconds_per_step": sec, "impl": "torch CPU: gather rows, shift/mask unpack, exp2 decode, sparse CSR mean matmul"}
 
 
 def run_reference(args):
-    """Reference arm: the whole configuration on the host - graph, table, sampler and the timed path all
-    on CPU (torch + the oracle's sampler); nothing of the CUDA library is loaded."""
+    """Reference arm: the reference's PyTorch-level CPU path (oracle/torch_cpu_path.py) on the same tables and the same
+    six blocks as the GPU arm, all host threads; nothing of the CUDA library is loaded."""
     rank = int(os.environ.get("RANK", 0))
     if rank != 0:
         return
-    import numpy as np
     import torch
-    from oracle import oracle as O
     from oracle import torch_cpu_path as T
     cores = os.cpu_count() or 1
     torch.set_num_threads(cores)
-    # graph: same generator as the GPU arm, on the CPU device
-    g = torch.Generator(); g.manual_seed(0)
-    u = torch.rand(NUM_NODES, generator=g, dtype=torch.float64).clamp_min(1e-12)
-    raw = u.pow(-1.0 / (ZIPF - 1.0)).clamp_max(NUM_NODES // 20)
-    deg = torch.floor(raw * (AVG_DEGREE / float(raw.mean()))).to(torch.int64)
-    indptr = torch.zeros(NUM_NODES + 1, dtype=torch.int64)
-    torch.cumsum(deg, 0, out=indptr[1:])
-    nnz = int(indptr[-1])
-    indices = torch.empty(nnz, dtype=torch.int64)
-    for s in range(0, nnz, 1 << 25):
-        e = min(s + (1 << 25), nnz)
-        indices[s:e] = torch.searchsorted(indptr, torch.randint(0, nnz, (e - s,), generator=g), right=True) - 1
-    ip_np, ix_np = indptr.numpy(), indices.numpy()
-    # tables: codes of N(0,1) features, encoded chunk-wise with the oracle's compressor
-    sample = torch.randn((250_000, FEAT_DIM), generator=g).numpy()
-    cb = O.sq_codebooks(sample, COLUMN_SLICE)
-    tables = {b: [] for b in BITS}
-    for s in range(0, NUM_NODES, 1 << 18):
-        x = torch.randn((min(1 << 18, NUM_NODES - s), FEAT_DIM), generator=g).numpy()
-        for b in BITS:
-            tables[b].append(O.sq_codes_to_storage(O.sq_compress(x, cb, b, COLUMN_SLICE), b))
-    tables_host = {b: (torch.from_numpy(np.concatenate(v)), torch.from_numpy(cb)) for b, v in tables.items()}
-    # minibatch blocks with the oracle's sampler
-    blocks = []
-    for mb in range(2):
-        frontier = torch.randperm(NUM_NODES, generator=g)[:BATCH].numpy()
-        for hop, pick in enumerate(reversed(FAN_OUT)):
-            sip, six = O.sample_neighbors(ip_np, ix_np, frontier, pick, mb, hop)
-            if hop == len(FAN_OUT) - 1:
-                blocks.append((torch.from_numpy(sip), torch.from_numpy(six)))
-            else:
-                fresh = np.setdiff1d(np.unique(six), frontier)
-                frontier = np.concatenate([frontier, fresh])
+    w = cpu_workload()
+    tables_host = cpu_tables(w)
+    blocks = cpu_blocks(w)
     times, edges = [], 0
     for s in range(args.warmup + args.steps):
         ip, ix = blocks[s % len(blocks)]
@@ -466,13 +640,10 @@ def run_reference(args):
             edges += ix.numel() * len(BITS)
     total = sum(times)
     value = edges / total
-    n_edges = statistics.mean(ix.numel() for _, ix in blocks)
     line = {"impl": "reference", "metric": METRIC, "value": value, "unit": "edges/s", "n_gpus": int(os.environ.get("WORLD_SIZE", 1)),
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": total / args.steps * 1e3, "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": "u8 codes -> f32", "data": "synthetic",
-            "config": {"workload": "SQ 1/2/4-bit packed table 2449029x128 (N(0,1) features), power-law graph (Zipf 2.1, mean degree 50), "
-                                   "1024 seeds x fan-out 12,12,12, outermost block, all three widths per step",
-                       "edges_per_block": int(n_edges), "index_dtype": "int64"},
+            "scaling": "weak", "vs_baseline": None, "dtype": "u8 codes -> f32", "data": "synthetic", "config": shared_config(w),
+            "arm_details": {"what": "torch CPU: gather the block's distinct source rows, shift/mask unpack, exp2 decode, sparse CSR mean matmul"},
             "cpu_baseline": {"value": value, "unit": "edges/s", "cores": cores, "kind": "port",
                              "sample": "every step is one full block at all three widths (no sub-sampling)"},
             "e2e": {"value": value, "unit": "edges/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
@@ -497,6 +668,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-epoch", action="store_true", help="skip the GraphSAGE epoch records")
     args = ap.parse_args()
     # Libraries (NCCL's version banner, for one) write to file descriptor 1; the JSON line must be the only thing
     # on stdout, so everything else is sent to stderr and the line is written to the saved descriptor.

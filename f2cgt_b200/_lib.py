@@ -50,6 +50,7 @@ SIGNATURES = {
     "f2c_sq_decompress": [p, ci, p, i64, p, i64, i64, i64, ci, i64, p],
     "f2c_vq_decompress": [p, ci, p, ci, p, i64, i64, i64, i64, i64, p],
     "f2c_spmm_csr": [p, ci, p, p, ci, p, i64, i64, ci, p],
+    "f2c_spmm_csr_backward": [p, p, p, ci, p, i64, i64, i64, ci, p],
     "f2c_sq_spmm_csr": [p, ci, p, i64, p, p, ci, p, i64, i64, i64, i64, ci, i64, ci, EP, p],
     "f2c_sq_spmm_csr_peer": [p, ci, i64, ci, p, i64, p, p, ci, p, i64, i64, i64, i64, ci, i64, ci, EP, p],
     "f2c_shard_create": [p, i64, p, p, p],

@@ -118,6 +118,67 @@ extern "C" int f2c_spmm_csr(const void* feat, int feat_dtype, const void* indptr
 #undef F2C_SP
 }
 
+// ---------------------------------------------------------------- backward of the mean / sum aggregation
+// grad_src[indices[k], :] += grad_out[d, :] * w(d) for every edge k of destination row d, w = 1 / max(deg, 1) for the
+// mean.  This is what autograd needs for the hidden GraphSAGE layers (the reference gets it from DGL's SAGEConv,
+// examples/models.py:31); the fused first layer has no gradient through its aggregation (its input is codes).
+// One warp per destination row; a lane owns float4 pieces of the row and adds them with vector reductions
+// (red.global.add.v4.f32), so the transposed block is never built.  Summation order over a source row's edges is
+// whatever the reductions land in: results agree with the transposed-CSC form up to fp32 rounding.
+namespace f2c {
+__device__ __forceinline__ void red_add_f4(float* p, float4 v) {
+  asm volatile("red.global.add.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(p), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
+}
+
+template <typename IdxT, bool VEC4>
+__global__ void __launch_bounds__(256) spmm_backward_kernel(const float* __restrict__ grad_out, float* __restrict__ grad_src,
+                                                            const IdxT* __restrict__ indptr, const IdxT* __restrict__ indices,
+                                                            int64_t n_dst, int feat_dim, int reduce) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int64_t n_warps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+  for (int64_t d = warp; d < n_dst; d += n_warps) {
+    const int64_t begin = (int64_t)indptr[d], end = (int64_t)indptr[d + 1];
+    if (end == begin) continue;
+    const float w = reduce == F2C_MEAN ? 1.0f / (float)(end - begin) : 1.0f;
+    if (VEC4) {
+      for (int c = lane * 4; c < feat_dim; c += 128) {
+        float4 g = *reinterpret_cast<const float4*>(grad_out + d * feat_dim + c);
+        g.x *= w; g.y *= w; g.z *= w; g.w *= w;
+        for (int64_t k = begin; k < end; ++k) red_add_f4(grad_src + (int64_t)indices[k] * feat_dim + c, g);
+      }
+    } else {
+      for (int c = lane; c < feat_dim; c += 32) {
+        const float g = grad_out[d * feat_dim + c] * w;
+        for (int64_t k = begin; k < end; ++k) atomicAdd(grad_src + (int64_t)indices[k] * feat_dim + c, g);
+      }
+    }
+  }
+}
+}  // namespace f2c
+
+extern "C" int f2c_spmm_csr_backward(const float* grad_out, const void* indptr, const void* indices, int index_dtype,
+                                     float* grad_src, int64_t n_dst, int64_t n_src, int64_t feat_dim, int reduce, void* stream) {
+  F2C_REQUIRE(n_dst >= 0 && n_src >= 0 && feat_dim >= 0, F2C_ERR_INVALID, "spmm_csr_backward: negative size");
+  F2C_REQUIRE(is_index_dtype(index_dtype), F2C_ERR_UNSUPPORTED, "spmm_csr_backward: indptr/indices must be int32 or int64");
+  F2C_REQUIRE(reduce == F2C_MEAN || reduce == F2C_SUM, F2C_ERR_INVALID, "spmm_csr_backward: reduce must be mean or sum");
+  F2C_REQUIRE(feat_dim < (1ll << 24), F2C_ERR_LIMIT, "spmm_csr_backward: feat_dim too large");
+  if (n_src * feat_dim == 0) return F2C_OK;
+  F2C_REQUIRE(grad_src != nullptr && (n_dst * feat_dim == 0 || (grad_out && indptr)), F2C_ERR_INVALID, "spmm_csr_backward: null pointer");
+  cudaStream_t st = (cudaStream_t)stream;
+  cudaError_t e = cudaMemsetAsync(grad_src, 0, (size_t)n_src * feat_dim * sizeof(float), st);
+  if (e != cudaSuccess) return set_error(F2C_ERR_CUDA, "spmm_csr_backward: %s", cudaGetErrorString(e));
+  if (n_dst == 0) return F2C_OK;
+  int64_t blocks = ceil_div(n_dst, 8);
+  if (blocks > current_sm_count() * 16) blocks = current_sm_count() * 16;
+  const bool vec = feat_dim % 4 == 0 && aligned(grad_out, 16) && aligned(grad_src, 16);
+#define F2C_BW(T, V) spmm_backward_kernel<T, V><<<(unsigned)blocks, 256, 0, st>>>(grad_out, grad_src, (const T*)indptr, (const T*)indices, n_dst, (int)feat_dim, reduce)
+  if (index_dtype == F2C_I32) { if (vec) F2C_BW(int32_t, true); else F2C_BW(int32_t, false); }
+  else { if (vec) F2C_BW(int64_t, true); else F2C_BW(int64_t, false); }
+#undef F2C_BW
+  return check_launch("spmm_csr_backward");
+}
+
 // ---------------------------------------------------------------- CSC sanity check (debug helper)
 namespace f2c {
 template <typename IdxT>

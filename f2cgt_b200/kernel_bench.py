@@ -180,6 +180,31 @@ def cases(b):
             del slot, sq_hot
         del vq
 
+    # ------------------------------------------------ two-level, configuration-5 codecs: D = 256, hot 2 % SQ 4 bits + VQ 4 x 64
+    # (256 KB of codebooks: two column parts), fan-out 15,10,5 (outermost hop takes 15).  The table has the rows of this
+    # benchmark's 2.45 M-node graph; the configuration's own graph (65.6 M nodes, 3.6 B edges) is too large to build here.
+    if b.wanted("two_level_spmm_sq4_vq4x64_config5", "vq_spmm_config5_4x64"):
+        D5 = 256
+        ip5, ix5 = b.block(fan_out=(15, 10, 5))
+        E5, n5 = ix5.numel(), ip5.numel() - 1
+        vq5 = torch.randint(0, 256, (N, 4), generator=g, dtype=torch.uint8, device=dev)
+        cbs5 = torch.randn(4, 256, 64, generator=g, device=dev)
+        b.run("vq_spmm_config5_4x64", lambda: ops.vq_decompress_spmm_csr(vq5, cbs5, ip5, ix5, D5),
+              nbytes=fused_bytes(E5, n5, 4, 8, D5, cbs5.numel() * 4), units=E5, note=f"E={E5} n_dst={n5} D=256, two column parts")
+        indptr, _ = b.graph()
+        deg = (indptr[1:] - indptr[:-1])
+        n_hot = N // 50
+        hot = torch.topk(deg, n_hot).indices
+        slot5 = torch.full((N,), -1, dtype=torch.int32, device=dev)
+        slot5[hot] = torch.arange(n_hot, dtype=torch.int32, device=dev)
+        sq5, sq5_cb = synth.sq_table_from_normal(n_hot, D5, 4, D5, seed=2, device=dev)
+        hot_edges = int((slot5[ix5] >= 0).sum())
+        nb5 = (E5 - hot_edges) * (4 + 8 + 4) + hot_edges * (128 + 8 + 4) + (n5 + 1) * 8 + n5 * D5 * 4 + cbs5.numel() * 4 + 20
+        b.run("two_level_spmm_sq4_vq4x64_config5",
+              lambda: ops.two_level_decompress_spmm_csr(sq5, sq5_cb, 4, D5, vq5, cbs5, slot5, ip5, ix5, D5),
+              nbytes=nb5, units=E5, note=f"E={E5} hot edges={hot_edges} n_dst={n5} D=256; 4 B/edge slot lookup counted")
+        del vq5, slot5, sq5
+
     # ------------------------------------------------ plain aggregation, dropout, packing, compress
     if not b.wanted("spmm_csr_f32", "dropout_inplace", "sq_compress_4bit", "packbits_4bit", "unpackbits_4bit") and \
             not b.wanted(*[f"kmeans_assign_d{d}_{m}" for d in (8, 32, 64) for m in ("l2", "cosine")]):

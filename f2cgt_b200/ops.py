@@ -193,6 +193,20 @@ def spmm_csr(feat, indptr, indices, reduce="mean"):
     return out
 
 
+def spmm_csr_backward(grad_out, indptr, indices, n_src, reduce="mean"):
+    """Gradient of ``spmm_csr(feat, indptr, indices)`` with respect to ``feat`` (float32 [n_src, D]): every edge adds
+    ``grad_out[d] / max(deg(d), 1)`` (mean) or ``grad_out[d]`` (sum) to the row of its source."""
+    _chk(grad_out, "grad_out", (torch.float32,))
+    n_dst = _csc(indptr, indices)
+    if grad_out.dim() != 2 or grad_out.shape[0] != n_dst:
+        raise RuntimeError("grad_out must be [n_dst, feat_dim]")
+    grad = torch.empty((int(n_src), grad_out.shape[1]), dtype=torch.float32, device=grad_out.device)
+    with _on(grad_out):
+        check(lib.f2c_spmm_csr_backward(_ptr(grad_out), _ptr(indptr), _ptr(indices), _DT[indptr.dtype], _ptr(grad), n_dst, int(n_src),
+                                        grad_out.shape[1], _REDUCE[reduce], _stream(grad_out)))
+    return grad
+
+
 def sq_decompress_spmm_csr(compress_feat, codebooks, indptr, indices, target_bit, column_slice, feat_dim, reduce="mean",
                            dropout=None, kernel="auto", check=False):
     """src/fusion_spmm.cu:240-272.  Fused SQ decode + mean aggregation -> float32 [n_dst, feat_dim]."""

@@ -111,7 +111,7 @@ def _linear_rows(fc, x):
 
 
 class _MeanAggregate(torch.autograd.Function):
-    """out[d] = mean over the block's neighbours of h[src]; backward scatters grad / deg along the transposed block."""
+    """out[d] = mean over the block's neighbours of h[src]; backward adds grad / deg to every neighbour's row."""
 
     @staticmethod
     def forward(ctx, h, indptr, indices, n_src):
@@ -122,18 +122,8 @@ class _MeanAggregate(torch.autograd.Function):
     @staticmethod
     def backward(ctx, grad_out):
         indptr, indices = ctx.saved_tensors
-        n_dst = indptr.numel() - 1
-        deg = (indptr[1:] - indptr[:-1]).clamp_min(1).to(grad_out.dtype)
-        scaled = (grad_out / deg[:, None]).contiguous()
-        # transposed block: edges sorted by source, destination of every edge as the "neighbour"
-        dst_of_edge = torch.repeat_interleave(torch.arange(n_dst, device=indptr.device, dtype=indptr.dtype), indptr[1:] - indptr[:-1],
-                                              output_size=indices.numel())
-        order = torch.argsort(indices, stable=True)
-        counts = torch.bincount(indices, minlength=ctx.n_src)
-        t_indptr = torch.zeros(ctx.n_src + 1, dtype=indptr.dtype, device=indptr.device)
-        torch.cumsum(counts, 0, out=t_indptr[1:])
-        grad_h = ops.spmm_csr(scaled, t_indptr, dst_of_edge[order].contiguous(), reduce="sum")
-        return grad_h, None, None, None
+        # one scatter kernel (vector reductions into the source rows) instead of building the transposed block
+        return ops.spmm_csr_backward(grad_out.float().contiguous(), indptr, indices, ctx.n_src), None, None, None
 
 
 class MySAGEConv(nn.Module):
@@ -147,7 +137,9 @@ class MySAGEConv(nn.Module):
         nn.init.xavier_uniform_(self.fc_neigh.weight, gain=gain)
 
     def forward(self, block, _unused=None):
-        sm, neighbours, dst = self.sm.for_block(block)
+        # (manager, neighbour ids, destination ids): fetched by the caller beforehand (so that a sharded table's row
+        # exchange can be timed and overlapped on its own) or here
+        sm, neighbours, dst = block.get("first_layer_input") or self.sm.for_block(block)
         h_neigh = sm.aggregate(block["indptr"], neighbours)  # raw codes in, no autograd through it
         h_self = sm.decode_rows(dst)
         return _linear_rows(self.fc_self, h_self) + _linear_rows(self.fc_neigh, h_neigh)

@@ -75,6 +75,95 @@ def build_data(cfg, device, index_dtype, table="replicated"):
     return indptr, indices, labels, train_ids, cm
 
 
+def train(preset="small", table="replicated", rank=0, world=1, local_rank=0, epochs=3, min_timed_steps=0, batch_size=1024, lr=0.003,
+          dropout=0.5, index_dtype="int64", max_steps=0, autocast=True):
+    """Train on the preset's synthetic data inside an already initialised process (and, for world > 1 or a sharded table,
+    process group); returns the record rank 0 reports (every rank gets it).  The first epoch is a discarded warm-up; when
+    ``min_timed_steps`` is set, enough further epochs are run to time at least that many steps per rank.  Per-phase device
+    times come from CUDA events on the current stream (sample / exchange / forward / backward / optimizer)."""
+    cfg = PRESETS[preset]
+    device = torch.device("cuda", local_rank)
+    idt = torch.int32 if index_dtype == "int32" else torch.int64
+    indptr, indices, labels, train_ids, cm = build_data(cfg, device, idt, table)
+
+    torch.manual_seed(0)
+    model = sage.SAGE(cfg["feat"], cfg["hidden"], cfg["classes"], len(cfg["fan_out"]), dropout, cm).to(device)
+    net = torch.nn.parallel.DistributedDataParallel(model, device_ids=[local_rank]) if world > 1 else model
+    optimizer = torch.optim.Adam(net.parameters(), lr=lr)
+    scheduler = torch.optim.lr_scheduler.ExponentialLR(optimizer, gamma=0.978)
+    loader = sage.GPUSamplingDataloader(indptr, indices, train_ids, batch_size, cfg["fan_out"], rank, world, shuffle=True)
+    steps = torch.tensor([len(loader)], device=device)
+    if world > 1:
+        dist.all_reduce(steps, op=dist.ReduceOp.MIN)  # every rank takes the same number of steps (gradient all-reduce)
+    steps = int(steps.item())
+    if max_steps:
+        steps = min(steps, max_steps)
+    if min_timed_steps:
+        epochs = max(epochs, 1 + (min_timed_steps + steps - 1) // steps)
+
+    phases = ("sample", "exchange", "forward", "backward", "optimizer")
+    epoch_s, losses, edges = [], [], 0
+    phase_ms = {k: 0.0 for k in phases}
+    timed_steps = 0
+    for epoch in range(epochs):
+        net.train()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        t0 = time.perf_counter()
+        it = iter(loader)
+        marks = []
+        for step in range(steps):
+            ev = [torch.cuda.Event(enable_timing=True) for _ in range(6)]
+            ev[0].record()
+            input_nodes, output_nodes, blocks = next(it)
+            y = labels[output_nodes]
+            ev[1].record()
+            blocks[0]["first_layer_input"] = cm.for_block(blocks[0])  # sharded table: the row exchange of this minibatch
+            ev[2].record()
+            with torch.autocast("cuda", dtype=torch.bfloat16, enabled=autocast):
+                pred = net(blocks)
+            loss = F.cross_entropy(pred.float(), y)
+            ev[3].record()
+            optimizer.zero_grad(set_to_none=True)
+            loss.backward()
+            ev[4].record()
+            optimizer.step()
+            ev[5].record()
+            marks.append(ev)
+            if epoch == epochs - 1:
+                edges += blocks[0]["indices_global"].numel()
+        scheduler.step()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        epoch_s.append(time.perf_counter() - t0)
+        losses.append(float(loss.detach()))
+        if epoch > 0 or epochs == 1:
+            timed_steps += steps
+            for ev in marks:
+                for i, k in enumerate(phases):
+                    phase_ms[k] += ev[i].elapsed_time(ev[i + 1])
+    timed = epoch_s[1:] if len(epoch_s) > 1 else epoch_s
+    stats = torch.tensor([sum(timed) / len(timed), float(edges)] + [phase_ms[k] / max(timed_steps, 1) for k in phases], device=device,
+                         dtype=torch.float64)
+    if world > 1:
+        mx = stats.clone(); dist.all_reduce(mx, op=dist.ReduceOp.MAX)
+        sm = stats.clone(); dist.all_reduce(sm, op=dist.ReduceOp.SUM)
+        stats = torch.cat([mx[:1], sm[1:2], mx[2:]])
+    stats = stats.tolist()
+    return {
+        "metric": "graphsage_epoch_seconds", "value": stats[0], "unit": "s/epoch", "n_gpus": world, "preset": preset,
+        "steps_per_epoch_per_gpu": steps, "timed_steps_per_gpu": timed_steps, "batch_size": batch_size, "epochs_run": epochs,
+        "epoch_seconds_all": [round(t, 4) for t in epoch_s], "ms_per_step": stats[0] / steps * 1e3,
+        "breakdown_ms": {k: round(v, 4) for k, v in zip(phases, stats[2:])},
+        "first_layer_edges_per_s": stats[1] / stats[0], "loss_last_step_per_epoch": [round(v, 4) for v in losses],
+        "config": {k: (list(v) if isinstance(v, tuple) else v) for k, v in cfg.items()}, "index_dtype": index_dtype,
+        "autocast_bf16": autocast, "table": table, "data": "synthetic", "scaling": "strong (train ids split over ranks)",
+        "timing": "wall clock around barrier + synchronize delimited epochs, first epoch discarded, max over ranks; breakdown = CUDA "
+                  "events on the current stream, mean per step, max over ranks"}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--preset", default="small", choices=sorted(PRESETS))
@@ -84,11 +173,11 @@ def main():
     ap.add_argument("--dropout", type=float, default=0.5)
     ap.add_argument("--index-dtype", default="int64", choices=["int32", "int64"])
     ap.add_argument("--max-steps", type=int, default=0, help="cut every epoch after this many steps (0 = whole epoch)")
+    ap.add_argument("--min-timed-steps", type=int, default=0, help="run enough epochs to time at least this many steps")
     ap.add_argument("--no-autocast", action="store_true")
     ap.add_argument("--table", default="replicated", choices=["replicated", "sharded"],
                     help="sharded: every table row-sharded over the ranks, rows fetched per minibatch with an all-to-all exchange")
     args = ap.parse_args()
-    cfg = PRESETS[args.preset]
 
     rank = int(os.environ.get("RANK", 0))
     world = int(os.environ.get("WORLD_SIZE", 1))
@@ -100,62 +189,10 @@ def main():
             os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
             os.environ.setdefault("MASTER_PORT", "29577")
         dist.init_process_group("nccl", device_id=device, rank=rank, world_size=world)
-    idt = torch.int32 if args.index_dtype == "int32" else torch.int64
-    indptr, indices, labels, train_ids, cm = build_data(cfg, device, idt, args.table)
-
-    torch.manual_seed(0)
-    model = sage.SAGE(cfg["feat"], cfg["hidden"], cfg["classes"], len(cfg["fan_out"]), args.dropout, cm).to(device)
-    net = torch.nn.parallel.DistributedDataParallel(model, device_ids=[local_rank]) if world > 1 else model
-    optimizer = torch.optim.Adam(net.parameters(), lr=args.lr)
-    scheduler = torch.optim.lr_scheduler.ExponentialLR(optimizer, gamma=0.978)
-    loader = sage.GPUSamplingDataloader(indptr, indices, train_ids, args.batch_size, cfg["fan_out"], rank, world, shuffle=True)
-    steps = torch.tensor([len(loader)], device=device)
-    if world > 1:
-        dist.all_reduce(steps, op=dist.ReduceOp.MIN)  # every rank takes the same number of steps (gradient all-reduce)
-    steps = int(steps.item())
-    if args.max_steps:
-        steps = min(steps, args.max_steps)
-
-    epoch_s, losses, edges = [], [], 0
-    for epoch in range(args.epochs):
-        net.train()
-        torch.cuda.synchronize()
-        if world > 1:
-            dist.barrier()
-        t0 = time.perf_counter()
-        it = iter(loader)
-        for step in range(steps):
-            input_nodes, output_nodes, blocks = next(it)
-            y = labels[output_nodes]
-            with torch.autocast("cuda", dtype=torch.bfloat16, enabled=not args.no_autocast):
-                pred = net(blocks)
-            loss = F.cross_entropy(pred.float(), y)
-            optimizer.zero_grad(set_to_none=True)
-            loss.backward()
-            optimizer.step()
-            if epoch == args.epochs - 1:
-                edges += blocks[0]["indices_global"].numel()
-        scheduler.step()
-        torch.cuda.synchronize()
-        if world > 1:
-            dist.barrier()
-        epoch_s.append(time.perf_counter() - t0)
-        losses.append(float(loss.detach()))
-    timed = epoch_s[1:] if len(epoch_s) > 1 else epoch_s
-    tmax = torch.tensor([sum(timed) / len(timed)], device=device, dtype=torch.float64)
-    etot = torch.tensor([float(edges)], device=device, dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
-        dist.all_reduce(etot, op=dist.ReduceOp.SUM)
+    rec = train(args.preset, args.table, rank, world, local_rank, args.epochs, args.min_timed_steps, args.batch_size, args.lr,
+                args.dropout, args.index_dtype, args.max_steps, not args.no_autocast)
     if rank == 0:
-        print(json.dumps({
-            "metric": "graphsage_epoch_seconds", "value": float(tmax[0]), "unit": "s/epoch", "n_gpus": world, "preset": args.preset,
-            "steps_per_epoch_per_gpu": steps, "batch_size": args.batch_size, "epochs_run": args.epochs,
-            "epoch_seconds_all": [round(t, 4) for t in epoch_s], "ms_per_step": float(tmax[0]) / steps * 1e3,
-            "first_layer_edges_per_s": float(etot[0]) / float(tmax[0]), "loss_last_step_per_epoch": [round(v, 4) for v in losses],
-            "config": {k: (list(v) if isinstance(v, tuple) else v) for k, v in cfg.items()}, "index_dtype": args.index_dtype,
-            "autocast_bf16": not args.no_autocast, "table": args.table, "data": "synthetic", "scaling": "strong (train ids split over ranks)",
-            "timing": "wall clock around barrier + synchronize delimited epochs, first epoch discarded, max over ranks"}), flush=True)
+        print(json.dumps(rec), flush=True)
     if dist.is_initialized():
         dist.destroy_process_group()
 

@@ -110,6 +110,12 @@ int f2c_vq_decompress(const void* codes, int code_dtype, const void* codebooks, 
 int f2c_spmm_csr(const void* feat, int feat_dtype, const void* indptr, const void* indices, int index_dtype,
                  void* out, int64_t n_dst, int64_t feat_dim, int reduce, void* stream);
 
+/* Backward of spmm_csr for fp32 features (no counterpart in src/: the reference's hidden layers are DGL's SAGEConv,
+ * examples/models.py:31, whose autograd does this).  grad_src [n_src, feat_dim] is zeroed, then
+ * grad_src[indices[k], :] += grad_out[d, :] / max(deg(d), 1) (mean) or += grad_out[d, :] (sum) for every edge k of row d. */
+int f2c_spmm_csr_backward(const float* grad_out, const void* indptr, const void* indices, int index_dtype,
+                          float* grad_src, int64_t n_dst, int64_t n_src, int64_t feat_dim, int reduce, void* stream);
+
 /* sq_decompress_spmm_csr(compress_feat, codebooks, indptr, indices, target_bit, column_slice, feat_dim)
  *  -  src/fusion_spmm.cu:240-272 (kernel :143-238).  out [n_dst, feat_dim] f32; the decoded rows are
  * never written to memory.  n_src = number of rows of `codes` (compress_feat.size(0)); every index

@@ -290,6 +290,34 @@ def test_pipelined_vq_kernel_equals_general_kernel(capi, oracle, n_cb, K, cs, D,
                     assert all(torch.equal(a, b) for a in fast), (kw, signed)
 
 
+def test_config5_shape_at_scale(capi, oracle):
+    """Configuration 5's codecs on a block of realistic size: D = 256, hot 2 % SQ 4 bits + VQ 4 x 64 (256 KB of
+    codebooks: two column parts), 150,000 source rows, 12,000 destination rows of up to 15 neighbours.  Every kernel
+    family against the composition decode-each-row-by-its-codec, then the plain mean (bit-equal), and the oracle."""
+    rng = np.random.default_rng(5)
+    n_src, n_hot, n_dst, D = 150_000, 3000, 12_000, 256
+    _, cb, sq = sq_table(oracle, rng, n_hot, D, 4, D)
+    cbs = rng.standard_normal((4, 256, 64)).astype(np.float32)
+    codes = rng.integers(0, 256, (n_src, 4)).astype(np.uint8)
+    slot = np.full(n_src, -1, np.int32)
+    hot = rng.choice(n_src, n_hot, replace=False)
+    slot[hot] = rng.permutation(n_hot).astype(np.int32)
+    deg = rng.integers(0, 16, n_dst)
+    indptr = np.concatenate([[0], np.cumsum(deg)]).astype(np.int64)
+    # half of the edges point at hot rows, as degree-proportional sampling does
+    indices = np.where(rng.random(int(indptr[-1])) < 0.5, rng.choice(hot, int(indptr[-1])), rng.integers(0, n_src, int(indptr[-1]))).astype(np.int64)
+    t = (dev(sq), dev(cb), 4, D, dev(codes), dev(cbs), dev(slot), dev(indptr), dev(indices), D)
+    full = capi.vq_decompress(dev(codes), dev(cbs), D)
+    full[dev(hot)] = capi.sq_decompress(dev(sq), dev(cb), 4, D, D)[dev(slot[hot].astype(np.int64))]
+    want = capi.spmm_csr(full, dev(indptr), dev(indices))
+    for kernel in ("auto", "stream", "prefetch", "general"):
+        assert torch.equal(capi.two_level_decompress_spmm_csr(*t, kernel=kernel), want), kernel
+    ref = oracle.two_level_decompress_spmm_csr(sq, cb, 4, D, codes, cbs, slot, indptr, indices, D, acc64=True)
+    assert close_to_oracle(host(want), ref, host(capi.spmm_csr(full.abs(), dev(indptr), dev(indices))))
+    cold = capi.vq_decompress_spmm_csr(dev(codes), dev(cbs), dev(indptr), dev(indices), D)
+    assert np.array_equal(host(cold), oracle.vq_decompress_spmm_csr(codes, cbs, indptr, indices, D))
+
+
 @pytest.mark.parametrize("kind", ["sq", "vq", "two_level"])
 def test_fused_dropout_equals_dropout_after(capi, oracle, kind):
     rng = np.random.default_rng(99)
