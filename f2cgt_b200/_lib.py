@@ -73,7 +73,7 @@ SIGNATURES = {
     "f2c_relabel_mark": [p, ci, i64, p, p, i64, p, p, p],
     "f2c_relabel_assign": [p, ci, i64, p, p, i64, p, p, p, p, p],
     "f2c_sample_degrees": [p, p, p, ci, i64, ci, p],
-    "f2c_sample_neighbors": [p, p, p, p, p, ci, i64, ci, u64, u64, p],
+    "f2c_sample_neighbors": [p, p, p, p, p, i64, ci, i64, ci, u64, u64, p],
     "f2c_last_error": [],
     "f2c_version": [],
 }

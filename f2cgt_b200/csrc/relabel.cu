@@ -48,7 +48,11 @@ __global__ void __launch_bounds__(256) relabel_insert_kernel(const IdxT* __restr
                                                              int32_t* tab_pos, int64_t cap_mask, int32_t* error) {
   const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
-  const int64_t slot = find_or_insert(tab_keys, cap_mask, (unsigned long long)(int64_t)keys[i]);
+  const int64_t key = (int64_t)keys[i];
+  // ids must be >= 0: -1 (the padding value of some samplers) is the table's empty marker and would share a slot with
+  // whatever key claims it next; a negative id is reported instead of being numbered wrongly
+  if (key < 0) { atomicExch(error, 2); return; }
+  const int64_t slot = find_or_insert(tab_keys, cap_mask, (unsigned long long)key);
   if (slot < 0) { atomicExch(error, 1); return; }
   atomicMin(tab_pos + slot, (int32_t)i);
 }

@@ -414,10 +414,14 @@ class KMeans:
 
 
 # ------------------------------------------------------------------ neighbour sampling
-def csr_sampling(indptr, indices, seeds, num_pick, replace=False, rng_seed=0, rng_offset=0):
+def csr_sampling(indptr, indices, seeds, num_pick, replace=False, rng_seed=0, rng_offset=0, exact=True):
     """The reference's ``ShmTensorLib.csr_sampling(indptr, indices, seeds, num_pick, replace)`` (call sites
     examples/dataloader.py:174-175,287-288): uniform sampling of at most ``num_pick`` in-neighbours per seed
-    without replacement.  Returns ``(sub_indptr, sub_indices)``, a CSC over the seeds with global ids."""
+    without replacement.  Returns ``(sub_indptr, sub_indices)``, a CSC over the seeds with global ids.
+
+    ``exact=False`` skips the host read of the edge count: ``sub_indices`` then has ``len(seeds) * num_pick`` entries, the
+    ones behind ``sub_indptr[-1]`` being copies of ``seeds[0]`` (a block's kernels only read what ``sub_indptr`` spans, and
+    relabelling the padded tensor numbers the nodes exactly as relabelling the used part would)."""
     if replace:
         raise RuntimeError("csr_sampling: only replace=False is implemented (the reference never passes True)")
     _chk(indptr, "indptr", (torch.int32, torch.int64))
@@ -430,9 +434,12 @@ def csr_sampling(indptr, indices, seeds, num_pick, replace=False, rng_seed=0, rn
         check(lib.f2c_sample_degrees(_ptr(indptr), _ptr(seeds), _ptr(deg), _DT[indptr.dtype], n, int(num_pick), st))
         sub_indptr = torch.zeros((n + 1,), dtype=indptr.dtype, device=indptr.device)
         torch.cumsum(deg, 0, out=sub_indptr[1:])
-        nnz = int(sub_indptr[-1].item()) if n > 0 else 0
+        if exact or n == 0:
+            nnz, capacity = (int(sub_indptr[-1].item()) if n > 0 else 0), 0
+        else:
+            nnz = capacity = n * int(num_pick)
         sub_indices = torch.empty((nnz,), dtype=indptr.dtype, device=indptr.device)
-        check(lib.f2c_sample_neighbors(_ptr(indptr), _ptr(indices), _ptr(seeds), _ptr(sub_indptr), _ptr(sub_indices),
+        check(lib.f2c_sample_neighbors(_ptr(indptr), _ptr(indices), _ptr(seeds), _ptr(sub_indptr), _ptr(sub_indices), capacity,
                                        _DT[indptr.dtype], n, int(num_pick), int(rng_seed) & 0xFFFFFFFFFFFFFFFF,
                                        int(rng_offset), st))
     return sub_indptr, sub_indices
@@ -465,8 +472,10 @@ def tensor_relabel(tensors):
         check(lib.f2c_relabel_mark(_ptr(keys), _DT[dt], n, _ptr(tab_keys), _ptr(tab_pos), cap, _ptr(first), _ptr(err), st))
         incl = torch.cumsum(first, 0, dtype=dt)
         rank = incl - first.to(dt)
-        n_unique = int(incl[-1].item())
-        if int(err.item()) != 0:
+        n_unique, overflow = torch.stack([incl[-1], err[0].to(dt)]).tolist()  # one host read for both
+        if overflow == 2:
+            raise RuntimeError("tensor_relabel: negative id (ids must be >= 0; strip a sampler's -1 padding first)")
+        if overflow != 0:
             raise RuntimeError("tensor_relabel: hash table overflow")
         unique = torch.empty((n_unique,), dtype=dt, device=dev)
         relabelled = torch.empty((n,), dtype=dt, device=dev)

@@ -4,8 +4,8 @@ Two ways to aggregate a block whose source rows live on other GPUs:
 
 * ``ShardedTable.fetch(ids)`` - the exchange the reference never needed (it keeps one pinned replica per machine,
   examples/load_dataset.py:63-85): ids are bucketed by owner, exchanged, the owners gather their rows, and the rows
-  are exchanged back, all as point-to-point operations grouped into one NCCL all-to-all
-  (``dist.batch_isend_irecv``; the same code runs over gloo on CPU, which is how the tests cover it).
+  are exchanged back, each exchange one NCCL ``all_to_all_single`` with per-peer split sizes (over gloo on CPU,
+  which is how the tests cover the host logic, the same exchange is a group of point-to-point operations).
   The fused kernel then runs on the fetched, block-local rows.
 * ``PeerTable`` - every rank maps the other ranks' shards through CUDA IPC (``f2c_shard_create`` / ``f2c_shard_open``)
   and the fused kernel reads remote rows itself with ordinary loads over NVLink (``f2c_sq_spmm_csr_peer``): no
@@ -18,7 +18,9 @@ import torch.distributed as dist
 
 
 def rows_per_rank(n_rows, world):
-    return (n_rows + world - 1) // world
+    """Rows per shard: ceil(n_rows / world), at least 2 (the kernels divide by it with a multiply-high that needs >= 2);
+    the last shards of a small or uneven table may be short or empty."""
+    return max(2, (n_rows + world - 1) // world)
 
 
 def shard_bounds(n_rows, world, rank):
@@ -37,10 +39,15 @@ def bucket_by_owner(ids, rpr, world):
 
 
 def _exchange(send, send_counts, recv_counts, group):
-    """Variable-size all-to-all of the leading dimension as one group of point-to-point operations."""
+    """Variable-size all-to-all of the leading dimension: ``all_to_all_single`` with split sizes on CUDA tensors, one
+    group of point-to-point operations on CPU tensors."""
     world = dist.get_world_size(group)
     rank = dist.get_rank(group)
     recv = send.new_empty((int(sum(recv_counts)),) + tuple(send.shape[1:]))
+    if send.is_cuda:  # NCCL: one all-to-all with per-peer split sizes (gloo, which the CPU tests run on, has none: see below)
+        dist.all_to_all_single(recv, send.contiguous(), output_split_sizes=[int(c) for c in recv_counts],
+                               input_split_sizes=[int(c) for c in send_counts], group=group)
+        return recv
     s_off = [0]
     r_off = [0]
     for r in range(world):
@@ -109,6 +116,36 @@ class ShardedTable:
         return self.fetch_rows(self.plan(ids))
 
 
+class _LibraryShards:
+    """Shard memory through the library: f2c_shard_create / open / close / free (CUDA IPC)."""
+
+    def create(self, rows):
+        import ctypes
+        from ._lib import lib, check
+        own = ctypes.c_void_p()
+        handle = (ctypes.c_ubyte * 64)()
+        check(lib.f2c_shard_create(rows.data_ptr(), rows.numel() * rows.element_size(), ctypes.byref(own), handle,
+                                   torch.cuda.current_stream(rows.device).cuda_stream))
+        return own.value, bytes(handle)
+
+    def open(self, handle):
+        import ctypes
+        from ._lib import lib, check
+        ptr = ctypes.c_void_p()
+        check(lib.f2c_shard_open((ctypes.c_ubyte * 64).from_buffer_copy(handle), ctypes.byref(ptr)))
+        return ptr.value
+
+    def close(self, ptr):
+        import ctypes
+        from ._lib import lib, check
+        check(lib.f2c_shard_close(ctypes.c_void_p(ptr)))
+
+    def free(self, ptr):
+        import ctypes
+        from ._lib import lib, check
+        check(lib.f2c_shard_free(ctypes.c_void_p(ptr)))
+
+
 class PeerTable:
     """Shards of all ranks mapped into this process through CUDA IPC (plain peer mappings, no multicast).
 
@@ -116,12 +153,15 @@ class PeerTable:
     (``f2c_shard_create``); every other rank opens the handle while ITS GPU is the current device
     (``f2c_shard_open``), which maps the memory into that GPU's address space with peer access.
     ``pointers[r]`` is the device address of rank r's shard as seen from this rank.  Construct and ``close`` it
-    collectively: every rank closes its mappings before any owner frees its shard."""
+    collectively: every rank closes its mappings before any owner frees its shard.
 
-    def __init__(self, local_rows, n_rows, group=None):
-        import ctypes
-        from ._lib import lib, check
-        if not local_rows.is_cuda or not local_rows.is_contiguous() or local_rows.dim() != 2:
+    A failure on any rank (allocation, export, mapping) is gathered and raised on EVERY rank after the collectives, so no
+    rank is left waiting in one.  An empty shard (the last ranks of a small or uneven table) is exported as one zero row.
+    ``backend`` replaces the library's shard calls (tests inject failures on CPU ranks with it)."""
+
+    def __init__(self, local_rows, n_rows, group=None, backend=None):
+        self.backend = backend or _LibraryShards()
+        if backend is None and (not local_rows.is_cuda or not local_rows.is_contiguous() or local_rows.dim() != 2):
             raise ValueError("local_rows must be a contiguous 2-D CUDA tensor")
         self.group = group
         self.world = dist.get_world_size(group)
@@ -135,26 +175,58 @@ class PeerTable:
         self.dtype = local_rows.dtype
         self.row_width = int(local_rows.shape[1])
         self.nbytes = local_rows.numel() * local_rows.element_size()
-        self._own = ctypes.c_void_p()
+        self._own = None
         self._opened = []
-        handle = (ctypes.c_ubyte * 64)()
-        with torch.cuda.device(self.device):
-            check(lib.f2c_shard_create(local_rows.data_ptr(), self.nbytes, ctypes.byref(self._own), handle,
-                                       torch.cuda.current_stream(self.device).cuda_stream))
+        self.pointers = []
+        self.shard_bytes = []
+        guard = torch.cuda.device(self.device) if self.device.type == "cuda" else _NoGuard()
+        with guard:
+            err, handle = None, b""
+            try:
+                export = local_rows if self.nbytes > 0 else torch.zeros((1, max(self.row_width, 1)), dtype=self.dtype, device=self.device)
+                self._own, handle = self.backend.create(export)
+            except Exception as e:  # noqa: BLE001
+                err = f"rank {self.rank}: {e}"
             metas = [None] * self.world
-            dist.all_gather_object(metas, (bytes(handle), self.nbytes), group=self.group)
-            self.pointers = []
-            self.shard_bytes = []
-            for r, (h, nbytes) in enumerate(metas):
-                self.shard_bytes.append(nbytes)
-                if r == self.rank:
-                    self.pointers.append(self._own.value)
-                    continue
-                ptr = ctypes.c_void_p()
-                check(lib.f2c_shard_open((ctypes.c_ubyte * 64).from_buffer_copy(h), ctypes.byref(ptr)))
-                self._opened.append(ptr)
-                self.pointers.append(ptr.value)
+            dist.all_gather_object(metas, (handle, self.nbytes, err), group=self.group)
+            failed = [m[2] for m in metas if m[2] is not None]
+            if not failed:
+                for r, (h, nbytes, _) in enumerate(metas):
+                    self.shard_bytes.append(nbytes)
+                    if r == self.rank:
+                        self.pointers.append(self._own)
+                        continue
+                    try:
+                        ptr = self.backend.open(h)
+                    except Exception as e:  # noqa: BLE001
+                        err = f"rank {self.rank} opening shard {r}: {e}"
+                        break
+                    self._opened.append(ptr)
+                    self.pointers.append(ptr)
+            opened = [None] * self.world  # second round: did every rank map every shard?
+            dist.all_gather_object(opened, err, group=self.group)
+            failed += [m for m in opened if m is not None and m not in failed]
+            if failed:
+                self._release()
+                raise RuntimeError("PeerTable: " + "; ".join(failed))
         dist.barrier(group=self.group)
+
+    def _release(self):
+        """Collective: unmap the other ranks' shards, then free the local one (errors while cleaning up are dropped)."""
+        for ptr in self._opened:
+            try:
+                self.backend.close(ptr)
+            except Exception:  # noqa: BLE001
+                pass
+        self._opened = []
+        dist.barrier(group=self.group)
+        if self._own:
+            try:
+                self.backend.free(self._own)
+            except Exception:  # noqa: BLE001
+                pass
+        self._own = None
+        self.pointers = []
 
     def read(self, r, byte_offset, nbytes):
         """Bytes [byte_offset, byte_offset + nbytes) of rank r's shard as a uint8 tensor on this GPU (copy engine)."""
@@ -169,15 +241,19 @@ class PeerTable:
 
     def close(self):
         """Collective: unmap the other ranks' shards, then free the local one."""
-        from ._lib import lib, check
         if self._own is None:
             return
-        with torch.cuda.device(self.device):
-            torch.cuda.synchronize(self.device)
-            for ptr in self._opened:
-                check(lib.f2c_shard_close(ptr))
-            self._opened = []
-            dist.barrier(group=self.group)
-            check(lib.f2c_shard_free(self._own))
-        self._own = None
-        self.pointers = []
+        if self.device.type == "cuda":
+            with torch.cuda.device(self.device):
+                torch.cuda.synchronize(self.device)
+                self._release()
+        else:
+            self._release()
+
+
+class _NoGuard:
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *a):
+        return False

@@ -68,7 +68,8 @@ def sq_codebook_from_sample(sample, column_slice):
     eps = 1e-5
     for b in range(0, D, column_slice):
         a = sample[:, b:b + column_slice].float().abs().flatten()
-        q = torch.quantile(a[:min(a.numel(), 1 << 24)].double(), torch.tensor([0.005, 0.995], dtype=torch.float64, device=a.device))
+        from .compress import _percentiles
+        q = _percentiles(a, (0.005, 0.995))
         fmin = max(float(q[0]), eps)
         fmax = max(float(q[1]), 2 * eps)
         mean = float(a.mean())

@@ -224,12 +224,15 @@ int f2c_check_csc(const void* indptr, const void* indices, int index_dtype, int6
  * submodule (call sites examples/dataloader.py:174-175,287-288): uniform neighbour sampling without
  * replacement.  Step 1 writes out_deg[i] = min(in_degree(seeds[i]), num_pick); the caller builds
  * out_indptr as the exclusive prefix sum of out_deg; step 2 writes the sampled GLOBAL neighbour ids of
- * seed i at out_indices[out_indptr[i] ...].  All id tensors share index_dtype.  num_pick <= 64. */
+ * seed i at out_indices[out_indptr[i] ...].  All id tensors share index_dtype.  num_pick <= 64.
+ * out_capacity = 0: out_indices has exactly out_indptr[n_seeds] entries.  out_capacity > 0: out_indices has that many
+ * entries (the worst case n_seeds * num_pick, so that the caller need not read the edge count back from the device);
+ * the unused tail is filled with seeds[0], a valid id that a later relabelling already knows. */
 int f2c_sample_degrees(const void* indptr, const void* seeds, void* out_deg, int index_dtype, int64_t n_seeds,
                        int num_pick, void* stream);
 int f2c_sample_neighbors(const void* indptr, const void* indices, const void* seeds, const void* out_indptr,
-                         void* out_indices, int index_dtype, int64_t n_seeds, int num_pick, uint64_t rng_seed,
-                         uint64_t rng_offset, void* stream);
+                         void* out_indices, int64_t out_capacity, int index_dtype, int64_t n_seeds, int num_pick,
+                         uint64_t rng_seed, uint64_t rng_offset, void* stream);
 
 /* tensor_relabel([seeds, sub_indices]) of the reference's absent ShmTensor submodule (call sites
  * examples/dataloader.py:176-177,289-290): the distinct ids of `keys` (the concatenation, seeds first) are numbered
@@ -238,7 +241,8 @@ int f2c_sample_neighbors(const void* indptr, const void* indices, const void* se
  * of `capacity` = f2c_relabel_capacity(n) slots: table_keys 8 B, table_pos 4 B per slot); the caller computes
  * rank = exclusive prefix sum of first (same dtype as the ids) and n_unique = its total; assign writes
  * unique[rank[i]] = keys[i] at first occurrences and relabelled[i] = new number of keys[i].  *error_flag (device)
- * becomes non-zero if the table overflowed (never with the advised capacity). */
+ * becomes 1 if the table overflowed (never with the advised capacity), 2 if a key is negative (ids must be >= 0:
+ * -1 is the table's empty marker). */
 int64_t f2c_relabel_capacity(int64_t n_keys);
 int f2c_relabel_mark(const void* keys, int index_dtype, int64_t n_keys, void* table_keys, void* table_pos, int64_t capacity,
                      int32_t* first, int32_t* error_flag, void* stream);

@@ -32,8 +32,18 @@ def test_sq_artefact(capi, oracle, ratio, bits, min_corr, tmp_path):
     assert table.dtype == torch.int8 and tuple(table.shape) == (30000, 64 * bits // 8)
     assert meta["data"]["compression_data"] == (torch.int8, (30000, 64 * bits // 8))
     # the stored codes are the oracle's codes for these codebooks (modulo elements on a quantisation boundary)
-    want = oracle.sq_codes_to_storage(oracle.sq_compress(x.cpu().numpy(), meta["codebooks"][0].cpu().numpy(), bits, 64), bits)
-    assert (table.cpu().numpy().view(np.uint8) != np.asarray(want).view(np.uint8)).mean() < 0.02
+    cb_np, x_np = meta["codebooks"][0].cpu().numpy(), x.cpu().numpy()
+    want = oracle.sq_compress(x_np, cb_np, bits, 64)
+    # compare element by element (unpacked): a stored code may differ from the oracle's only where the pre-floor value
+    # sits on a quantisation boundary (log2f differs by an ulp between libdevice and libm), and then by one bucket
+    stored = table.view(torch.uint8) if bits < 8 else table
+    got = capi.unpackbits(stored.contiguous(), bits, 64).cpu().numpy().astype(np.int64) if bits < 8 else table.cpu().numpy().astype(np.int64)
+    want_store = np.asarray(want).astype(np.int64) & ((1 << bits) - 1) if bits < 8 else np.asarray(want).astype(np.int64)
+    bad = got != want_store
+    if bad.any():
+        pre = oracle.sq_compress_prefloor(x_np, cb_np, bits, 64)
+        assert np.all(np.abs(pre[bad] - np.round(pre[bad])) < max(1e-3, 2.0 ** (bits - 1) * 2e-6))
+        assert bad.mean() < 0.015
     dec = compress.decompress(meta)
     assert corr(dec, x) > min_corr
     compress.save(meta, str(tmp_path))
@@ -68,3 +78,25 @@ def test_vq_and_two_level_artefact(capi, tmp_path):
     others = torch.tensor([i for i in range(200) if i not in set(seeds.tolist())], device="cuda")
     assert torch.equal(cm.decode_rows(others), dec[others])
     assert corr(hot_dec, x[seeds]) > 0.97
+
+
+def test_rank_split_equals_single_process(capi):
+    """The compressor split over a process group (column slices for the codebooks, row ranges for the codes) gives the
+    artefact a single process computes for the same world size.  One rank here; two ranks in tests/test_gpu_multi.py."""
+    import os
+    import torch.distributed as dist
+    from f2cgt_b200 import compress
+    g = torch.Generator(device="cuda").manual_seed(4)
+    x = torch.randn(20000, 64, generator=g, device="cuda")
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    os.environ.setdefault("MASTER_PORT", "29533")
+    dist.init_process_group("gloo", rank=0, world_size=1)
+    try:
+        for ratio in (8, 64):
+            a = compress.compress(x, target_compression_ratio=ratio, max_iter=10)
+            b = compress.compress(x, target_compression_ratio=ratio, max_iter=10, group=dist.group.WORLD)
+            assert torch.equal(a["compression_data"], b["compression_data"]) and torch.equal(a["codebooks"][0], b["codebooks"][0])
+            c = compress.compress(x, target_compression_ratio=ratio, max_iter=10, group=dist.group.WORLD, gather=False)
+            assert c["row_range"] == (0, 20000) and torch.equal(c["compression_data"], a["compression_data"])
+    finally:
+        dist.destroy_process_group()

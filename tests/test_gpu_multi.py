@@ -60,11 +60,25 @@ def _worker(rank, world, port, q):
                 assert torch.equal(peers.read(r, whole.numel() - n, n), whole[-n:]), f"mapping of shard {r}: tail differs"
             print(f"rank {rank} bits {bits}: mappings ok", file=sys.stderr, flush=True)
             # 3. the kernel reads remote rows itself
-            got = ops.sq_decompress_spmm_csr_peer(peers, cb, indptr, indices, bits, D, D)
-            torch.cuda.synchronize()
-            assert torch.equal(got, want), f"peer loads differ at {bits} bits"
+            for kernel in ("auto", "stream", "prefetch"):
+                got = ops.sq_decompress_spmm_csr_peer(peers, cb, indptr, indices, bits, D, D, kernel=kernel)
+                torch.cuda.synchronize()
+                assert torch.equal(got, want), f"peer loads ({kernel} kernel) differ at {bits} bits"
             print(f"rank {rank} bits {bits}: peer loads ok", file=sys.stderr, flush=True)
             peers.close()  # collective: nobody frees its shard while a peer may still read it
+        # a table too small to give every rank rows: the last shard is short or empty
+        for tiny in (3, 2):
+            g = torch.Generator().manual_seed(tiny)
+            table = torch.randint(0, 256, (tiny, 64), generator=g, dtype=torch.uint8).to(device)
+            cb = torch.tensor([[1e-3, 4.0, -9.97, 2.0, 0.7]], dtype=torch.float32, device=device)
+            indptr = torch.tensor([0, 2, 2, 5], dtype=torch.int64, device=device)
+            indices = torch.tensor([0, tiny - 1, 1, 0, tiny - 1], dtype=torch.int64, device=device)
+            lo, hi = shard.shard_bounds(tiny, world, rank)
+            peers = shard.PeerTable(table[lo:hi].clone(), tiny)
+            got = ops.sq_decompress_spmm_csr_peer(peers, cb, indptr, indices, 4, D, D)
+            assert torch.equal(got, capi.sq_decompress_spmm_csr(table, cb, indptr, indices, 4, D, D)), f"{tiny}-row table"
+            peers.close()
+        assert ops.device_status() == 0
         q.put((rank, "ok"))
     except Exception as e:  # noqa: BLE001
         q.put((rank, repr(e)))
@@ -144,3 +158,46 @@ def test_sharded_compression_manager_equals_resident_tables(world):
     if torch.cuda.device_count() < world:
         pytest.skip("needs more GPUs")
     _run(_manager_worker, world)
+
+
+def _compress_worker(rank, world, port, q):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    torch.cuda.set_device(rank)
+    device = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=device)
+    try:
+        from f2cgt_b200 import compress
+        g = torch.Generator(device=device).manual_seed(9)  # the same features on every rank
+        n, D = 30001, 128
+        protos = torch.randn(4, 64, 32, generator=g, device=device) * 2
+        which = torch.randint(0, 64, (n, 4), generator=g, device=device)
+        x = torch.cat([protos[s][which[:, s]] for s in range(4)], dim=1) + 0.05 * torch.randn(n, D, generator=g, device=device)
+        seeds = torch.randperm(n, generator=g, device=device)[:700]
+        for kw in (dict(target_compression_ratio=8), dict(target_compression_ratio=128, seeds=seeds, max_iter=10)):
+            split = compress.compress(x, group=dist.group.WORLD, **kw)               # column slices / row ranges per rank
+            single = compress.compress(x, world_size=world, **kw)                     # the same artefact in one process
+            assert split["methods"] == single["methods"] and split["configs"] == single["configs"]
+            for a, b in zip(split["codebooks"], single["codebooks"]):
+                assert torch.equal(a, b), "codebooks differ"
+            assert torch.equal(split["compression_data"], single["compression_data"])
+            if "seeds" in kw:
+                assert torch.equal(split["seeds_compression_data"], single["seeds_compression_data"])
+            shard_only = compress.compress(x, group=dist.group.WORLD, gather=False, **kw)
+            lo, hi = shard_only["row_range"]
+            assert torch.equal(shard_only["compression_data"], single["compression_data"][lo:hi])
+        q.put((rank, "ok"))
+    except Exception as e:  # noqa: BLE001
+        import traceback
+        q.put((rank, repr(e) + traceback.format_exc()[-600:]))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_compressor_rank_split_two_gpus():
+    """The offline compressor split over two ranks (examples/process_compress.py:82-107,192-196,225,236-238) writes the
+    artefact one process writes."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    _run(_compress_worker, 2)

@@ -95,3 +95,22 @@ def test_blocks_feed_the_fused_kernel(capi, oracle):
         assert torch.equal(by_global, by_local)
     for outer, inner in zip(blocks[:-1], blocks[1:]):
         assert torch.equal(outer["dst_nodes"], inner["src_nodes"])
+
+
+def test_relabel_rejects_negative_ids_and_padded_sampling_numbers_alike(capi):
+    from f2cgt_b200 import ops
+    ids = torch.tensor([5, 3, -1, 5], dtype=torch.int64, device="cuda")
+    with pytest.raises(RuntimeError, match="negative id"):
+        ops.tensor_relabel([ids])
+    # csr_sampling(exact=False) pads its index tensor with copies of seeds[0]: same CSC, same numbering
+    from f2cgt_b200 import synth
+    indptr, indices = synth.power_law_graph(5000, 20, 2.1, seed=2, device="cuda")
+    seeds = torch.randperm(5000, device="cuda")[:300]
+    ip_a, ix_a = ops.csr_sampling(indptr, indices, seeds, 7, False, rng_seed=5, rng_offset=2)
+    ip_b, ix_b = ops.csr_sampling(indptr, indices, seeds, 7, False, rng_seed=5, rng_offset=2, exact=False)
+    nnz = int(ip_a[-1])
+    assert torch.equal(ip_a, ip_b) and ix_b.numel() == 300 * 7 and torch.equal(ix_a, ix_b[:nnz])
+    assert bool((ix_b[nnz:] == seeds[0]).all())
+    ua, (_, la) = ops.tensor_relabel([seeds, ix_a])
+    ub, (_, lb) = ops.tensor_relabel([seeds, ix_b])
+    assert torch.equal(ua, ub) and torch.equal(la, lb[:nnz])

@@ -123,3 +123,111 @@ def test_sharded_compression_manager_assembles_block_tables():
     for p in procs:
         p.join(timeout=30)
     assert results == {0: "ok", 1: "ok"}, results
+
+
+class _FakeShards:
+    """Stand-in for the library's shard calls on CPU ranks: handles are made-up bytes, `fail` names the call that raises."""
+
+    def __init__(self, fail=None):
+        self.fail, self.log = fail, []
+
+    def create(self, rows):
+        if self.fail == "create":
+            raise RuntimeError("out of memory (injected)")
+        self.log.append("create")
+        return 1000 + rows.shape[0], b"handle-%d" % rows.shape[0]
+
+    def open(self, handle):
+        if self.fail == "open":
+            raise RuntimeError("cannot map (injected)")
+        self.log.append("open")
+        return 5000 + len(handle)
+
+    def close(self, ptr):
+        self.log.append("close")
+
+    def free(self, ptr):
+        self.log.append("free")
+
+
+def _peer_error_worker(rank, world, port, q):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        # an uneven table whose last shard is empty: 2 rows over 2 ranks of at least 2 rows each
+        n_rows = 2
+        lo, hi = shard.shard_bounds(n_rows, world, rank)
+        assert (lo, hi) == ((0, 2) if rank == 0 else (2, 2))
+        rows = torch.zeros((hi - lo, 16), dtype=torch.uint8)
+        ok = shard.PeerTable(rows, n_rows, backend=_FakeShards())
+        assert len(ok.pointers) == world and ok.shard_bytes == [32, 0]
+        ok.close()
+        assert ok.backend.log == ["create", "open", "close", "free"]
+        # a failure on ONE rank is raised on EVERY rank, after the collectives (nobody hangs)
+        for call in ("create", "open"):
+            backend = _FakeShards(fail=call if rank == 1 else None)
+            try:
+                shard.PeerTable(rows, n_rows, backend=backend)
+                raise AssertionError("no error raised")
+            except RuntimeError as e:
+                assert "rank 1" in str(e) and "injected" in str(e), str(e)
+        q.put((rank, "ok"))
+    except Exception as e:  # noqa: BLE001
+        import traceback
+        q.put((rank, repr(e) + traceback.format_exc()[-500:]))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_peer_table_raises_collectively_and_takes_empty_shards():
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_peer_error_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    results = dict(q.get(timeout=120) for _ in procs)
+    for p in procs:
+        p.join(timeout=30)
+    assert results == {0: "ok", 1: "ok"}, results
+
+
+def _split_worker(rank, world, port, q):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from f2cgt_b200 import compress
+        # 5 column slices over 2 ranks: 3 + 2; 11 rows: 6 + 5 (examples/process_compress.py:192-196,236-238)
+        (s_lo, s_hi), (r_lo, r_hi) = compress.split_plan(11, 5, world, rank)
+        assert (s_lo, s_hi, r_lo, r_hi) == ((0, 3, 0, 6) if rank == 0 else (3, 5, 6, 11))
+        # more ranks than slices: the last ranks own nothing
+        assert compress.split_plan(11, 1, world, 1)[0] == (1, 1)
+        part = torch.arange(s_lo, s_hi, dtype=torch.float32).reshape(-1, 1, 1).expand(-1, 2, 3).contiguous()
+        whole = compress.gather_parts(part, dist.group.WORLD)
+        assert whole.shape == (5, 2, 3) and torch.equal(whole[:, 0, 0], torch.arange(5, dtype=torch.float32))
+        rows = torch.arange(r_lo, r_hi, dtype=torch.int8).reshape(-1, 1)
+        assert torch.equal(compress.gather_parts(rows, dist.group.WORLD).reshape(-1), torch.arange(11, dtype=torch.int8))
+        # a rank with nothing to contribute
+        nothing = torch.zeros((0, 4)) if rank == 1 else torch.ones((2, 4))
+        assert torch.equal(compress.gather_parts(nothing, dist.group.WORLD), torch.ones((2, 4)))
+        q.put((rank, "ok"))
+    except Exception as e:  # noqa: BLE001
+        import traceback
+        q.put((rank, repr(e) + traceback.format_exc()[-500:]))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_compressor_split_plan_and_gather():
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_split_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    results = dict(q.get(timeout=120) for _ in procs)
+    for p in procs:
+        p.join(timeout=30)
+    assert results == {0: "ok", 1: "ok"}, results
