@@ -36,12 +36,19 @@ def _init_kmeanspp(x, k, gen):
 
 
 def _update(x, labels, centers):
+    """Mean of every cluster's points, deterministically (a scatter-add would sum in whatever order its atomics land, and
+    a fit would not be reproducible): points sorted by label, float64 prefix sums, one difference per cluster."""
     k = centers.shape[0]
-    sums = torch.zeros_like(centers)
-    sums.index_add_(0, labels, x)
-    cnt = torch.bincount(labels, minlength=k).to(torch.float32).unsqueeze(1)
+    order = torch.argsort(labels, stable=True)
+    csum = torch.cumsum(x[order].double(), dim=0)
+    cnt = torch.bincount(labels, minlength=k)
+    end = torch.cumsum(cnt, 0)                      # one past the last point of every cluster, in sorted order
+    zero = torch.zeros((1, x.shape[1]), dtype=torch.float64, device=x.device)
+    padded = torch.cat([zero, csum], dim=0)         # padded[j] = sum of the first j sorted points
+    sums = (padded[end] - padded[end - cnt]).float()
+    cntf = cnt.to(torch.float32).unsqueeze(1)
     # empty clusters keep their previous centre (examples/my_kmeans.py:133-144)
-    return torch.where(cnt > 0, sums / cnt.clamp_min(1), centers)
+    return torch.where(cntf > 0, sums / cntf.clamp_min(1), centers)
 
 
 def _inertia(x, labels, centers, metric):
