@@ -254,7 +254,7 @@ __global__ void __launch_bounds__(VqCta<HB>::kThreads, 1) vq_fast_kernel(const V
         if (lane < cnt) {
           const int64_t id = (int64_t)indices[k0 + lane];
           load_code_row<ROWW>(c, codes + id * ROWB);
-          if (HB != 0) sl_mine = __ldg(p.slot + id);
+          if (HB != 0) sl_mine = hot_slot_of(p, id);
         }
         __syncwarp();
         stage_codes(c, cnt);
@@ -303,7 +303,7 @@ __global__ void __launch_bounds__(VqCta<HB>::kThreads, 1) vq_fast_kernel(const V
       if (on && lane < min(deg2, 32)) {
         const int64_t id = (int64_t)idx2;
         load_code_row<ROWW>(code3, codes + id * ROWB);
-        if (HB != 0) slot3 = __ldg(p.slot + id);
+        if (HB != 0) slot3 = hot_slot_of(p, id);
       }
     }
     // ================= stage 1: row rP - W: its indptr pair has arrived; fetch the neighbour ids

@@ -119,7 +119,7 @@ __global__ void __launch_bounds__(kVqThreads) vq_spmm_kernel(const VqParams p) {
         const int cnt = (int)(end - k0 < 32 ? end - k0 : 32);
         int64_t mine = lane < cnt ? (int64_t)indices[k0 + lane] : 0;
         int myslot = -1;
-        if (HB != 0 && lane < cnt) myslot = __ldg(p.slot + mine);
+        if (HB != 0 && lane < cnt) myslot = hot_slot_of(p, (int64_t)mine);
         for (int t0 = 0; t0 < cnt; t0 += U) {
           float4 v[U];
 #pragma unroll
@@ -269,7 +269,7 @@ extern "C" int f2c_vq_spmm_csr(const void* codes, int code_dtype, const float* c
 extern "C" int f2c_hybrid_spmm_csr(const void* sq_codes, int sq_dtype, const float* sq_codebooks, int64_t sq_n_codebooks,
                                    int bits, int64_t sq_column_slice, int64_t sq_src_dim, const void* vq_codes,
                                    int vq_dtype, const float* vq_codebooks, int64_t vq_n_codebooks, int64_t length,
-                                   int64_t vq_column_slice, const int32_t* slot, const void* indptr, const void* indices,
+                                   int64_t vq_column_slice, const int32_t* slot, int64_t n_hot, const void* indptr, const void* indices,
                                    int index_dtype, float* out, int64_t n_dst, int64_t feat_dim, int reduce,
                                    const f2c_epilogue* epilogue, void* stream) {
   const char* op = "two_level_decompress_spmm_csr";
@@ -280,7 +280,7 @@ extern "C" int f2c_hybrid_spmm_csr(const void* sq_codes, int sq_dtype, const flo
   if (rc) return rc;
   F2C_REQUIRE(is_index_dtype(index_dtype), F2C_ERR_UNSUPPORTED, "%s: indptr/indices must be int32 or int64", op);
   F2C_REQUIRE(reduce == F2C_MEAN || reduce == F2C_SUM, F2C_ERR_INVALID, "%s: reduce must be mean or sum", op);
-  F2C_REQUIRE(n_dst * feat_dim == 0 || (indptr && out && vq_codebooks && sq_codebooks && slot), F2C_ERR_INVALID,
+  F2C_REQUIRE(n_dst * feat_dim == 0 || (indptr && out && vq_codebooks && sq_codebooks && (slot || n_hot >= 0)), F2C_ERR_INVALID,
               "%s: null pointer", op);
   const int sq_bytes = dtype_size(sq_dtype);
   F2C_REQUIRE((bits == 16) == (sq_bytes == 2), F2C_ERR_UNSUPPORTED,
@@ -297,7 +297,7 @@ extern "C" int f2c_hybrid_spmm_csr(const void* sq_codes, int sq_dtype, const flo
   p.n_cb = (int)vq_n_codebooks; p.cs = (int)vq_column_slice; p.feat_dim = (int)feat_dim; p.K = (uint32_t)length;
   p.code_kind = vq_dtype == F2C_U8 ? 0 : vq_dtype == F2C_I8 ? 1 : 2;
   p.reduce = reduce; p.vec_store = 1; p.drop = make_dropout(epilogue);
-  p.sq_codes = (const uint8_t*)sq_codes; p.sq_codebooks = sq_codebooks; p.slot = slot; p.sq_row_bytes = sq_row_bytes;
+  p.sq_codes = (const uint8_t*)sq_codes; p.sq_codebooks = sq_codebooks; p.slot = slot; p.n_hot = n_hot; p.sq_row_bytes = sq_row_bytes;
   p.sq_cs = (int)sq_column_slice; p.sq_n_cb = (int)sq_n_codebooks; p.sq_signed = sq_dtype == F2C_I8;
   cudaStream_t st = (cudaStream_t)stream;
   const int variant = kernel_variant(epilogue);

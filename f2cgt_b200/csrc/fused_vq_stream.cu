@@ -3,9 +3,9 @@
 // {4,...,128} dividing 128, hot rows 8- or 4-bit SQ.  Same arithmetic and CSC summation order as the other kernel
 // families (reference: src/fusion_spmm.cu:72-141 for VQ, src/sq_quantization.cu:123-153 for the hot rows).
 //
-// A CTA owns a contiguous slice of the destination rows.  Its producer warp streams, per edge and in CSC order, the
-// neighbour id, then the neighbour's VQ code row (4..16 bytes) and - for the two-level op - its hot-row slot into
-// shared-memory rings with cp.async (stream_pipe.cuh).  Consumer warps own one destination row at a time; a lane owns
+// A CTA owns a contiguous slice of the destination rows.  Its producer warps stage, per edge and in CSC order, the
+// neighbour id (cp.async), then the neighbour's VQ code row (4..16 bytes) and - for the two-level op - its hot-row slot
+// (plain loads, stored into shared-memory rings; stream_pipe.cuh has the watermarks).  Consumer warps own one destination row at a time; a lane owns
 // four consecutive columns (one LDS.128 from the centroid its code selects, a coalesced 512-byte row store).  What is
 // left of the dependent chain indptr -> ids -> (slot, codes) -> hot row for a consumer is its last link: the hot rows
 // of a warp's NEXT destination row are requested (one coalesced 4-byte load per lane and hot edge, up to U per row)
@@ -33,6 +33,7 @@ constexpr int kThreads = (kConsumers + kProducers) * 32;
 constexpr int U = 16;             // hot rows requested ahead per destination row
 constexpr int kLongRow = 32;      // rows with more neighbours bypass the rings
 constexpr int kLutBytes = 256 * 256;
+constexpr int kPerLane = 2;       // edges per producer lane and batch (a warp's share of a batch is at most 64 edges)
 
 struct Layout {  // byte offsets in dynamic shared memory, from the host
   uint32_t lut, ptr, ids, codes, slots, sync;
@@ -68,6 +69,18 @@ __device__ __forceinline__ uint32_t ldg_nc_u16(const void* p) {
   uint16_t v;
   asm volatile("ld.global.nc.L1::no_allocate.u16 %0, [%1];" : "=h"(v) : "l"(p));
   return v;
+}
+
+template <int ROWW> struct CodeRow { uint32_t w[ROWW]; };
+template <int ROWW> __device__ __forceinline__ void load_code_row(CodeRow<ROWW>& c, const void* p) {
+  if (ROWW == 1) c.w[0] = ldg_nc_u32(p);
+  else if (ROWW == 2) { uint2 v = ldg_nc_u64(p); c.w[0] = v.x; c.w[1] = v.y; }
+  else { uint4 v = ldg_nc_u128(p); c.w[0] = v.x; c.w[1] = v.y; c.w[ROWW > 2 ? 2 : 0] = v.z; c.w[ROWW > 3 ? 3 : 0] = v.w; }
+}
+template <int ROWW> __device__ __forceinline__ void store_code_row(uint32_t a, const CodeRow<ROWW>& c) {
+  if (ROWW == 1) asm volatile("st.shared.b32 [%0], %1;" ::"r"(a), "r"(c.w[0]) : "memory");
+  else if (ROWW == 2) asm volatile("st.shared.v2.b32 [%0], {%1, %2};" ::"r"(a), "r"(c.w[0]), "r"(c.w[ROWW > 1 ? 1 : 0]) : "memory");
+  else asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(a), "r"(c.w[0]), "r"(c.w[ROWW > 1 ? 1 : 0]), "r"(c.w[ROWW > 2 ? 2 : 0]), "r"(c.w[ROWW > 3 ? 3 : 0]) : "memory");
 }
 
 // HB = 0: VQ only.  HB = 8 / 4: two-level with 8- / 4-bit hot rows.  ROWW = 32-bit words of one VQ code row.
@@ -153,49 +166,78 @@ __global__ void __launch_bounds__(kThreads, 1) vq_stream_kernel(const VqParams p
 
     if (is_producer) {
       // =========================================================== producer warps
-      const uint32_t pw = (uint32_t)(warp - C);                 // this warp copies edges [pw * sub, (pw + 1) * sub) of every batch
+      // Warp pw stages edges [pw * sub, (pw + 1) * sub) of every batch: at most kPerLane edges per lane.  The neighbour ids
+      // stream in with cp.async (coalesced, kIdLead batches ahead); code rows and slots are random 4..16-byte reads, which
+      // cp.async handles badly (one L1 line per request, ~100 requests in flight per warp), so they are plain loads into
+      // registers, one batch in flight while the previous one is stored into the rings and published.
+      const uint32_t pw = (uint32_t)(warp - C);
       const uint32_t my_ids_w = ids_w + pw * (kIdLead + 1) * sub * ib;
       const uint32_t nb = (ne + batch - 1) / batch;
       bool ok = true;
-      for (uint32_t it = 0; it < nb + kIdLead + kRowLag; ++it) {
-        if (it < nb) {
-          const uint32_t b0 = it * batch + pw * sub;
-          const uint32_t n = b0 < ne ? min(sub, ne - b0) : 0u;
-          const uint32_t dst = my_ids_w + (it % (kIdLead + 1)) * sub * ib;
-          for (uint32_t j = lane; j < n; j += 32) cp_async<ib>(dst + j * ib, gids + b0 + j);
-        }
-        cp_async_commit();
-        cp_async_wait<2 * kIdLead>();
-        __syncwarp();
-        if (ok && it >= (uint32_t)kIdLead && it - kIdLead < nb) {
-          const uint32_t jb = it - kIdLead;
-          const uint32_t b0 = jb * batch + pw * sub;
-          const uint32_t n = b0 < ne ? min(sub, ne - b0) : 0u;
-          ok = wait_space(sync, C, b0 + n, cap, lane, error);
-          if (ok) {
-            const uint32_t src_ids = my_ids_w + (jb % (kIdLead + 1)) * sub * ib;
-            const uint32_t pos0 = b0 % cap;
-#pragma unroll 4
-            for (uint32_t e = lane; e < n; e += 32) {
-              const uint32_t id = lds_u32(src_ids + e * ib);
-              uint32_t pos = pos0 + e;
-              if (pos >= cap) pos -= cap;
-              const uint8_t* src = codes + (uint64_t)id * ROWB;
-              cp_async<ROWB>(codes_w + pos * ROWB, src);
-              if (HB != 0) cp_async<4>(slots_w + pos * 4u, p.slot + id);
-              if (pos < (uint32_t)kLongRow) {  // mirror behind the ring's end: rows never wrap
-                cp_async<ROWB>(codes_w + (pos + cap) * ROWB, src);
-                if (HB != 0) cp_async<4>(slots_w + (pos + cap) * 4u, p.slot + id);
+      CodeRow<ROWW> code_r[2][kPerLane];
+      int slot_r[2][kPerLane];
+#pragma unroll
+      for (int k = 0; k < kPerLane; ++k) { slot_r[0][k] = -1; slot_r[1][k] = -1; }
+      auto share_of = [&](uint32_t j, uint32_t& b0, uint32_t& n) {
+        b0 = j * batch + pw * sub;
+        n = (j < nb && b0 < ne) ? min(sub, ne - b0) : 0u;
+      };
+      for (uint32_t it0 = 0; it0 < nb + kIdLead + 1; it0 += 2) {
+#pragma unroll
+        for (int P = 0; P < 2; ++P) {
+          const uint32_t it = it0 + P;
+          uint32_t b0, n;
+          // (a) neighbour ids of batch `it`
+          share_of(it, b0, n);
+          {
+            const uint32_t dst = my_ids_w + (it % (kIdLead + 1)) * sub * ib;
+            for (uint32_t j = lane; j < n; j += 32) cp_async<ib>(dst + j * ib, gids + b0 + j);
+          }
+          cp_async_commit();
+          cp_async_wait<kIdLead>();
+          __syncwarp();
+          // (b) request code rows and slots of batch it - kIdLead (its ids have landed) into register set P
+          if (it >= (uint32_t)kIdLead) {
+            const uint32_t jl = it - kIdLead;
+            share_of(jl, b0, n);
+            const uint32_t src_ids = my_ids_w + (jl % (kIdLead + 1)) * sub * ib;
+#pragma unroll
+            for (int k = 0; k < kPerLane; ++k) {
+              const uint32_t e = lane + 32u * k;
+              if (e < n) {
+                const uint32_t id = lds_u32(src_ids + e * ib);
+                load_code_row<ROWW>(code_r[P][k], codes + (uint64_t)id * ROWB);
+                if (HB != 0) slot_r[P][k] = hot_slot_of(p, (int64_t)id);
               }
             }
           }
-        }
-        cp_async_commit();
-        cp_async_wait<2 * kRowLag>();
-        producer_barrier<kProducers>();  // every producer warp's share of that batch has landed
-        if (it >= (uint32_t)(kIdLead + kRowLag)) {
-          const uint32_t jc = it - kIdLead - kRowLag;
-          if (pw == 0 && lane == 0 && ld_acquire(&sync->abort) == 0u) st_release(&sync->staged, min((jc + 1) * batch, ne));
+          // (c) store batch it - kIdLead - 1 (register set P ^ 1, requested one iteration ago) and publish it
+          if (it >= (uint32_t)kIdLead + 1u) {
+            const uint32_t js = it - kIdLead - 1;
+            share_of(js, b0, n);
+            if (ok && n > 0) ok = wait_space(sync, C, b0 + n, cap, lane, error);
+            if (ok) {
+              const uint32_t pos0 = b0 % cap;
+#pragma unroll
+              for (int k = 0; k < kPerLane; ++k) {
+                const uint32_t e = lane + 32u * k;
+                if (e < n) {
+                  uint32_t pos = pos0 + e;
+                  if (pos >= cap) pos -= cap;
+                  store_code_row<ROWW>(codes_w + pos * ROWB, code_r[P ^ 1][k]);
+                  if (HB != 0) asm volatile("st.shared.s32 [%0], %1;" ::"r"(slots_w + pos * 4u), "r"(slot_r[P ^ 1][k]) : "memory");
+                  if (pos < (uint32_t)kLongRow) {  // mirror behind the ring's end: rows never wrap
+                    store_code_row<ROWW>(codes_w + (pos + cap) * ROWB, code_r[P ^ 1][k]);
+                    if (HB != 0) asm volatile("st.shared.s32 [%0], %1;" ::"r"(slots_w + (pos + cap) * 4u), "r"(slot_r[P ^ 1][k]) : "memory");
+                  }
+                }
+              }
+            }
+            producer_barrier<kProducers>();  // every producer warp's share of that batch is in the rings
+            if (js < nb && pw == 0 && lane == 0 && ld_acquire(&sync->abort) == 0u) st_release(&sync->staged, min((js + 1) * batch, ne));
+          } else {
+            producer_barrier<kProducers>();
+          }
         }
       }
       cp_async_wait<0>();
@@ -341,7 +383,7 @@ __global__ void __launch_bounds__(kThreads, 1) vq_stream_kernel(const VqParams p
                 int sl_mine = -1;
                 if (lane < n) {
                   id_mine = (int64_t)gids[beg[P] + k0 + lane];
-                  if (HB != 0) sl_mine = __ldg(p.slot + id_mine);
+                  if (HB != 0) sl_mine = hot_slot_of(p, id_mine);
                 }
                 for (int u = 0; u < n; ++u) {
                   const int sl_ = HB != 0 ? __shfl_sync(0xffffffffu, sl_mine, u) : -1;

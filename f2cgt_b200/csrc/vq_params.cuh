@@ -21,7 +21,8 @@ struct VqParams {
   // two-level extension
   const uint8_t* sq_codes;  // [n_hot, sq_row_bytes]
   const float* sq_codebooks;
-  const int32_t* slot;
+  const int32_t* slot;      // [n_src] row of the SQ table or -1; nullptr = hot-first numbering: source s is hot iff s < n_hot, row s
+  int64_t n_hot;
   int64_t sq_row_bytes;
   int sq_cs, sq_n_cb, sq_signed;
   // geometry of the codebooks staged by the pipelined kernel (fused_vq_fast.cu)
@@ -33,5 +34,11 @@ struct VqParams {
 // Streamed (fused_vq_stream.cu) or register-prefetch (fused_vq_fast.cu) kernel for the common shapes, by `variant`
 // (an f2c_kernel value); sets *served = false (and launches nothing) when the shape is not one of theirs.
 int launch_vq_fast(VqParams& p, int hot_bits, int index_dtype, int variant, cudaStream_t st, const char* op, bool* served);
+
+// Hot-row slot of source node `id`: looked up, or - with hot-first numbering (no slot array) - the id itself.
+__device__ __forceinline__ int hot_slot_of(const VqParams& p, int64_t id) {
+  if (p.slot != nullptr) return __ldg(p.slot + id);
+  return id < p.n_hot ? (int)id : -1;
+}
 
 }  // namespace f2c

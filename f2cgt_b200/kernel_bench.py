@@ -150,7 +150,7 @@ def cases(b):
 
     # ------------------------------------------------ fused VQ (configurations 3 and 4) and the two-level kernel
     for n_cb, cs, tag in ((16, 8, "config3_16x8"), (4, 32, "config4_4x32")):
-        if not b.wanted(f"vq_spmm_{tag}", "vq_decompress_4x32", "two_level_spmm_sq8_vq4x32"):
+        if not b.wanted(f"vq_spmm_{tag}", "vq_decompress_4x32", "two_level_spmm_sq8_vq4x32", "two_level_spmm_sq8_vq4x32_hot_first"):
             continue
         vq = torch.randint(0, 256, (N, n_cb), generator=g, dtype=torch.uint8, device=dev)
         cbs = torch.randn(n_cb, 256, cs, generator=g, device=dev)
@@ -177,7 +177,17 @@ def cases(b):
                   lambda: ops.two_level_decompress_spmm_csr(sq_hot, sq_cb, 8, FEAT, vq, cbs, slot, ip, ix, FEAT,
                                                             dropout=dict(p=0.5, seed=1, offset=0, training=True, scale=False)),
                   nbytes=nb, units=E, note="dropout fused in the epilogue")
-            del slot, sq_hot
+            # the same block with HOT-FIRST NUMBERING: nodes renumbered by descending degree, so the hot 5 % are ids
+            # 0 .. n_hot-1 and the kernel needs no slot array (same edges, same hot set; one random 4-byte read less per edge)
+            rank_of = torch.empty(N, dtype=torch.int64, device=dev)
+            rank_of[torch.argsort(deg, descending=True, stable=True)] = torch.arange(N, dtype=torch.int64, device=dev)
+            ix_hf = rank_of[ix].contiguous()
+            hot_hf = int((ix_hf < n_hot).sum())
+            nb_hf = (E - hot_hf) * (4 + 8) + hot_hf * (128 + 8) + (n_dst + 1) * 8 + n_dst * FEAT * 4 + cbs.numel() * 4 + 20
+            b.run("two_level_spmm_sq8_vq4x32_hot_first",
+                  lambda: ops.two_level_decompress_spmm_csr(sq_hot, sq_cb, 8, FEAT, vq, cbs, None, ip, ix_hf, FEAT),
+                  nbytes=nb_hf, units=E, note=f"E={E} hot edges={hot_hf} n_dst={n_dst}; hot nodes numbered first, no slot array")
+            del slot, sq_hot, rank_of, ix_hf
         del vq
 
     # ------------------------------------------------ two-level, configuration-5 codecs: D = 256, hot 2 % SQ 4 bits + VQ 4 x 64

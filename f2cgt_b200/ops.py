@@ -285,12 +285,14 @@ def fusion_decompress(sq_data, sq_codebooks, target_bits, column_slice, vq_data,
 def two_level_decompress_spmm_csr(sq_data, sq_codebooks, target_bits, column_slice, vq_data, vq_codebooks, slot, indptr,
                                   indices, feat_dim, reduce="mean", dropout=None, kernel="auto", check=False):
     """Two-level aggregation in one launch.  Source row s is decoded from row ``slot[s]`` of the SQ table
-    when ``slot[s] >= 0`` (int32), from row s of the VQ table otherwise; then the reference mean."""
+    when ``slot[s] >= 0`` (int32), from row s of the VQ table otherwise; then the reference mean.
+    ``slot=None``: hot-first numbering - the hot nodes are ids ``0 .. len(sq_data) - 1`` and node s reads SQ row s."""
     _chk(sq_data, "sq_data", (torch.uint8, torch.int8, torch.int16))
     _chk(sq_codebooks, "sq_codebooks", (torch.float32,))
     _chk(vq_data, "vq_data", (torch.uint8, torch.int8, torch.int16))
     _chk(vq_codebooks, "vq_codebooks", (torch.float32,))
-    _chk(slot, "slot", (torch.int32,))
+    if slot is not None:
+        _chk(slot, "slot", (torch.int32,))
     n_dst = _csc(indptr, indices)
     n_cb, K, cs = vq_codebooks.shape
     _check_block(check, indptr, indices, vq_data.shape[0])
@@ -299,7 +301,7 @@ def two_level_decompress_spmm_csr(sq_data, sq_codebooks, target_bits, column_sli
     with _on(vq_data):
         _lib.check(lib.f2c_hybrid_spmm_csr(_ptr(sq_data), _DT[sq_data.dtype], _ptr(sq_codebooks), sq_codebooks.shape[0],
                                       target_bits, column_slice, sq_data.shape[1], _ptr(vq_data), _DT[vq_data.dtype],
-                                      _ptr(vq_codebooks), n_cb, K, cs, _ptr(slot), _ptr(indptr), _ptr(indices),
+                                      _ptr(vq_codebooks), n_cb, K, cs, _ptr(slot), sq_data.shape[0], _ptr(indptr), _ptr(indices),
                                       _DT[indptr.dtype], _ptr(out), n_dst, feat_dim, _REDUCE[reduce], ep, _stream(vq_data)))
     return out
 

@@ -25,7 +25,7 @@ from . import ops
 class CompressionManager:
     """methods: ["sq"] | ["vq"] | ["sq", "vq"] (two-level: level 0 = hot rows, level 1 = every row)."""
 
-    def __init__(self, feat_dim, methods, configs, codebooks, tables, slot=None):
+    def __init__(self, feat_dim, methods, configs, codebooks, tables, slot=None, hot_first=False):
         self.feat_dim = int(feat_dim)
         self.methods = list(methods)
         self.configs = list(configs)      # per level (column_slice, target_bits) as the reference stores them
@@ -33,8 +33,10 @@ class CompressionManager:
         self.tables = list(tables)
         self.slot = slot                  # int32 [n_nodes]: row of the hot table, -1 for cold nodes (two-level only)
         self.is_two_level = len(self.methods) >= 2
-        if self.is_two_level and (self.methods != ["sq", "vq"] or slot is None):
-            raise ValueError("two-level compression is hot SQ rows over a VQ table, with a slot array")
+        # hot_first: the graph is numbered so that the hot nodes are ids 0 .. len(tables[0]) - 1 (no slot array, one random
+        # read less per edge)
+        if self.is_two_level and (self.methods != ["sq", "vq"] or (slot is None and not hot_first)):
+            raise ValueError("two-level compression is hot SQ rows over a VQ table, with a slot array or hot-first numbering")
 
     def aggregate(self, indptr, indices_global, dropout=None):
         if self.is_two_level:

@@ -172,11 +172,14 @@ int f2c_hybrid_decompress(const void* sq_codes, int sq_dtype, const float* sq_co
 /* Two-level aggregation in ONE launch (no counterpart kernel in the reference, which aggregates the
  * level-2 table only: examples/conv.py:56-66, examples/compress.py:58-61).  Source row s is decoded
  * from row slot[s] of the SQ table when slot[s] >= 0 and from row s of the VQ table otherwise;
- * value = reference decode of that codec, aggregation = reference mean (src/fusion_spmm.cu:24-42). */
+ * value = reference decode of that codec, aggregation = reference mean (src/fusion_spmm.cu:24-42).
+ * slot = NULL selects HOT-FIRST NUMBERING: the graph's nodes are numbered so that the n_hot hot ones come first,
+ * source row s is hot iff s < n_hot and its SQ row is row s.  That removes one random 4-byte read per edge (the
+ * slot lookup) and one link of the dependent load chain; with a slot array n_hot is ignored. */
 int f2c_hybrid_spmm_csr(const void* sq_codes, int sq_dtype, const float* sq_codebooks, int64_t sq_n_codebooks,
                         int bits, int64_t sq_column_slice, int64_t sq_src_dim, const void* vq_codes,
                         int vq_dtype, const float* vq_codebooks, int64_t vq_n_codebooks, int64_t length,
-                        int64_t vq_column_slice, const int32_t* slot, const void* indptr, const void* indices,
+                        int64_t vq_column_slice, const int32_t* slot, int64_t n_hot, const void* indptr, const void* indices,
                         int index_dtype, float* out, int64_t n_dst, int64_t feat_dim, int reduce,
                         const f2c_epilogue* epilogue, void* stream);
 

@@ -232,6 +232,14 @@ def test_two_level_is_composition(capi, oracle, bits, D, n_cb, cs):
         assert torch.equal(got, capi.spmm_csr(full, dev(indptr), dev(indices)))
         want = oracle.two_level_decompress_spmm_csr(sq, cb, bits, D, codes, cbs, slot, indptr, indices, D, acc64=True)
         assert close_to_oracle(host(got), want, host(capi.spmm_csr(full.abs(), dev(indptr), dev(indices))))
+    # hot-first numbering: no slot array, node s < n_hot reads SQ row s
+    prefix = np.where(np.arange(n_src) < n_hot, np.arange(n_src), -1).astype(np.int32)
+    for kernel in ("auto", "stream", "prefetch", "general"):
+        fn = lambda sl: capi.two_level_decompress_spmm_csr(dev(sq), dev(cb), bits, D, dev(codes), dev(cbs), sl, dev(indptr),  # noqa: E731
+                                                           dev(indices), D, kernel=kernel)
+        a = _served(lambda: fn(None))
+        if a is not None:
+            assert torch.equal(a, fn(dev(prefix))), kernel
     # all-cold and all-hot degenerate to the single-codec kernels
     cold = capi.two_level_decompress_spmm_csr(dev(sq), dev(cb), bits, D, dev(codes), dev(cbs), dev(np.full(n_src, -1, np.int32)),
                                               dev(indptr), dev(indices), D)
