@@ -537,7 +537,7 @@ def other_kernels_leg():
     try:
         import argparse as _ap
         from f2cgt_b200 import kernel_bench
-        b = kernel_bench.Bench(_ap.Namespace(only="vq_spmm,two_level", reps=10, small=False, launches=0, json=""))
+        b = kernel_bench.Bench(_ap.Namespace(only="vq_spmm,two_level", reps=10, small=False, launches=0, json="", kernel="auto"))
         kernel_bench.cases(b)
         return [{k: r[k] for k in ("kernel", "ms", "algorithmic_bytes", "gbs", "frac_of_hbm_peak", "edges_per_s", "note") if k in r}
                 for r in b.rows]

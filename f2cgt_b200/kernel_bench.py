@@ -1,13 +1,14 @@
 """Per-kernel micro-benchmark: every operator of the library on the shapes of the five benchmark
 configurations, timed with CUDA events and compared with the roofline that bounds it.
 
-    python -m f2cgt_b200.kernel_bench [--only SUBSTR] [--reps 20] [--small] [--json PATH] [--launches N]
+    python -m f2cgt_b200.kernel_bench [--only SUBSTR] [--reps 20] [--small] [--json PATH] [--launches N] [--kernel FAMILY]
 
 * fused aggregation kernels and decoders: algorithmic bytes / time against the measured HBM copy bandwidth;
 * k-means assignment: 2*n*k*d flops / time (reported beside the bytes figure).
 
 Between launches a 256 MiB read sweep evicts L2.  ``--small`` shrinks the tables so that one launch under a
-profiler stays short; ``--launches N`` runs each selected case exactly N times without timing (for a profiler).
+profiler stays short; ``--launches N`` runs each selected case exactly N times without timing (for a profiler);
+``--kernel stream|prefetch|general`` pins the kernel family of the fused aggregation cases (default: the library's choice).
 Synthetic, seeded inputs; graph and sampler are the ones of ``f2cgt_b200.synth``.
 """
 import argparse
@@ -43,6 +44,7 @@ class Bench:
         self.peak, self.peak_kind = hbm_peak()
         self._graph = None
         self._blocks = {}
+        self.kernel = getattr(args, "kernel", "auto") or "auto"
 
     # ---- workload pieces
     def n_nodes(self):
@@ -128,7 +130,7 @@ def cases(b):
             continue
         codes, cb = synth.sq_table_from_normal(N, FEAT, bits, FEAT, seed=0, device=dev)
         rb = codes.shape[1]
-        b.run(f"sq_spmm_{bits}bit", lambda c=codes, k=cb, w=bits: ops.sq_decompress_spmm_csr(c, k, ip, ix, w, FEAT, FEAT),
+        b.run(f"sq_spmm_{bits}bit", lambda c=codes, k=cb, w=bits: ops.sq_decompress_spmm_csr(c, k, ip, ix, w, FEAT, FEAT, kernel=b.kernel),
               nbytes=fused_bytes(E, n_dst, rb, 8, FEAT, 20), units=E, note=f"E={E} n_dst={n_dst} table {N}x{rb}B")
         if bits == 8:
             rows = min(N, 1_000_000)
@@ -154,7 +156,7 @@ def cases(b):
             continue
         vq = torch.randint(0, 256, (N, n_cb), generator=g, dtype=torch.uint8, device=dev)
         cbs = torch.randn(n_cb, 256, cs, generator=g, device=dev)
-        b.run(f"vq_spmm_{tag}", lambda c=vq, k=cbs: ops.vq_decompress_spmm_csr(c, k, ip, ix, FEAT),
+        b.run(f"vq_spmm_{tag}", lambda c=vq, k=cbs: ops.vq_decompress_spmm_csr(c, k, ip, ix, FEAT, kernel=b.kernel),
               nbytes=fused_bytes(E, n_dst, n_cb, 8, FEAT, cbs.numel() * 4), units=E, note=f"E={E} n_dst={n_dst}")
         if n_cb == 4:
             rows = min(N, 1_000_000)
@@ -171,7 +173,7 @@ def cases(b):
             hot_edges = int((slot[ix] >= 0).sum())
             nb = (E - hot_edges) * (4 + 8 + 4) + hot_edges * (128 + 8 + 4) + (n_dst + 1) * 8 + n_dst * FEAT * 4 + cbs.numel() * 4 + 20
             b.run("two_level_spmm_sq8_vq4x32",
-                  lambda: ops.two_level_decompress_spmm_csr(sq_hot, sq_cb, 8, FEAT, vq, cbs, slot, ip, ix, FEAT),
+                  lambda: ops.two_level_decompress_spmm_csr(sq_hot, sq_cb, 8, FEAT, vq, cbs, slot, ip, ix, FEAT, kernel=b.kernel),
                   nbytes=nb, units=E, note=f"E={E} hot edges={hot_edges} n_dst={n_dst}; 4 B/edge slot lookup counted")
             b.run("two_level_spmm_sq8_vq4x32_dropout",
                   lambda: ops.two_level_decompress_spmm_csr(sq_hot, sq_cb, 8, FEAT, vq, cbs, slot, ip, ix, FEAT,
@@ -252,6 +254,7 @@ def main():
     ap.add_argument("--small", action="store_true")
     ap.add_argument("--launches", type=int, default=0)
     ap.add_argument("--json", default="")
+    ap.add_argument("--kernel", default="auto", choices=["auto", "stream", "prefetch", "general"])
     args = ap.parse_args()
     b = Bench(args)
     cases(b)
