@@ -462,8 +462,8 @@ def run_ours(args):
         from f2cgt_b200 import train_graphsage
         del flush
         torch.cuda.empty_cache()
-        for table in ("replicated", "sharded"):
-            if table == "sharded" and world == 1:
+        for table in ("replicated", "sharded_peer", "sharded"):
+            if table != "replicated" and world == 1:
                 continue
             try:
                 rec = train_graphsage.train("small", table, rank, world, local_rank, epochs=2, min_timed_steps=100)

@@ -61,6 +61,8 @@ SIGNATURES = {
     "f2c_vq_spmm_csr": [p, ci, p, p, p, ci, p, i64, i64, i64, i64, i64, ci, EP, p],
     "f2c_hybrid_decompress": [p, ci, p, i64, ci, i64, i64, i64, p, ci, p, i64, i64, i64, i64, p, i64, p],
     "f2c_hybrid_spmm_csr": [p, ci, p, i64, ci, i64, i64, p, ci, p, i64, i64, i64, p, i64, p, p, ci, p, i64, i64, ci, EP, p],
+    "f2c_hybrid_spmm_csr_peer": [p, p, p, ci, i64, i64, i64, i64, ci, p, i64, ci, i64, i64, ci, p, i64, i64, i64, p, p, ci, p, i64, i64,
+                                 ci, EP, p],
     "f2c_dropout": [p, i64, f32, ci, u64, u64, ci, p],
     "f2c_pairwise_distance": [p, p, p, i64, i64, i64, ci, p],
     "f2c_kmeans_assign_workspace": [i64, i64, i64],

@@ -71,7 +71,9 @@ template <int ROWW> __device__ __forceinline__ void load_code_row(CodeRow<ROWW>&
 }
 
 // HB = 0: VQ only.  HB = 8 / 4: two-level with 8- / 4-bit hot rows.  ROWW = 32-bit words of one VQ code row.
-template <int HB, typename IdxT, int ROWW>
+// PEER: the three tables are row-sharded over the GPUs of the box and every shard is mapped into this process; rows of
+// other ranks are read with ordinary loads over NVLink (no collective, no staging copy, nothing waits on another rank).
+template <int HB, typename IdxT, int ROWW, bool PEER = false>
 __global__ void __launch_bounds__(VqCta<HB>::kThreads, 1) vq_fast_kernel(const VqParams p) {
   constexpr int kThreads = VqCta<HB>::kThreads, kWarps = VqCta<HB>::kWarps;
   extern __shared__ __align__(128) unsigned char smem[];
@@ -141,7 +143,8 @@ __global__ void __launch_bounds__(VqCta<HB>::kThreads, 1) vq_fast_kernel(const V
   const uint32_t cb_addr = smem_u32(cb_s) + lane_base;
   uint32_t* wbuf = reinterpret_cast<uint32_t*>(wbuf_all) + wid * 32 * ROWW;
   const uint32_t wb_addr = smem_u32(wbuf) + (uint32_t)s;  // byte s of every staged code row
-  const uint8_t* hot_base = HB != 0 ? p.sq_codes + (colc * (HB == 0 ? 8 : HB)) / 8 : nullptr;
+  const uint32_t hot_col_off = (uint32_t)((colc * (HB == 0 ? 8 : HB)) / 8);
+  const uint8_t* hot_base = (HB != 0 && !PEER) ? p.sq_codes + hot_col_off : nullptr;
   const uint32_t hot_row_bytes = (uint32_t)p.sq_row_bytes;
   const bool clamp = K < 256;
 
@@ -168,8 +171,26 @@ __global__ void __launch_bounds__(VqCta<HB>::kThreads, 1) vq_fast_kernel(const V
     }
   };
   auto load_hot = [&](int sl_) -> uint32_t {
-    const uint8_t* q = hot_base + (uint64_t)(uint32_t)sl_ * hot_row_bytes;
+    const uint8_t* q;
+    if (PEER) {
+      const uint32_t owner = (uint32_t)__umul64hi((unsigned long long)(uint32_t)sl_, p.peer.magic_hot);
+      q = p.peer.hot[owner] + hot_col_off + (uint64_t)((uint32_t)sl_ - owner * p.peer.rps_hot) * hot_row_bytes;
+    } else {
+      q = hot_base + (uint64_t)(uint32_t)sl_ * hot_row_bytes;
+    }
     return HB == 8 ? ldg_nc_u32(q) : ldg_nc_u16(q);
+  };
+  // code row and slot of source node `id`
+  auto fetch_node = [&](int64_t id, CodeRow<ROWW>& c, int& sl_) {
+    if (PEER) {
+      const uint32_t owner = (uint32_t)__umul64hi((unsigned long long)id, p.peer.magic_nodes);
+      const uint32_t local = (uint32_t)id - owner * p.peer.rps_nodes;
+      load_code_row<ROWW>(c, p.peer.code[owner] + (uint64_t)local * ROWB);
+      if (HB != 0) sl_ = p.peer.slot[0] != nullptr ? __ldg(p.peer.slot[owner] + local) : (id < p.n_hot ? (int)id : -1);
+    } else {
+      load_code_row<ROWW>(c, codes + id * ROWB);
+      if (HB != 0) sl_ = hot_slot_of(p, id);
+    }
   };
   auto stage_codes = [&](const CodeRow<ROWW>& c, int cnt) {
     if (lane < cnt) {
@@ -253,8 +274,7 @@ __global__ void __launch_bounds__(VqCta<HB>::kThreads, 1) vq_fast_kernel(const V
         int sl_mine = -1;
         if (lane < cnt) {
           const int64_t id = (int64_t)indices[k0 + lane];
-          load_code_row<ROWW>(c, codes + id * ROWB);
-          if (HB != 0) sl_mine = hot_slot_of(p, id);
+          fetch_node(id, c, sl_mine);
         }
         __syncwarp();
         stage_codes(c, cnt);
@@ -302,8 +322,7 @@ __global__ void __launch_bounds__(VqCta<HB>::kThreads, 1) vq_fast_kernel(const V
       slot3 = -1;
       if (on && lane < min(deg2, 32)) {
         const int64_t id = (int64_t)idx2;
-        load_code_row<ROWW>(code3, codes + id * ROWB);
-        if (HB != 0) slot3 = hot_slot_of(p, id);
+        fetch_node(id, code3, slot3);
       }
     }
     // ================= stage 1: row rP - W: its indptr pair has arrived; fetch the neighbour ids
@@ -318,11 +337,11 @@ __global__ void __launch_bounds__(VqCta<HB>::kThreads, 1) vq_fast_kernel(const V
   }
 }
 
-template <int HB, typename IdxT>
+template <int HB, typename IdxT, bool PEER>
 static int launch_rows(const VqParams& p, int roww, dim3 grid, size_t smem, cudaStream_t st, const char* op) {
 #define F2C_VQF(RW)                                                                                      \
   {                                                                                                      \
-    auto kern = vq_fast_kernel<HB, IdxT, RW>;                                                            \
+    auto kern = vq_fast_kernel<HB, IdxT, RW, PEER>;                                                      \
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);  \
     if (e != cudaSuccess) return set_error(F2C_ERR_CUDA, "%s: %s", op, cudaGetErrorString(e));           \
     kern<<<grid, VqCta<HB>::kThreads, smem, st>>>(p);                                                               \
@@ -338,22 +357,26 @@ static int launch_rows(const VqParams& p, int roww, dim3 grid, size_t smem, cuda
 
 int launch_vq_stream(VqParams& p, int hot_bits, int index_dtype, cudaStream_t st, const char* op, bool* served);
 
-int launch_vq_fast(VqParams& p, int hot_bits, int index_dtype, int variant, cudaStream_t st, const char* op, bool* served) {
+int launch_vq_fast(VqParams& p, int hot_bits, int index_dtype, int variant, cudaStream_t st, const char* op, bool* served,
+                   bool peer) {
   using namespace vqf;
   *served = false;
+  if (peer && variant == F2C_KERNEL_STREAM) return F2C_OK;  // sharded tables: this file's kernel only
   // The streamed kernels are selectable but not the default here: on B200 (same block as above) VQ 16 x 8 ties (41-43 us),
   // VQ 4 x 32 is 45-49 us against 35 us and the two-level op 130-140 us against 64 us for this file's kernel.
   if (variant == F2C_KERNEL_STREAM) return launch_vq_stream(p, hot_bits, index_dtype, st, op, served);
+  const void* codes_base = peer ? (const void*)p.peer.code[0] : p.codes;
+  const void* hot_table = peer ? (const void*)p.peer.hot[0] : (const void*)p.sq_codes;
   const int cs = p.cs;
   const int64_t row_bytes = p.n_cb;  // uint8 codes
   if (p.code_kind != 0 || p.K > 256 || p.n_dst >= (1ll << 30)) return F2C_OK;
-  if (!(row_bytes == 4 || row_bytes == 8 || row_bytes == 16) || !aligned(p.codes, (size_t)row_bytes)) return F2C_OK;
+  if (!(row_bytes == 4 || row_bytes == 8 || row_bytes == 16) || !aligned(codes_base, (size_t)row_bytes)) return F2C_OK;
   if (cs < 4 || cs > 128 || (128 % cs) != 0 || p.feat_dim % 4 != 0 || !aligned(p.out, 16) || !aligned(p.codebooks, 16)) return F2C_OK;
   if (!(hot_bits == 0 || hot_bits == 8 || hot_bits == 4)) return F2C_OK;
   if (hot_bits != 0) {
     if (p.sq_n_cb > 1 && p.sq_cs % 4 != 0) return F2C_OK;
     const int align = hot_bits == 8 ? 4 : 2;
-    if (p.sq_row_bytes % align != 0 || p.sq_row_bytes >= (1ll << 31) || !aligned(p.sq_codes, align)) return F2C_OK;
+    if (p.sq_row_bytes % align != 0 || p.sq_row_bytes >= (1ll << 31) || !aligned(hot_table, align)) return F2C_OK;
   }
   // a column part = at most 128 columns whose codebooks fit beside the table and the code tiles
   const int sub_per_128 = 128 / cs;
@@ -379,10 +402,14 @@ int launch_vq_fast(VqParams& p, int hot_bits, int index_dtype, int variant, cuda
   dim3 grid((unsigned)grid_x, (unsigned)parts);
   const size_t smem = (size_t)p.fast_cb_bytes + fixed;
   *served = true;
-#define F2C_VQF_IDX(HB) \
-  return index_dtype == F2C_I32 ? launch_rows<HB, int32_t>(p, roww, grid, smem, st, op) : launch_rows<HB, int64_t>(p, roww, grid, smem, st, op)
-  if (hot_bits == 0) F2C_VQF_IDX(0);
-  if (hot_bits == 8) F2C_VQF_IDX(8);
+#define F2C_VQF_IDX(HB)                                                                                                            \
+  if (peer)                                                                                                                        \
+    return index_dtype == F2C_I32 ? launch_rows<HB, int32_t, true>(p, roww, grid, smem, st, op)                                    \
+                                  : launch_rows<HB, int64_t, true>(p, roww, grid, smem, st, op);                                   \
+  return index_dtype == F2C_I32 ? launch_rows<HB, int32_t, false>(p, roww, grid, smem, st, op)                                     \
+                                : launch_rows<HB, int64_t, false>(p, roww, grid, smem, st, op)
+  if (hot_bits == 0) { F2C_VQF_IDX(0); }
+  if (hot_bits == 8) { F2C_VQF_IDX(8); }
   F2C_VQF_IDX(4);
 #undef F2C_VQF_IDX
 }

@@ -318,3 +318,72 @@ extern "C" int f2c_hybrid_spmm_csr(const void* sq_codes, int sq_dtype, const flo
   }
 #undef F2C_HY
 }
+
+// The two-level (or, without an SQ table, the plain VQ) aggregation over tables that are row-sharded across the GPUs of one
+// NVSwitch box: every shard pointer must be dereferenceable from the current device (own memory or a mapping made with
+// f2c_shard_open).  One kernel reads remote code rows, slots and hot rows itself over NVLink.
+extern "C" int f2c_hybrid_spmm_csr_peer(const void* const* sq_shards_host, const void* const* vq_shards_host,
+                                        const int32_t* const* slot_shards_host, int world, int64_t rows_per_shard,
+                                        int64_t hot_rows_per_shard, int64_t n_rows, int64_t n_hot, int sq_dtype,
+                                        const float* sq_codebooks, int64_t sq_n_codebooks, int bits, int64_t sq_column_slice,
+                                        int64_t sq_src_dim, int vq_dtype, const float* vq_codebooks, int64_t vq_n_codebooks,
+                                        int64_t length, int64_t vq_column_slice, const void* indptr, const void* indices,
+                                        int index_dtype, float* out, int64_t n_dst, int64_t feat_dim, int reduce,
+                                        const f2c_epilogue* epilogue, void* stream) {
+  const char* op = "two_level_decompress_spmm_csr_peer";
+  const bool two_level = sq_shards_host != nullptr;
+  F2C_REQUIRE(n_dst >= 0 && n_rows >= 0 && n_hot >= 0, F2C_ERR_INVALID, "%s: negative size", op);
+  F2C_REQUIRE(world >= 1 && world <= 8, F2C_ERR_LIMIT, "%s: 1 to 8 shards (got %d)", op, world);
+  F2C_REQUIRE(vq_shards_host != nullptr, F2C_ERR_INVALID, "%s: null pointer", op);
+  F2C_REQUIRE(rows_per_shard >= 2 && rows_per_shard < (1ll << 32) && rows_per_shard * world >= n_rows, F2C_ERR_INVALID,
+              "%s: %d shards of %lld rows do not cover %lld rows", op, world, (long long)rows_per_shard, (long long)n_rows);
+  int rc = validate_vq(op, vq_dtype, vq_n_codebooks, length, vq_column_slice, feat_dim);
+  if (rc) return rc;
+  F2C_REQUIRE(is_index_dtype(index_dtype), F2C_ERR_UNSUPPORTED, "%s: indptr/indices must be int32 or int64", op);
+  F2C_REQUIRE(reduce == F2C_MEAN || reduce == F2C_SUM, F2C_ERR_INVALID, "%s: reduce must be mean or sum", op);
+  F2C_REQUIRE(n_dst * feat_dim == 0 || (indptr && out && vq_codebooks), F2C_ERR_INVALID, "%s: null pointer", op);
+  VqParams p{};
+  int64_t sq_row_bytes = 0;
+  if (two_level) {
+    rc = validate_sq(op, sq_dtype, sq_n_codebooks, sq_src_dim, feat_dim, bits, sq_column_slice);
+    if (rc) return rc;
+    F2C_REQUIRE(sq_codebooks != nullptr, F2C_ERR_INVALID, "%s: null pointer", op);
+    F2C_REQUIRE(hot_rows_per_shard >= 2 && hot_rows_per_shard < (1ll << 32) && hot_rows_per_shard * world >= n_hot, F2C_ERR_INVALID,
+                "%s: %d shards of %lld hot rows do not cover %lld", op, world, (long long)hot_rows_per_shard, (long long)n_hot);
+    F2C_REQUIRE(feat_dim % 4 == 0 && vq_column_slice % 4 == 0 && (sq_n_codebooks == 1 || sq_column_slice % 4 == 0),
+                F2C_ERR_UNSUPPORTED, "%s: feat_dim and both column_slice values must be multiples of 4", op);
+    sq_row_bytes = sq_src_dim * dtype_size(sq_dtype);
+  }
+  if (n_dst == 0 || feat_dim == 0) return F2C_OK;
+  for (int r = 0; r < world; ++r) {
+    rc = ensure_readable_from_current_device(vq_shards_host[r], op, "VQ", r);
+    if (rc) return rc;
+    p.peer.code[r] = (const uint8_t*)vq_shards_host[r];
+    if (two_level) {
+      rc = ensure_readable_from_current_device(sq_shards_host[r], op, "SQ", r);
+      if (rc) return rc;
+      p.peer.hot[r] = (const uint8_t*)sq_shards_host[r];
+      if (slot_shards_host != nullptr) {
+        rc = ensure_readable_from_current_device(slot_shards_host[r], op, "slot", r);
+        if (rc) return rc;
+        p.peer.slot[r] = slot_shards_host[r];
+      }
+    }
+  }
+  for (int r = world; r < 8; ++r) { p.peer.code[r] = p.peer.code[0]; p.peer.hot[r] = p.peer.hot[0]; p.peer.slot[r] = p.peer.slot[0]; }
+  p.peer.rps_nodes = (uint32_t)rows_per_shard;
+  p.peer.magic_nodes = ~0ull / (unsigned long long)rows_per_shard + 1ull;
+  p.peer.rps_hot = (uint32_t)(two_level ? hot_rows_per_shard : 2);
+  p.peer.magic_hot = ~0ull / (unsigned long long)p.peer.rps_hot + 1ull;
+  p.codes = p.peer.code[0]; p.codebooks = vq_codebooks; p.indptr = indptr; p.indices = indices; p.out = out; p.n_dst = n_dst;
+  p.n_cb = (int)vq_n_codebooks; p.cs = (int)vq_column_slice; p.feat_dim = (int)feat_dim; p.K = (uint32_t)length;
+  p.code_kind = vq_dtype == F2C_U8 ? 0 : vq_dtype == F2C_I8 ? 1 : 2;
+  p.reduce = reduce; p.vec_store = 1; p.drop = make_dropout(epilogue);
+  p.sq_codes = p.peer.hot[0]; p.sq_codebooks = sq_codebooks; p.slot = nullptr; p.n_hot = n_hot; p.sq_row_bytes = sq_row_bytes;
+  p.sq_cs = (int)sq_column_slice; p.sq_n_cb = (int)sq_n_codebooks; p.sq_signed = sq_dtype == F2C_I8;
+  bool served = false;
+  rc = launch_vq_fast(p, two_level ? bits : 0, index_dtype, F2C_KERNEL_PREFETCH, (cudaStream_t)stream, op, &served, true);
+  if (served || rc) return rc;
+  return set_error(F2C_ERR_UNSUPPORTED, "%s: shape not served by the sharded kernel (uint8 codes, 4/8/16 code bytes per row, "
+                                        "column_slice dividing 128, hot rows 8- or 4-bit)", op);
+}

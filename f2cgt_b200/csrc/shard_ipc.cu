@@ -12,6 +12,7 @@
 #include <string.h>
 
 #include "common.cuh"
+#include "vq_params.cuh"
 
 namespace f2c {
 #define F2C_IPC_CUDA(call)                                                                        \
@@ -22,6 +23,29 @@ namespace f2c {
       return set_error(F2C_ERR_CUDA, "%s: %s failed: %s", op, #call, cudaGetErrorString(e_));   \
     }                                                                                             \
   } while (0)
+int ensure_readable_from_current_device(const void* ptr, const char* op, const char* what, int index) {
+  int here = 0;
+  F2C_IPC_CUDA(cudaGetDevice(&here));
+  F2C_REQUIRE(ptr != nullptr, F2C_ERR_INVALID, "%s: %s shard %d is null", op, what, index);
+  cudaPointerAttributes attr{};
+  F2C_IPC_CUDA(cudaPointerGetAttributes(&attr, ptr));
+  F2C_REQUIRE(attr.type == cudaMemoryTypeDevice || attr.type == cudaMemoryTypeManaged, F2C_ERR_INVALID,
+              "%s: %s shard %d is not device memory", op, what, index);
+  if (attr.type == cudaMemoryTypeDevice && attr.device != here) {
+    int can = 0;
+    F2C_IPC_CUDA(cudaDeviceCanAccessPeer(&can, here, attr.device));
+    F2C_REQUIRE(can, F2C_ERR_UNSUPPORTED, "%s: GPU %d cannot read %s shard %d on GPU %d (no peer access)", op, here, what, index,
+                attr.device);
+    cudaError_t e = cudaDeviceEnablePeerAccess(attr.device, 0);
+    if (e == cudaErrorPeerAccessAlreadyEnabled) {
+      (void)cudaGetLastError();
+    } else {
+      F2C_IPC_CUDA(e);
+    }
+  }
+  return F2C_OK;
+}
+
 }  // namespace f2c
 
 using namespace f2c;

@@ -306,6 +306,39 @@ def two_level_decompress_spmm_csr(sq_data, sq_codebooks, target_bits, column_sli
     return out
 
 
+def two_level_decompress_spmm_csr_peer(sq_peers, sq_codebooks, target_bits, column_slice, vq_peers, vq_codebooks, slot_peers, indptr,
+                                       indices, feat_dim, reduce="mean", dropout=None):
+    """``two_level_decompress_spmm_csr`` (or, with ``sq_peers=None``, ``vq_decompress_spmm_csr``) over tables row-sharded across
+    the GPUs of the box (``f2cgt_b200.shard.PeerTable`` objects: VQ codes and slots sharded by node id, hot SQ rows by slot):
+    indices are global node ids, the kernel reads remote rows itself over NVLink.  ``slot_peers=None``: hot-first numbering."""
+    import ctypes
+    _chk(vq_codebooks, "vq_codebooks", (torch.float32,))
+    n_dst = _csc(indptr, indices)
+    n_cb, K, cs = vq_codebooks.shape
+    world = vq_peers.world
+
+    def ptrs(t):
+        if t is None:
+            return None
+        if len(t.pointers) != world:
+            raise RuntimeError("a peer table is closed or spans another number of ranks")
+        return (ctypes.c_void_p * world)(*t.pointers)
+    two = sq_peers is not None
+    if two:
+        _chk(sq_codebooks, "sq_codebooks", (torch.float32,))
+    out = torch.empty((n_dst, feat_dim), dtype=torch.float32, device=indptr.device)
+    ep = _epilogue(dropout)
+    with _on(indptr):
+        check(lib.f2c_hybrid_spmm_csr_peer(ptrs(sq_peers), ptrs(vq_peers), ptrs(slot_peers), world, vq_peers.rpr,
+                                           sq_peers.rpr if two else 0, vq_peers.n_rows, sq_peers.n_rows if two else 0,
+                                           _DT[sq_peers.dtype] if two else _lib.I8, _ptr(sq_codebooks) if two else 0,
+                                           sq_codebooks.shape[0] if two else 1, int(target_bits) if two else 8, int(column_slice) if two else 1,
+                                           sq_peers.row_width if two else 1, _DT[vq_peers.dtype], _ptr(vq_codebooks), n_cb, K, cs,
+                                           _ptr(indptr), _ptr(indices), _DT[indptr.dtype], _ptr(out), n_dst, feat_dim, _REDUCE[reduce], ep,
+                                           _stream(indptr)))
+    return out
+
+
 # ------------------------------------------------------------------ dropout
 def dropout_inplace(output, p, is_training, seed=None, offset=0, scale=False):
     """src/fusion_dropout.cu:21-29: zero with probability p when training, survivors unchanged

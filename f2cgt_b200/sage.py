@@ -97,6 +97,44 @@ class ShardedCompressionManager:
         return local, block["indices_local"], dst_local
 
 
+class PeerCompressionManager:
+    """The same compressed feature matrix with every table row-sharded over the ranks AND mapped into every rank
+    (``f2cgt_b200.shard.PeerTable``, CUDA IPC): the fused kernel reads the rows other ranks own over NVLink while it
+    aggregates, so a minibatch needs no exchange step at all.  Construct and ``close`` it collectively.
+
+    local_tables / table_rows as for ``ShardedCompressionManager``: [hot SQ shard, VQ shard] (two-level) or [VQ shard]."""
+
+    def __init__(self, feat_dim, methods, configs, codebooks, local_tables, table_rows, local_slot=None, group=None):
+        from . import shard
+        self.feat_dim, self.methods, self.configs, self.codebooks = int(feat_dim), list(methods), list(configs), list(codebooks)
+        self.is_two_level = len(self.methods) >= 2
+        if self.methods not in (["vq"], ["sq", "vq"]):
+            raise ValueError("the sharded kernel serves a VQ table, alone or under hot SQ rows")
+        self.level2 = shard.PeerTable(local_tables[-1].contiguous(), table_rows[-1], group)
+        self.hot = self.slot = None
+        if self.is_two_level:
+            self.hot = shard.PeerTable(local_tables[0].contiguous(), table_rows[0], group)
+            if local_slot is not None:  # None: hot-first numbering
+                self.slot = shard.PeerTable(local_slot.reshape(-1, 1).contiguous(), table_rows[-1], group)
+
+    def aggregate(self, indptr, indices_global, dropout=None):
+        cs, bits = self.configs[0] if self.is_two_level else (1, 8)
+        return ops.two_level_decompress_spmm_csr_peer(self.hot, self.codebooks[0] if self.is_two_level else None, bits, cs, self.level2,
+                                                      self.codebooks[-1], self.slot, indptr, indices_global, self.feat_dim, dropout=dropout)
+
+    def decode_rows(self, nodes):
+        ident = torch.arange(nodes.numel() + 1, dtype=nodes.dtype, device=nodes.device)
+        return self.aggregate(ident, nodes)
+
+    def for_block(self, block):
+        return self, block["indices_global"], block["dst_nodes"]
+
+    def close(self):
+        for t in (self.slot, self.hot, self.level2):
+            if t is not None:
+                t.close()
+
+
 def _bucket(n):
     """Row counts of sampled blocks change every step; the matrix products behind the Linear layers pick (and cache)
     their algorithms per shape, so inputs are zero-padded to a few recurring row counts."""

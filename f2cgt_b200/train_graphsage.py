@@ -61,13 +61,13 @@ def build_data(cfg, device, index_dtype, table="replicated"):
     labels = torch.randint(0, cfg["classes"], (n,), generator=g, device=device)
     train_ids = torch.randperm(n, generator=g, device=device)[:cfg["train"]].to(index_dtype)
     methods, configs, cbs = ["sq", "vq"], [(cfg["feat"], bits), (cs, 8)], [sq_cb, vq_cbs]
-    if table == "sharded":  # every rank keeps only its row shard of the three tables
+    if table in ("sharded", "sharded_peer"):  # every rank keeps only its row shard of the three tables
         from f2cgt_b200 import shard
         rank, world = dist.get_rank(), dist.get_world_size()
         lo, hi = shard.shard_bounds(n, world, rank)
         hlo, hhi = shard.shard_bounds(n_hot, world, rank)
-        cm = sage.ShardedCompressionManager(cfg["feat"], methods, configs, cbs, [sq_codes[hlo:hhi].clone(), vq_codes[lo:hi].clone()],
-                                            [n_hot, n], slot[lo:hi].clone())
+        kind = sage.ShardedCompressionManager if table == "sharded" else sage.PeerCompressionManager
+        cm = kind(cfg["feat"], methods, configs, cbs, [sq_codes[hlo:hhi].clone(), vq_codes[lo:hi].clone()], [n_hot, n], slot[lo:hi].clone())
         del sq_codes, vq_codes, slot
         torch.cuda.empty_cache()
     else:
@@ -152,6 +152,9 @@ def train(preset="small", table="replicated", rank=0, world=1, local_rank=0, epo
         sm = stats.clone(); dist.all_reduce(sm, op=dist.ReduceOp.SUM)
         stats = torch.cat([mx[:1], sm[1:2], mx[2:]])
     stats = stats.tolist()
+    if hasattr(cm, "close"):
+        torch.cuda.synchronize()
+        cm.close()
     return {
         "metric": "graphsage_epoch_seconds", "value": stats[0], "unit": "s/epoch", "n_gpus": world, "preset": preset,
         "steps_per_epoch_per_gpu": steps, "timed_steps_per_gpu": timed_steps, "batch_size": batch_size, "epochs_run": epochs,
@@ -175,8 +178,9 @@ def main():
     ap.add_argument("--max-steps", type=int, default=0, help="cut every epoch after this many steps (0 = whole epoch)")
     ap.add_argument("--min-timed-steps", type=int, default=0, help="run enough epochs to time at least this many steps")
     ap.add_argument("--no-autocast", action="store_true")
-    ap.add_argument("--table", default="replicated", choices=["replicated", "sharded"],
-                    help="sharded: every table row-sharded over the ranks, rows fetched per minibatch with an all-to-all exchange")
+    ap.add_argument("--table", default="replicated", choices=["replicated", "sharded", "sharded_peer"],
+                    help="sharded: every table row-sharded over the ranks, rows fetched per minibatch with an all-to-all exchange; "
+                         "sharded_peer: the same shards mapped into every rank, the fused kernel reads remote rows over NVLink")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", 0))
@@ -184,7 +188,7 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", 0))
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)
-    if world > 1 or args.table == "sharded":
+    if world > 1 or args.table != "replicated":
         if world == 1:
             os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
             os.environ.setdefault("MASTER_PORT", "29577")

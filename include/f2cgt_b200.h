@@ -183,6 +183,21 @@ int f2c_hybrid_spmm_csr(const void* sq_codes, int sq_dtype, const float* sq_code
                         int index_dtype, float* out, int64_t n_dst, int64_t feat_dim, int reduce,
                         const f2c_epilogue* epilogue, void* stream);
 
+/* The two-level aggregation (sq_shards_host != NULL) or the plain VQ aggregation (sq_shards_host == NULL, SQ arguments
+ * ignored) over tables row-sharded across the GPUs of one box, like f2c_sq_spmm_csr_peer: node row r (VQ codes, slot) is
+ * row r % rows_per_shard of shard r / rows_per_shard, hot row h is row h % hot_rows_per_shard of SQ shard
+ * h / hot_rows_per_shard; the *_shards_host arrays are HOST arrays of `world` (<= 8) device pointers dereferenceable from
+ * the current device.  slot_shards_host == NULL = hot-first numbering (node s < n_hot reads hot row s).  Served for the
+ * shapes of the fast kernel (uint8 codes, 4/8/16 code bytes per row, column_slice dividing 128, 8- or 4-bit hot rows). */
+int f2c_hybrid_spmm_csr_peer(const void* const* sq_shards_host, const void* const* vq_shards_host,
+                             const int32_t* const* slot_shards_host, int world, int64_t rows_per_shard,
+                             int64_t hot_rows_per_shard, int64_t n_rows, int64_t n_hot, int sq_dtype,
+                             const float* sq_codebooks, int64_t sq_n_codebooks, int bits, int64_t sq_column_slice,
+                             int64_t sq_src_dim, int vq_dtype, const float* vq_codebooks, int64_t vq_n_codebooks,
+                             int64_t length, int64_t vq_column_slice, const void* indptr, const void* indices,
+                             int index_dtype, float* out, int64_t n_dst, int64_t feat_dim, int reduce,
+                             const f2c_epilogue* epilogue, void* stream);
+
 /* dropout_inplace(output, p, is_training)  -  src/fusion_dropout.cu:21-29 (kernel :6-19), which the
  * reference defines but never binds.  Counter-based (Philox4x32-10) instead of a time-seeded
  * per-thread XORWOW state, so a (seed, offset) pair reproduces the mask. */

@@ -429,3 +429,42 @@ def test_peer_sharded_table_equals_whole_table(capi, oracle, bits, world):
     got = ops.sq_decompress_spmm_csr_peer(pt, dev(cb), dev(indptr), dev(indices), bits, 128, D)
     want = capi.sq_decompress_spmm_csr(table, dev(cb), dev(indptr), dev(indices), bits, 128, D)
     assert torch.equal(got, want)
+
+
+@pytest.mark.parametrize("hot_bits,D,n_cb,cs", [(8, 128, 4, 32), (4, 256, 4, 64), (8, 128, 16, 8), (0, 128, 4, 32)])
+@pytest.mark.parametrize("world,hot_first", [(2, False), (3, True), (8, False)])
+def test_two_level_over_sharded_tables_equals_whole_tables(capi, oracle, hot_bits, D, n_cb, cs, world, hot_first):
+    """The sharded two-level / VQ entry point with every shard on this GPU (the pointers could as well be peer mappings)."""
+    from f2cgt_b200 import ops, shard
+    rng = np.random.default_rng(hot_bits + world + D)
+    n_src, n_hot, n_dst = 1003, 101, 400
+    cbs = dev(rng.standard_normal((n_cb, 256, cs)).astype(np.float32))
+    codes = dev(rng.integers(0, 256, (n_src, n_cb)).astype(np.uint8))
+    indptr, indices = random_csc(rng, n_dst, n_src, max_deg=40)
+    ip, ix = dev(indptr), dev(indices)
+
+    class Peers:  # what shard.PeerTable exposes
+        def __init__(self, table, n_rows):
+            self.world, self.n_rows = world, n_rows
+            self.rpr = shard.rows_per_rank(n_rows, world)
+            self.keep = [table[r * self.rpr:(r + 1) * self.rpr].clone() if r * self.rpr < n_rows else table[:1].clone() for r in range(world)]
+            self.pointers = [t.data_ptr() for t in self.keep]
+            self.dtype, self.row_width = table.dtype, table.shape[1]
+    vq_peers = Peers(codes, n_src)
+    if hot_bits == 0:
+        got = ops.two_level_decompress_spmm_csr_peer(None, None, 0, 0, vq_peers, cbs, None, ip, ix, D)
+        assert torch.equal(got, capi.vq_decompress_spmm_csr(codes, cbs, ip, ix, D))
+        return
+    _, cb, sq = sq_table(oracle, rng, n_hot, D, hot_bits, D)
+    sq_t = dev(sq)
+    if hot_first:
+        slot = torch.where(torch.arange(n_src, device="cuda") < n_hot, torch.arange(n_src, device="cuda"), -1).to(torch.int32)
+        slot_peers = None
+    else:
+        slot_np = np.full(n_src, -1, np.int32)
+        slot_np[rng.choice(n_src, n_hot, replace=False)] = rng.permutation(n_hot).astype(np.int32)
+        slot = dev(slot_np)
+        slot_peers = Peers(slot.reshape(-1, 1), n_src)
+    got = ops.two_level_decompress_spmm_csr_peer(Peers(sq_t, n_hot), dev(cb), hot_bits, D, vq_peers, cbs, slot_peers, ip, ix, D)
+    want = capi.two_level_decompress_spmm_csr(sq_t, dev(cb), hot_bits, D, codes, cbs, slot, ip, ix, D)
+    assert torch.equal(got, want)

@@ -139,6 +139,19 @@ def _manager_worker(rank, world, port, q):
             sm, neigh, dst = parts.for_block(b)
             assert torch.equal(sm.aggregate(b["indptr"], neigh), whole.aggregate(b["indptr"], b["indices_global"]))
             assert torch.equal(sm.decode_rows(dst), whole.decode_rows(b["dst_nodes"]))
+        # the same shards mapped into every rank: the kernel reads remote code rows, slots and hot rows itself (no exchange)
+        peers = sage.PeerCompressionManager(D, methods, configs, cbs, [sq_codes[hlo:hhi].clone(), vq_codes[lo:hi].clone()],
+                                            [n_hot, n], slot[lo:hi].clone())
+        sm, neigh, dst = peers.for_block(b)
+        assert torch.equal(sm.aggregate(b["indptr"], neigh), whole.aggregate(b["indptr"], b["indices_global"]))
+        assert torch.equal(sm.decode_rows(dst), whole.decode_rows(b["dst_nodes"]))
+        torch.cuda.synchronize()
+        peers.close()
+        vq_peers = sage.PeerCompressionManager(D, ["vq"], [(32, 8)], [vq_cbs], [vq_codes[lo:hi].clone()], [n])
+        ref_vq = sage.CompressionManager(D, ["vq"], [(32, 8)], [vq_cbs], [vq_codes])
+        assert torch.equal(vq_peers.aggregate(b["indptr"], b["indices_global"]), ref_vq.aggregate(b["indptr"], b["indices_global"]))
+        torch.cuda.synchronize()
+        vq_peers.close()
         # single-level table through the same path
         one = sage.ShardedCompressionManager(D, ["vq"], [(32, 8)], [vq_cbs], [vq_codes[lo:hi].clone()], [n])
         sm, neigh, dst = one.for_block(b)
