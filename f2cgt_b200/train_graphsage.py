@@ -1,6 +1,6 @@
 """GraphSAGE node classification over two-level compressed features: the training loop of the reference's
 examples/train_graphsage_nodeclass.py (3-layer SAGE, fused first layer, Adam lr 0.003, ExponentialLR 0.978, one
-process per GPU, DistributedDataParallel gradient all-reduce over NCCL) on seeded synthetic data with the shapes of
+process per GPU, gradients all-reduced over NCCL every step) on seeded synthetic data with the shapes of
 the benchmark configurations, reporting seconds per epoch.
 
     python -m f2cgt_b200.train_graphsage [--preset small|config4|config5] [--epochs 3]
@@ -88,7 +88,21 @@ def train(preset="small", table="replicated", rank=0, world=1, local_rank=0, epo
 
     torch.manual_seed(0)
     model = sage.SAGE(cfg["feat"], cfg["hidden"], cfg["classes"], len(cfg["fan_out"]), dropout, cm).to(device)
-    net = torch.nn.parallel.DistributedDataParallel(model, device_ids=[local_rank]) if world > 1 else model
+    net = model
+    flat_grad = None
+    if world > 1:
+        # Data parallel as the reference runs it (DistributedDataParallel, examples/train_graphsage_nodeclass.py:50-54): same
+        # initial weights on every rank, gradients averaged over the ranks with an NCCL all-reduce every step.  The model has
+        # ~0.1 M parameters, so the gradients live in ONE flat buffer (every p.grad is a view of it) and a step costs one
+        # all-reduce and one scale instead of DDP's bucket and hook machinery (measured: 0.5-0.8 ms per step).
+        params = [p for p in model.parameters() if p.requires_grad]
+        for p in params:
+            dist.broadcast(p.data, src=0)
+        flat_grad = torch.zeros(sum(p.numel() for p in params), dtype=torch.float32, device=device)
+        off = 0
+        for p in params:
+            p.grad = flat_grad[off:off + p.numel()].view_as(p)
+            off += p.numel()
     optimizer = torch.optim.Adam(net.parameters(), lr=lr)
     scheduler = torch.optim.lr_scheduler.ExponentialLR(optimizer, gamma=0.978)
     loader = sage.GPUSamplingDataloader(indptr, indices, train_ids, batch_size, cfg["fan_out"], rank, world, shuffle=True)
@@ -125,8 +139,14 @@ def train(preset="small", table="replicated", rank=0, world=1, local_rank=0, epo
                 pred = net(blocks)
             loss = F.cross_entropy(pred.float(), y)
             ev[3].record()
-            optimizer.zero_grad(set_to_none=True)
-            loss.backward()
+            if flat_grad is None:
+                optimizer.zero_grad(set_to_none=True)
+                loss.backward()
+            else:
+                flat_grad.zero_()  # the views stay attached to the parameters
+                loss.backward()
+                dist.all_reduce(flat_grad)
+                flat_grad.mul_(1.0 / world)
             ev[4].record()
             optimizer.step()
             ev[5].record()

@@ -102,7 +102,9 @@ def load():
 
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default=os.environ.get("F2CGT_REFERENCE", "/root/reference"))
+    here = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    ap.add_argument("--reference", default=os.environ.get("F2CGT_REFERENCE") or os.path.join(os.path.dirname(here), "reference"),
+                    help="checkout of gpzlx1/F2CGT (default: $F2CGT_REFERENCE, else a directory `reference` beside this repository)")
     ap.add_argument("--jobs", type=int, default=5)
     ap.add_argument("--force", action="store_true")
     a = ap.parse_args()
