@@ -76,10 +76,13 @@ SIGNATURES = {
     "f2c_relabel_assign": [p, ci, i64, p, p, i64, p, p, p, p, p],
     "f2c_sample_degrees": [p, p, p, ci, i64, ci, p],
     "f2c_sample_neighbors": [p, p, p, p, p, i64, ci, i64, ci, u64, u64, p],
+    "f2c_sample_block_workspace": [i64, ci, ci],
+    "f2c_sample_block": [p, p, p, ci, i64, ci, u64, u64, p, p, p, p, p, p, i64, p],
     "f2c_last_error": [],
     "f2c_version": [],
 }
-_RESTYPE = {"f2c_last_error": C.c_char_p, "f2c_kmeans_assign_workspace": C.c_int64, "f2c_relabel_capacity": C.c_int64}
+_RESTYPE = {"f2c_last_error": C.c_char_p, "f2c_kmeans_assign_workspace": C.c_int64, "f2c_relabel_capacity": C.c_int64,
+            "f2c_sample_block_workspace": C.c_int64}
 
 for _name, _args in SIGNATURES.items():
     _fn = getattr(lib, _name)  # AttributeError here = header and library out of step

@@ -521,3 +521,35 @@ def tensor_relabel(tensors):
         out.append(relabelled[off:off + t.numel()].reshape(t.shape))
         off += t.numel()
     return unique, out
+
+
+def sample_block(indptr, indices, seeds, num_pick, rng_seed=0, rng_offset=0):
+    """One hop of a block: ``csr_sampling`` followed by ``tensor_relabel([seeds, sub_indices])`` (the pair at
+    examples/dataloader.py:174-177) as ONE library call and one host read.  Returns ``(sub_indptr, sub_indices, unique,
+    local_indices)`` with the numbering of the separate operators; ``sub_indices`` / ``local_indices`` have
+    ``len(seeds) * num_pick`` entries of which the first ``sub_indptr[-1]`` are the block's edges (the rest repeat
+    ``seeds[0]`` and its new number, and no kernel reads them)."""
+    _chk(indptr, "indptr", (torch.int32, torch.int64))
+    _chk(indices, "indices", (indptr.dtype,))
+    _chk(seeds, "seeds", (indptr.dtype,))
+    n, dt, dev = seeds.numel(), indptr.dtype, indptr.device
+    if n == 0:
+        raise RuntimeError("sample_block: needs at least one seed")
+    n_keys = n * (int(num_pick) + 1)
+    ws_bytes = lib.f2c_sample_block_workspace(n, int(num_pick), _DT[dt])
+    if ws_bytes <= 0:
+        raise RuntimeError("sample_block: num_pick must be in [1, 64]")
+    with _on(indptr):
+        ws = torch.empty((ws_bytes,), dtype=torch.uint8, device=dev)
+        sub_indptr = torch.empty((n + 1,), dtype=dt, device=dev)
+        buf = torch.empty((3, n_keys), dtype=dt, device=dev)  # keys, unique, relabelled
+        header = torch.empty((4,), dtype=torch.int64, device=dev)
+        check(lib.f2c_sample_block(_ptr(indptr), _ptr(indices), _ptr(seeds), _DT[dt], n, int(num_pick),
+                                   int(rng_seed) & 0xFFFFFFFFFFFFFFFF, int(rng_offset), _ptr(sub_indptr), _ptr(buf[0]), _ptr(buf[1]),
+                                   _ptr(buf[2]), _ptr(header), _ptr(ws), ws_bytes, _stream(indptr)))
+        _nnz, n_unique, err, _ = header.tolist()
+    if err == 2:
+        raise RuntimeError("sample_block: negative id in the graph or the seeds")
+    if err != 0:
+        raise RuntimeError("sample_block: hash table overflow")
+    return sub_indptr, buf[0, n:], buf[1, :n_unique], buf[2, n:]

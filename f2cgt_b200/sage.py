@@ -254,11 +254,11 @@ class GPUSamplingDataloader:
         output_nodes = seeds
         blocks = []
         for hop, num_pick in enumerate(reversed(self.num_picks)):
-            # exact=False: no host read of the edge count; the index tensors carry a tail behind indptr[-1] that no kernel reads
-            sub_indptr, sub_indices = ops.csr_sampling(self.indptr, self.indices, seeds, num_pick, False,
-                                                       rng_seed=(self.rng_seed * 7919 + self.epoch) * 65536 + self.rank, rng_offset=step * 8 + hop,
-                                                       exact=False)
-            unique, (_, local) = ops.tensor_relabel([seeds, sub_indices])
+            # one library call and one host read (the number of distinct nodes) per hop; the index tensors carry a tail
+            # behind indptr[-1] that no kernel reads
+            sub_indptr, sub_indices, unique, local = ops.sample_block(
+                self.indptr, self.indices, seeds, num_pick,
+                rng_seed=(self.rng_seed * 7919 + self.epoch) * 65536 + self.rank, rng_offset=step * 8 + hop)
             blocks.insert(0, dict(dst_nodes=seeds, src_nodes=unique, indptr=sub_indptr, indices_global=sub_indices, indices_local=local))
             seeds = unique
         return seeds, output_nodes, blocks

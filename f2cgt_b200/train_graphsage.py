@@ -103,7 +103,7 @@ def train(preset="small", table="replicated", rank=0, world=1, local_rank=0, epo
         for p in params:
             p.grad = flat_grad[off:off + p.numel()].view_as(p)
             off += p.numel()
-    optimizer = torch.optim.Adam(net.parameters(), lr=lr)
+    optimizer = torch.optim.Adam(net.parameters(), lr=lr, fused=True)  # one kernel for all parameters (the model is tiny)
     scheduler = torch.optim.lr_scheduler.ExponentialLR(optimizer, gamma=0.978)
     loader = sage.GPUSamplingDataloader(indptr, indices, train_ids, batch_size, cfg["fan_out"], rank, world, shuffle=True)
     steps = torch.tensor([len(loader)], device=device)

@@ -268,6 +268,22 @@ int f2c_relabel_assign(const void* keys, int index_dtype, int64_t n_keys, const 
                        int64_t capacity, const int32_t* first, const void* rank, void* unique, void* relabelled,
                        void* stream);
 
+/* One hop of a minibatch block in one call: csr_sampling followed by tensor_relabel([seeds, sub_indices]), the pair the
+ * reference's loader runs per hop (examples/dataloader.py:167-182).  Same sampler, same numbering as the separate entry
+ * points above; the prefix sums run inside, so the host makes one call and one read per hop.
+ *   sub_indptr [n_seeds + 1]                CSC offsets of the block
+ *   keys       [n_seeds * (num_pick + 1)]   seeds, then the sampled global ids; entries behind n_seeds + sub_indptr[n_seeds]
+ *                                           are copies of seeds[0]
+ *   unique     [n_seeds * (num_pick + 1)]   distinct ids in order of first occurrence; the first header[1] are valid
+ *   relabelled [n_seeds * (num_pick + 1)]   keys rewritten to positions in unique
+ *   header_device [4] (int64, device)       {edges sampled, distinct ids, relabel error flag (0 ok, 1 table overflow,
+ *                                           2 negative id), 0}
+ * workspace: f2c_sample_block_workspace(n_seeds, num_pick, index_dtype) bytes of device memory, 256-byte aligned. */
+int64_t f2c_sample_block_workspace(int64_t n_seeds, int num_pick, int index_dtype);
+int f2c_sample_block(const void* indptr, const void* indices, const void* seeds, int index_dtype, int64_t n_seeds, int num_pick,
+                     uint64_t rng_seed, uint64_t rng_offset, void* sub_indptr, void* keys, void* unique, void* relabelled,
+                     int64_t* header_device, void* workspace, int64_t workspace_bytes, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

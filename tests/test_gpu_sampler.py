@@ -114,3 +114,37 @@ def test_relabel_rejects_negative_ids_and_padded_sampling_numbers_alike(capi):
     ua, (_, la) = ops.tensor_relabel([seeds, ix_a])
     ub, (_, lb) = ops.tensor_relabel([seeds, ix_b])
     assert torch.equal(ua, ub) and torch.equal(la, lb[:nnz])
+
+
+@pytest.mark.parametrize("idx", [np.int64, np.int32])
+@pytest.mark.parametrize("num_pick,n_seeds", [(1, 1), (5, 700), (12, 1000), (64, 33)])
+def test_sample_block_equals_the_separate_operators_and_the_oracle(capi, oracle, idx, num_pick, n_seeds):
+    """The one-call hop gives the sampler's CSC and the relabelling's numbering, bit for bit."""
+    from f2cgt_b200 import ops
+    rng = np.random.default_rng(num_pick * 31 + n_seeds)
+    indptr, indices = small_graph(rng, 3000, 40, idx)
+    seeds = rng.choice(3000, n_seeds, replace=False).astype(idx)
+    ip, ix, uniq, local = ops.sample_block(dev(indptr), dev(indices), dev(seeds), num_pick, rng_seed=11, rng_offset=3)
+    want_ip, want_ix = oracle.sample_neighbors(indptr, indices, seeds, num_pick, 11, 3)
+    want_uniq, (_, want_local) = oracle.tensor_relabel([seeds, want_ix])
+    nnz = int(want_ip[-1])
+    assert ix.numel() == n_seeds * num_pick and local.numel() == n_seeds * num_pick
+    assert np.array_equal(host(ip), want_ip)
+    assert np.array_equal(host(ix)[:nnz], want_ix) and np.all(host(ix)[nnz:] == seeds[0])
+    assert np.array_equal(host(uniq), want_uniq)
+    assert np.array_equal(host(local)[:nnz], want_local) and np.all(host(local)[nnz:] == 0)
+    # and the separate entry points agree with it
+    ip2, ix2 = ops.csr_sampling(dev(indptr), dev(indices), dev(seeds), num_pick, False, rng_seed=11, rng_offset=3)
+    uniq2, (_, local2) = ops.tensor_relabel([dev(seeds), ix2])
+    assert torch.equal(ip, ip2) and torch.equal(ix[:nnz], ix2) and torch.equal(uniq, uniq2) and torch.equal(local[:nnz], local2)
+
+
+def test_sample_block_of_isolated_seeds(capi):
+    """Seeds without neighbours: an empty block whose only nodes are the seeds."""
+    from f2cgt_b200 import ops
+    indptr = torch.zeros(11, dtype=torch.int64, device="cuda")
+    indices = torch.zeros(0, dtype=torch.int64, device="cuda")
+    seeds = torch.tensor([4, 2, 9], device="cuda")
+    ip, ix, uniq, local = ops.sample_block(indptr, indices, seeds, 5)
+    assert ip.tolist() == [0, 0, 0, 0] and uniq.tolist() == [4, 2, 9]
+    assert ix.tolist() == [4] * 15 and local.tolist() == [0] * 15
