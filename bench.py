@@ -469,9 +469,10 @@ def run_ours(args):
                 rec = train_graphsage.train("small", table, rank, world, local_rank, epochs=2, min_timed_steps=100)
                 epoch.append({"table": table, "ms_per_step": rec["ms_per_step"], "s_per_epoch": rec["value"], "steps": rec["steps_per_epoch_per_gpu"],
                               "timed_steps": rec["timed_steps_per_gpu"], "breakdown_ms": rec["breakdown_ms"],
+                              "precision": rec["precision"], "blocks_built_ahead": rec["blocks_built_ahead"],
                               "graph": "2,449,029 nodes, mean degree 50 (the 111 M-node graph of the two-level configuration is not built here)",
                               "codecs": "two-level: hot 5 % SQ 8 bits + VQ 4 x 32 (ratio 128), D = 128, 172 classes, 122,880 training ids "
-                                        "split over the ranks, batch 1024, fan-out 12,12,12, dropout 0.5, bf16 autocast"})
+                                        "split over the ranks, batch 1024, fan-out 12,12,12, dropout 0.5"})
             except Exception as e:  # noqa: BLE001
                 epoch.append({"table": table, "error": repr(e)[:300]})
         flush = torch.zeros(64 << 20, dtype=torch.float32, device=device)

@@ -180,13 +180,24 @@ def _csc(indptr, indices):
     return indptr.numel() - 1
 
 
-def spmm_csr(feat, indptr, indices, reduce="mean"):
+def _block_out(n_dst, width, dtype, device, out_rows):
+    """Output of a block kernel: ``[n_dst, width]``, or - with ``out_rows > n_dst`` - ``[out_rows, width]`` whose rows behind
+    ``n_dst`` are zero: a caller that pads row counts to a few recurring sizes (for the matrix products that follow) gets
+    the padded tensor without a copy."""
+    if out_rows is None or out_rows <= n_dst:
+        return torch.empty((n_dst, width), dtype=dtype, device=device)
+    out = torch.empty((int(out_rows), width), dtype=dtype, device=device)
+    out[n_dst:].zero_()
+    return out
+
+
+def spmm_csr(feat, indptr, indices, reduce="mean", out_rows=None):
     """src/fusion_spmm.cu:45-70.  Mean of neighbour rows; output has the dtype of ``feat``."""
     _chk(feat, "feat", (torch.float32, torch.float16, torch.float64))
     n_dst = _csc(indptr, indices)
     if feat.dim() != 2:
         raise RuntimeError("feat must be 2-D")
-    out = torch.empty((n_dst, feat.shape[1]), dtype=feat.dtype, device=feat.device)
+    out = _block_out(n_dst, feat.shape[1], feat.dtype, feat.device, out_rows)
     with _on(feat):
         check(lib.f2c_spmm_csr(_ptr(feat), _DT[feat.dtype], _ptr(indptr), _ptr(indices), _DT[indptr.dtype], _ptr(out), n_dst,
                                feat.shape[1], _REDUCE[reduce], _stream(feat)))
@@ -208,7 +219,7 @@ def spmm_csr_backward(grad_out, indptr, indices, n_src, reduce="mean"):
 
 
 def sq_decompress_spmm_csr(compress_feat, codebooks, indptr, indices, target_bit, column_slice, feat_dim, reduce="mean",
-                           dropout=None, kernel="auto", check=False):
+                           dropout=None, kernel="auto", check=False, out_rows=None):
     """src/fusion_spmm.cu:240-272.  Fused SQ decode + mean aggregation -> float32 [n_dst, feat_dim]."""
     _chk(compress_feat, "compress_feat", (torch.uint8, torch.int8, torch.int16))
     _chk(codebooks, "codebooks", (torch.float32,))
@@ -216,7 +227,7 @@ def sq_decompress_spmm_csr(compress_feat, codebooks, indptr, indices, target_bit
     if compress_feat.dim() != 2:
         raise RuntimeError("compress_feat must be 2-D")
     _check_block(check, indptr, indices, compress_feat.shape[0])
-    out = torch.empty((n_dst, feat_dim), dtype=torch.float32, device=compress_feat.device)
+    out = _block_out(n_dst, feat_dim, torch.float32, compress_feat.device, out_rows)
     ep = _epilogue(dropout, kernel)
     with _on(compress_feat):
         _lib.check(lib.f2c_sq_spmm_csr(_ptr(compress_feat), _DT[compress_feat.dtype], _ptr(codebooks), codebooks.shape[0],
@@ -227,13 +238,13 @@ def sq_decompress_spmm_csr(compress_feat, codebooks, indptr, indices, target_bit
 
 
 def sq_decompress_spmm_csr_peer(peer_table, codebooks, indptr, indices, target_bit, column_slice, feat_dim, reduce="mean",
-                                dropout=None, kernel="auto"):
+                                dropout=None, kernel="auto", out_rows=None):
     """``sq_decompress_spmm_csr`` over a row-sharded table (``f2cgt_b200.shard.PeerTable``): indices are global row ids,
     remote rows are read by the kernel itself over NVLink."""
     import ctypes
     _chk(codebooks, "codebooks", (torch.float32,))
     n_dst = _csc(indptr, indices)
-    out = torch.empty((n_dst, feat_dim), dtype=torch.float32, device=indptr.device)
+    out = _block_out(n_dst, feat_dim, torch.float32, indptr.device, out_rows)
     if len(peer_table.pointers) != peer_table.world:
         raise RuntimeError("the peer table is closed")
     ptrs = (ctypes.c_void_p * peer_table.world)(*peer_table.pointers)
@@ -247,7 +258,7 @@ def sq_decompress_spmm_csr_peer(peer_table, codebooks, indptr, indices, target_b
 
 
 def vq_decompress_spmm_csr(compress_feat, codebooks, indptr, indices, feat_dim, reduce="mean", dropout=None, kernel="auto",
-                           check=False):
+                           check=False, out_rows=None):
     """src/fusion_spmm.cu:107-141.  Fused VQ decode + mean aggregation -> float32 [n_dst, feat_dim]."""
     _chk(compress_feat, "compress_feat", (torch.uint8, torch.int8, torch.int16))
     _chk(codebooks, "codebooks", (torch.float32,))
@@ -256,7 +267,7 @@ def vq_decompress_spmm_csr(compress_feat, codebooks, indptr, indices, feat_dim, 
         raise RuntimeError("compress_feat must be [rows, n_codebooks] and codebooks [n_codebooks, length, column_slice]")
     n_cb, K, cs = codebooks.shape
     _check_block(check, indptr, indices, compress_feat.shape[0])
-    out = torch.empty((n_dst, feat_dim), dtype=torch.float32, device=compress_feat.device)
+    out = _block_out(n_dst, feat_dim, torch.float32, compress_feat.device, out_rows)
     ep = _epilogue(dropout, kernel)
     with _on(compress_feat):
         _lib.check(lib.f2c_vq_spmm_csr(_ptr(compress_feat), _DT[compress_feat.dtype], _ptr(codebooks), _ptr(indptr), _ptr(indices),
@@ -283,7 +294,7 @@ def fusion_decompress(sq_data, sq_codebooks, target_bits, column_slice, vq_data,
 
 
 def two_level_decompress_spmm_csr(sq_data, sq_codebooks, target_bits, column_slice, vq_data, vq_codebooks, slot, indptr,
-                                  indices, feat_dim, reduce="mean", dropout=None, kernel="auto", check=False):
+                                  indices, feat_dim, reduce="mean", dropout=None, kernel="auto", check=False, out_rows=None):
     """Two-level aggregation in one launch.  Source row s is decoded from row ``slot[s]`` of the SQ table
     when ``slot[s] >= 0`` (int32), from row s of the VQ table otherwise; then the reference mean.
     ``slot=None``: hot-first numbering - the hot nodes are ids ``0 .. len(sq_data) - 1`` and node s reads SQ row s."""
@@ -296,7 +307,7 @@ def two_level_decompress_spmm_csr(sq_data, sq_codebooks, target_bits, column_sli
     n_dst = _csc(indptr, indices)
     n_cb, K, cs = vq_codebooks.shape
     _check_block(check, indptr, indices, vq_data.shape[0])
-    out = torch.empty((n_dst, feat_dim), dtype=torch.float32, device=vq_data.device)
+    out = _block_out(n_dst, feat_dim, torch.float32, vq_data.device, out_rows)
     ep = _epilogue(dropout, kernel)
     with _on(vq_data):
         _lib.check(lib.f2c_hybrid_spmm_csr(_ptr(sq_data), _DT[sq_data.dtype], _ptr(sq_codebooks), sq_codebooks.shape[0],
@@ -307,7 +318,7 @@ def two_level_decompress_spmm_csr(sq_data, sq_codebooks, target_bits, column_sli
 
 
 def two_level_decompress_spmm_csr_peer(sq_peers, sq_codebooks, target_bits, column_slice, vq_peers, vq_codebooks, slot_peers, indptr,
-                                       indices, feat_dim, reduce="mean", dropout=None):
+                                       indices, feat_dim, reduce="mean", dropout=None, out_rows=None):
     """``two_level_decompress_spmm_csr`` (or, with ``sq_peers=None``, ``vq_decompress_spmm_csr``) over tables row-sharded across
     the GPUs of the box (``f2cgt_b200.shard.PeerTable`` objects: VQ codes and slots sharded by node id, hot SQ rows by slot):
     indices are global node ids, the kernel reads remote rows itself over NVLink.  ``slot_peers=None``: hot-first numbering."""
@@ -326,7 +337,7 @@ def two_level_decompress_spmm_csr_peer(sq_peers, sq_codebooks, target_bits, colu
     two = sq_peers is not None
     if two:
         _chk(sq_codebooks, "sq_codebooks", (torch.float32,))
-    out = torch.empty((n_dst, feat_dim), dtype=torch.float32, device=indptr.device)
+    out = _block_out(n_dst, feat_dim, torch.float32, indptr.device, out_rows)
     ep = _epilogue(dropout)
     with _on(indptr):
         check(lib.f2c_hybrid_spmm_csr_peer(ptrs(sq_peers), ptrs(vq_peers), ptrs(slot_peers), world, vq_peers.rpr,
@@ -523,12 +534,15 @@ def tensor_relabel(tensors):
     return unique, out
 
 
-def sample_block(indptr, indices, seeds, num_pick, rng_seed=0, rng_offset=0):
-    """One hop of a block: ``csr_sampling`` followed by ``tensor_relabel([seeds, sub_indices])`` (the pair at
-    examples/dataloader.py:174-177) as ONE library call and one host read.  Returns ``(sub_indptr, sub_indices, unique,
-    local_indices)`` with the numbering of the separate operators; ``sub_indices`` / ``local_indices`` have
-    ``len(seeds) * num_pick`` entries of which the first ``sub_indptr[-1]`` are the block's edges (the rest repeat
-    ``seeds[0]`` and its new number, and no kernel reads them)."""
+class _PendingBlock:
+    __slots__ = ("sub_indptr", "buf", "n", "host", "event")
+
+
+def sample_block_launch(indptr, indices, seeds, num_pick, rng_seed=0, rng_offset=0):
+    """First half of ``sample_block``: queues the hop on the current stream, starts the copy of its three counters to pinned
+    host memory and returns without waiting.  ``sample_block_finish`` of the returned object gives the result; its
+    ``event`` tells (``query()``) whether that would block.  A loader uses the pair to build the next minibatch on a
+    side stream while the current one trains."""
     _chk(indptr, "indptr", (torch.int32, torch.int64))
     _chk(indices, "indices", (indptr.dtype,))
     _chk(seeds, "seeds", (indptr.dtype,))
@@ -539,17 +553,39 @@ def sample_block(indptr, indices, seeds, num_pick, rng_seed=0, rng_offset=0):
     ws_bytes = lib.f2c_sample_block_workspace(n, int(num_pick), _DT[dt])
     if ws_bytes <= 0:
         raise RuntimeError("sample_block: num_pick must be in [1, 64]")
+    pend = _PendingBlock()
     with _on(indptr):
         ws = torch.empty((ws_bytes,), dtype=torch.uint8, device=dev)
-        sub_indptr = torch.empty((n + 1,), dtype=dt, device=dev)
-        buf = torch.empty((3, n_keys), dtype=dt, device=dev)  # keys, unique, relabelled
+        pend.sub_indptr = torch.empty((n + 1,), dtype=dt, device=dev)
+        pend.buf = buf = torch.empty((3, n_keys), dtype=dt, device=dev)  # keys, unique, relabelled
         header = torch.empty((4,), dtype=torch.int64, device=dev)
         check(lib.f2c_sample_block(_ptr(indptr), _ptr(indices), _ptr(seeds), _DT[dt], n, int(num_pick),
-                                   int(rng_seed) & 0xFFFFFFFFFFFFFFFF, int(rng_offset), _ptr(sub_indptr), _ptr(buf[0]), _ptr(buf[1]),
+                                   int(rng_seed) & 0xFFFFFFFFFFFFFFFF, int(rng_offset), _ptr(pend.sub_indptr), _ptr(buf[0]), _ptr(buf[1]),
                                    _ptr(buf[2]), _ptr(header), _ptr(ws), ws_bytes, _stream(indptr)))
-        _nnz, n_unique, err, _ = header.tolist()
+        pend.host = torch.empty((4,), dtype=torch.int64, pin_memory=True)
+        pend.host.copy_(header, non_blocking=True)
+        pend.event = torch.cuda.Event()
+        pend.event.record(torch.cuda.current_stream(dev))
+    pend.n = n
+    return pend
+
+
+def sample_block_finish(pend):
+    """Second half of ``sample_block``: waits for the hop (host side only) and returns its tensors."""
+    pend.event.synchronize()
+    _nnz, n_unique, err, _ = pend.host.tolist()
     if err == 2:
         raise RuntimeError("sample_block: negative id in the graph or the seeds")
     if err != 0:
         raise RuntimeError("sample_block: hash table overflow")
-    return sub_indptr, buf[0, n:], buf[1, :n_unique], buf[2, n:]
+    n, buf = pend.n, pend.buf
+    return pend.sub_indptr, buf[0, n:], buf[1, :n_unique], buf[2, n:]
+
+
+def sample_block(indptr, indices, seeds, num_pick, rng_seed=0, rng_offset=0):
+    """One hop of a block: ``csr_sampling`` followed by ``tensor_relabel([seeds, sub_indices])`` (the pair at
+    examples/dataloader.py:174-177) as ONE library call and one host read.  Returns ``(sub_indptr, sub_indices, unique,
+    local_indices)`` with the numbering of the separate operators; ``sub_indices`` / ``local_indices`` have
+    ``len(seeds) * num_pick`` entries of which the first ``sub_indptr[-1]`` are the block's edges (the rest repeat
+    ``seeds[0]`` and its new number, and no kernel reads them)."""
+    return sample_block_finish(sample_block_launch(indptr, indices, seeds, num_pick, rng_seed, rng_offset))

@@ -38,20 +38,21 @@ class CompressionManager:
         if self.is_two_level and (self.methods != ["sq", "vq"] or (slot is None and not hot_first)):
             raise ValueError("two-level compression is hot SQ rows over a VQ table, with a slot array or hot-first numbering")
 
-    def aggregate(self, indptr, indices_global, dropout=None):
+    def aggregate(self, indptr, indices_global, dropout=None, out_rows=None):
+        """``out_rows``: allocate that many output rows (zero behind the block's own), see ``ops._block_out``."""
         if self.is_two_level:
             cs, bits = self.configs[0]
             return ops.two_level_decompress_spmm_csr(self.tables[0], self.codebooks[0], bits, cs, self.tables[1], self.codebooks[1],
-                                                     self.slot, indptr, indices_global, self.feat_dim, dropout=dropout)
+                                                     self.slot, indptr, indices_global, self.feat_dim, dropout=dropout, out_rows=out_rows)
         if self.methods[0] == "vq":
-            return ops.vq_decompress_spmm_csr(self.tables[0], self.codebooks[0], indptr, indices_global, self.feat_dim, dropout=dropout)
+            return ops.vq_decompress_spmm_csr(self.tables[0], self.codebooks[0], indptr, indices_global, self.feat_dim, dropout=dropout,
+                                              out_rows=out_rows)
         cs, bits = self.configs[0]
         return ops.sq_decompress_spmm_csr(self.tables[0], self.codebooks[0], indptr, indices_global, bits, cs, self.feat_dim,
-                                          dropout=dropout)
+                                          dropout=dropout, out_rows=out_rows)
 
-    def decode_rows(self, nodes):
-        ident = torch.arange(nodes.numel() + 1, dtype=nodes.dtype, device=nodes.device)
-        return self.aggregate(ident, nodes)
+    def decode_rows(self, nodes, out_rows=None):
+        return self.aggregate(_identity_offsets(nodes), nodes, out_rows=out_rows)
 
     def for_block(self, block):
         """(manager, neighbour ids, destination ids) with which the first layer reads this block: the resident tables
@@ -117,14 +118,14 @@ class PeerCompressionManager:
             if local_slot is not None:  # None: hot-first numbering
                 self.slot = shard.PeerTable(local_slot.reshape(-1, 1).contiguous(), table_rows[-1], group)
 
-    def aggregate(self, indptr, indices_global, dropout=None):
+    def aggregate(self, indptr, indices_global, dropout=None, out_rows=None):
         cs, bits = self.configs[0] if self.is_two_level else (1, 8)
         return ops.two_level_decompress_spmm_csr_peer(self.hot, self.codebooks[0] if self.is_two_level else None, bits, cs, self.level2,
-                                                      self.codebooks[-1], self.slot, indptr, indices_global, self.feat_dim, dropout=dropout)
+                                                      self.codebooks[-1], self.slot, indptr, indices_global, self.feat_dim, dropout=dropout,
+                                                      out_rows=out_rows)
 
-    def decode_rows(self, nodes):
-        ident = torch.arange(nodes.numel() + 1, dtype=nodes.dtype, device=nodes.device)
-        return self.aggregate(ident, nodes)
+    def decode_rows(self, nodes, out_rows=None):
+        return self.aggregate(_identity_offsets(nodes), nodes, out_rows=out_rows)
 
     def for_block(self, block):
         return self, block["indices_global"], block["dst_nodes"]
@@ -135,19 +136,87 @@ class PeerCompressionManager:
                 t.close()
 
 
+_CACHE = {}
+
+
+def _identity_offsets(nodes):
+    """[0, 1, ..., len(nodes)] in the dtype and on the device of ``nodes``: the CSC of "every row is its own only
+    neighbour", under which a fused aggregation is a row decode.  One growing tensor per (device, dtype)."""
+    key = ("ident", nodes.device, nodes.dtype)
+    have = _CACHE.get(key)
+    if have is None or have.numel() < nodes.numel() + 1:
+        have = _CACHE[key] = torch.arange(max(2 * nodes.numel(), 4096) + 1, dtype=nodes.dtype, device=nodes.device)
+    return have[:nodes.numel() + 1]
+
+
+def _ones_row(m, like):
+    key = ("ones", like.device, like.dtype)
+    have = _CACHE.get(key)
+    if have is None or have.shape[1] < m:
+        have = _CACHE[key] = torch.ones((1, max(2 * m, 4096)), dtype=like.dtype, device=like.device)
+    return have[:, :m]
+
+
 def _bucket(n):
     """Row counts of sampled blocks change every step; the matrix products behind the Linear layers pick (and cache)
-    their algorithms per shape, so inputs are zero-padded to a few recurring row counts."""
+    their algorithms per shape, and the caching allocator keeps blocks per size, so the layers work on row counts rounded
+    up to a few recurring values.  The extra rows are carried through the network instead of being cut off and padded
+    again at every product: they never feed a real row (aggregation reads by index, below the block's row count), their
+    gradients are zero, and only the final output is sliced."""
     step = 4096 if n > 16384 else 512 if n > 2048 else 128
     return (n + step - 1) // step * step
 
 
-def _linear_rows(fc, x):
-    n = x.shape[0]
-    m = _bucket(n)
-    if m != n:
-        x = torch.nn.functional.pad(x, (0, 0, 0, m - n))
-    return fc(x)[:n]
+class _SageProduct(torch.autograd.Function):
+    """y = x_self @ w_self^T + x_neigh @ w_neigh^T + bias for inputs that need no gradient (the decoded first layer)."""
+
+    @staticmethod
+    def forward(ctx, x_self, x_neigh, w_self, w_neigh, bias):
+        ctx.save_for_backward(x_self, x_neigh)
+        ctx.has_bias = bias is not None
+        y = torch.addmm(bias, x_self, w_self.t()) if bias is not None else torch.mm(x_self, w_self.t())
+        return y.addmm_(x_neigh, w_neigh.t())
+
+    @staticmethod
+    def backward(ctx, dy):
+        x_self, x_neigh = ctx.saved_tensors
+        dy = dy.contiguous()
+        dyt = dy.t()
+        db = torch.mm(_ones_row(dy.shape[0], dy), dy).reshape(-1) if ctx.has_bias else None
+        return None, None, torch.mm(dyt, x_self), torch.mm(dyt, x_neigh), db
+
+
+class _SageLayer(torch.autograd.Function):
+    """A hidden mean-SAGE layer in one autograd node: y = h[:m] @ w_self^T + mean_neigh(h) @ w_neigh^T + bias over m >= n_dst
+    rows (rows behind n_dst: see ``_bucket``).  The backward pass is written out - five products, one scatter kernel - so a
+    step queues a third of the kernels autograd would for the same layer built from Linear, slice and pad nodes."""
+
+    @staticmethod
+    def forward(ctx, h, indptr, indices, n_dst, m, w_self, w_neigh, bias):
+        neigh = ops.spmm_csr(h, indptr, indices, out_rows=m)
+        h_self = h[:m]
+        y = torch.addmm(bias, h_self, w_self.t()) if bias is not None else torch.mm(h_self, w_self.t())
+        y.addmm_(neigh, w_neigh.t())
+        ctx.save_for_backward(h, neigh, indptr, indices, w_self, w_neigh)
+        ctx.n_dst, ctx.m, ctx.has_bias = n_dst, m, bias is not None
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        h, neigh, indptr, indices, w_self, w_neigh = ctx.saved_tensors
+        n_dst, m = ctx.n_dst, ctx.m
+        dy = dy.contiguous()
+        dyt = dy.t()
+        dw_self = torch.mm(dyt, h[:m])
+        dw_neigh = torch.mm(dyt, neigh)
+        db = torch.mm(_ones_row(m, dy), dy).reshape(-1) if ctx.has_bias else None
+        dh = None
+        if ctx.needs_input_grad[0]:
+            d_neigh = torch.mm(dy, w_neigh)
+            # one scatter kernel (vector reductions into the source rows) instead of building the transposed block
+            dh = ops.spmm_csr_backward(d_neigh[:n_dst], indptr, indices, h.shape[0])
+            dh[:m].addmm_(dy, w_self)
+        return dh, None, None, None, None, dw_self, dw_neigh, db
 
 
 class _MeanAggregate(torch.autograd.Function):
@@ -162,7 +231,6 @@ class _MeanAggregate(torch.autograd.Function):
     @staticmethod
     def backward(ctx, grad_out):
         indptr, indices = ctx.saved_tensors
-        # one scatter kernel (vector reductions into the source rows) instead of building the transposed block
         return ops.spmm_csr_backward(grad_out.float().contiguous(), indptr, indices, ctx.n_src), None, None, None
 
 
@@ -176,13 +244,18 @@ class MySAGEConv(nn.Module):
         nn.init.xavier_uniform_(self.fc_self.weight, gain=gain)
         nn.init.xavier_uniform_(self.fc_neigh.weight, gain=gain)
 
-    def forward(self, block, _unused=None):
+    def forward_padded(self, block, _unused=None):
+        """[_bucket(n_dst), out]: the layer's output with the extra rows of ``_bucket`` left in place."""
         # (manager, neighbour ids, destination ids): fetched by the caller beforehand (so that a sharded table's row
         # exchange can be timed and overlapped on its own) or here
         sm, neighbours, dst = block.get("first_layer_input") or self.sm.for_block(block)
-        h_neigh = sm.aggregate(block["indptr"], neighbours)  # raw codes in, no autograd through it
-        h_self = sm.decode_rows(dst)
-        return _linear_rows(self.fc_self, h_self) + _linear_rows(self.fc_neigh, h_neigh)
+        m = _bucket(dst.numel())
+        h_neigh = sm.aggregate(block["indptr"], neighbours, out_rows=m)  # raw codes in, no autograd through it
+        h_self = sm.decode_rows(dst, out_rows=m)
+        return _SageProduct.apply(h_self, h_neigh, self.fc_self.weight, self.fc_neigh.weight, self.fc_self.bias)
+
+    def forward(self, block, _unused=None):
+        return self.forward_padded(block)[:block["dst_nodes"].numel()]
 
 
 class SAGEConv(nn.Module):
@@ -194,11 +267,17 @@ class SAGEConv(nn.Module):
         nn.init.xavier_uniform_(self.fc_self.weight, gain=gain)
         nn.init.xavier_uniform_(self.fc_neigh.weight, gain=gain)
 
-    def forward(self, block, h):
+    def forward_padded(self, block, h):
+        """``h``: [>= n_src, in] float32 (rows behind the block's source nodes are ignored); returns [m, out] with
+        m = min(_bucket(n_dst), rows of h)."""
         n_dst = block["dst_nodes"].numel()
-        h32 = h.float().contiguous()
-        h_neigh = _MeanAggregate.apply(h32, block["indptr"], block["indices_local"], h.shape[0])
-        return _linear_rows(self.fc_self, h[:n_dst]) + _linear_rows(self.fc_neigh, h_neigh)
+        h = h.float().contiguous()
+        m = min(_bucket(n_dst), h.shape[0])
+        return _SageLayer.apply(h, block["indptr"], block["indices_local"], n_dst, m, self.fc_self.weight, self.fc_neigh.weight,
+                                self.fc_self.bias)
+
+    def forward(self, block, h):
+        return self.forward_padded(block, h)[:block["dst_nodes"].numel()]
 
 
 class SAGE(nn.Module):
@@ -214,22 +293,32 @@ class SAGE(nn.Module):
     def forward(self, blocks, x=None):
         h = x
         for i, (layer, block) in enumerate(zip(self.layers, blocks)):
-            h = layer(block, h)
+            h = layer.forward_padded(block, h)
             if i != len(self.layers) - 1:
                 h = self.dropout(torch.relu(h))
-        return h
+        n_out = blocks[-1]["dst_nodes"].numel()
+        return h if h.shape[0] == n_out else h[:n_out]
 
 
 class GPUSamplingDataloader:
-    """Seeds are split contiguously over the ranks (examples/dataloader.py:102-108), shuffled per epoch."""
+    """Seeds are split contiguously over the ranks (examples/dataloader.py:102-108), shuffled per epoch.
 
-    def __init__(self, indptr, indices, seeds, batchsize, num_picks, rank=0, world=1, shuffle=True, rng_seed=0):
+    ``ahead=True`` (default) builds every minibatch one step early on a CUDA stream of its own.  A block is a chain of
+    small dependent kernels with one host read per hop; on the training stream that chain would sit on the critical path
+    of every step although it needs nothing from the model.  Here ``__next__`` hands out the minibatch built during the
+    previous step and queues the first hop of the next; each later hop is queued by ``poke()`` - which the training loop
+    calls between its phases and which never blocks - or, at the latest, by the next ``__next__``.  The minibatches are
+    the same either way: sampling draws are keyed by epoch, step and hop."""
+
+    def __init__(self, indptr, indices, seeds, batchsize, num_picks, rank=0, world=1, shuffle=True, rng_seed=0, ahead=True):
         self.indptr, self.indices = indptr, indices
         self.batchsize, self.num_picks = int(batchsize), list(num_picks)
         self.shuffle, self.rng_seed, self.epoch = shuffle, rng_seed, 0
         per = (seeds.numel() + world - 1) // world
         self.seeds = seeds[rank * per:(rank + 1) * per]
         self.rank = rank
+        self.side = torch.cuda.Stream(device=indptr.device) if ahead else None
+        self._gen = self._result = self._wait = None
 
     def __len__(self):
         return (self.seeds.numel() + self.batchsize - 1) // self.batchsize
@@ -243,22 +332,71 @@ class GPUSamplingDataloader:
         else:
             self.order = self.seeds
         self.epoch += 1
+        self._gen = self._result = self._wait = None
+        if self.side is not None:
+            self.side.wait_stream(torch.cuda.current_stream(self.indptr.device))  # the shuffled order is read over there
+            self._start()
         return self
 
-    def __next__(self):
-        if self.curr >= len(self):
-            raise StopIteration
-        seeds = self.order[self.curr * self.batchsize:(self.curr + 1) * self.batchsize]
-        step = self.curr
-        self.curr += 1
-        output_nodes = seeds
-        blocks = []
+    def _hops(self, seeds, step):
+        """Generator over one minibatch: yields the pending hop after queueing it, returns the minibatch."""
+        output_nodes, blocks = seeds, []
         for hop, num_pick in enumerate(reversed(self.num_picks)):
             # one library call and one host read (the number of distinct nodes) per hop; the index tensors carry a tail
             # behind indptr[-1] that no kernel reads
-            sub_indptr, sub_indices, unique, local = ops.sample_block(
-                self.indptr, self.indices, seeds, num_pick,
-                rng_seed=(self.rng_seed * 7919 + self.epoch) * 65536 + self.rank, rng_offset=step * 8 + hop)
+            pending = ops.sample_block_launch(self.indptr, self.indices, seeds, num_pick,
+                                              rng_seed=(self.rng_seed * 7919 + self.epoch) * 65536 + self.rank, rng_offset=step * 8 + hop)
+            yield pending
+            sub_indptr, sub_indices, unique, local = ops.sample_block_finish(pending)
             blocks.insert(0, dict(dst_nodes=seeds, src_nodes=unique, indptr=sub_indptr, indices_global=sub_indices, indices_local=local))
             seeds = unique
         return seeds, output_nodes, blocks
+
+    def _start(self):
+        if self.curr >= len(self):
+            self._gen = None
+            return
+        seeds = self.order[self.curr * self.batchsize:(self.curr + 1) * self.batchsize]
+        self._gen = self._hops(seeds, self.curr)
+        self.curr += 1
+        self._advance()
+
+    def _advance(self):
+        """Finish the pending hop (blocks until the GPU is done with it) and queue the next one."""
+        with torch.cuda.stream(self.side):
+            try:
+                self._wait = next(self._gen)
+            except StopIteration as done:
+                self._result, self._gen, self._wait = done.value, None, None
+
+    def poke(self):
+        """Move the minibatch under construction one hop forward if that needs no waiting; call it wherever the host has
+        just queued a stretch of GPU work."""
+        if self._gen is not None and self._wait is not None and self._wait.event.query():
+            self._advance()
+
+    def __next__(self):
+        if self.side is None:
+            if self.curr >= len(self):
+                raise StopIteration
+            gen = self._hops(self.order[self.curr * self.batchsize:(self.curr + 1) * self.batchsize], self.curr)
+            self.curr += 1
+            try:
+                while True:
+                    next(gen)
+            except StopIteration as done:
+                return done.value
+        if self._gen is None and self._result is None:
+            raise StopIteration
+        while self._result is None:
+            self._advance()
+        batch, self._result = self._result, None
+        cur = torch.cuda.current_stream(self.indptr.device)
+        cur.wait_stream(self.side)
+        input_nodes, output_nodes, blocks = batch
+        for b in blocks:  # allocated on the side stream, used on this one from now on
+            for v in b.values():
+                if torch.is_tensor(v):
+                    v.record_stream(cur)
+        self._start()
+        return batch

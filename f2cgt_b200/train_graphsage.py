@@ -76,7 +76,7 @@ def build_data(cfg, device, index_dtype, table="replicated"):
 
 
 def train(preset="small", table="replicated", rank=0, world=1, local_rank=0, epochs=3, min_timed_steps=0, batch_size=1024, lr=0.003,
-          dropout=0.5, index_dtype="int64", max_steps=0, autocast=True):
+          dropout=0.5, index_dtype="int64", max_steps=0, precision="tf32", ahead=True):
     """Train on the preset's synthetic data inside an already initialised process (and, for world > 1 or a sharded table,
     process group); returns the record rank 0 reports (every rank gets it).  The first epoch is a discarded warm-up; when
     ``min_timed_steps`` is set, enough further epochs are run to time at least that many steps per rank.  Per-phase device
@@ -105,7 +105,14 @@ def train(preset="small", table="replicated", rank=0, world=1, local_rank=0, epo
             off += p.numel()
     optimizer = torch.optim.Adam(net.parameters(), lr=lr, fused=True)  # one kernel for all parameters (the model is tiny)
     scheduler = torch.optim.lr_scheduler.ExponentialLR(optimizer, gamma=0.978)
-    loader = sage.GPUSamplingDataloader(indptr, indices, train_ids, batch_size, cfg["fan_out"], rank, world, shuffle=True)
+    loader = sage.GPUSamplingDataloader(indptr, indices, train_ids, batch_size, cfg["fan_out"], rank, world, shuffle=True, ahead=ahead)
+    # The reference trains in fp32 (examples/train_graphsage_nodeclass.py has no autocast).  "tf32": fp32 storage, matrix
+    # products on the tensor cores with tf32 inputs and fp32 accumulation - no cast kernels at all, which matters because
+    # the step is bound by the host's launch rate, not by the GPU.  "fp32": plain.
+    if precision not in ("tf32", "fp32"):
+        raise ValueError("precision must be tf32 or fp32")
+    tf32_before = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = precision == "tf32"
     steps = torch.tensor([len(loader)], device=device)
     if world > 1:
         dist.all_reduce(steps, op=dist.ReduceOp.MIN)  # every rank takes the same number of steps (gradient all-reduce)
@@ -119,6 +126,7 @@ def train(preset="small", table="replicated", rank=0, world=1, local_rank=0, epo
     epoch_s, losses, edges = [], [], 0
     phase_ms = {k: 0.0 for k in phases}
     timed_steps = 0
+    marks = [[torch.cuda.Event(enable_timing=True) for _ in range(6)] for _ in range(steps)]
     for epoch in range(epochs):
         net.train()
         torch.cuda.synchronize()
@@ -126,19 +134,19 @@ def train(preset="small", table="replicated", rank=0, world=1, local_rank=0, epo
             dist.barrier()
         t0 = time.perf_counter()
         it = iter(loader)
-        marks = []
+        first_layer_edges = []
         for step in range(steps):
-            ev = [torch.cuda.Event(enable_timing=True) for _ in range(6)]
+            ev = marks[step]  # reused every epoch: creating six events costs the host as much as queueing four kernels
             ev[0].record()
             input_nodes, output_nodes, blocks = next(it)
             y = labels[output_nodes]
             ev[1].record()
             blocks[0]["first_layer_input"] = cm.for_block(blocks[0])  # sharded table: the row exchange of this minibatch
             ev[2].record()
-            with torch.autocast("cuda", dtype=torch.bfloat16, enabled=autocast):
-                pred = net(blocks)
-            loss = F.cross_entropy(pred.float(), y)
+            pred = net(blocks)
+            loss = F.cross_entropy(pred, y)
             ev[3].record()
+            loader.poke()  # next minibatch: one hop further on its own stream, if that needs no waiting
             if flat_grad is None:
                 optimizer.zero_grad(set_to_none=True)
                 loss.backward()
@@ -148,16 +156,19 @@ def train(preset="small", table="replicated", rank=0, world=1, local_rank=0, epo
                 dist.all_reduce(flat_grad)
                 flat_grad.mul_(1.0 / world)
             ev[4].record()
+            loader.poke()
             optimizer.step()
             ev[5].record()
-            marks.append(ev)
+            loader.poke()
             if epoch == epochs - 1:
-                edges = edges + blocks[0]["indptr"][-1]  # stays on the device: the index tensors are padded, indptr is exact
+                first_layer_edges.append(blocks[0]["indptr"][-1:])  # a view; summed after the epoch (index tensors are padded, indptr is exact)
         scheduler.step()
         torch.cuda.synchronize()
         if world > 1:
             dist.barrier()
         epoch_s.append(time.perf_counter() - t0)
+        if first_layer_edges:
+            edges = float(torch.cat(first_layer_edges).sum())
         losses.append(float(loss.detach()))
         if epoch > 0 or epochs == 1:
             timed_steps += steps
@@ -172,6 +183,7 @@ def train(preset="small", table="replicated", rank=0, world=1, local_rank=0, epo
         sm = stats.clone(); dist.all_reduce(sm, op=dist.ReduceOp.SUM)
         stats = torch.cat([mx[:1], sm[1:2], mx[2:]])
     stats = stats.tolist()
+    torch.backends.cuda.matmul.allow_tf32 = tf32_before
     if hasattr(cm, "close"):
         torch.cuda.synchronize()
         cm.close()
@@ -182,7 +194,7 @@ def train(preset="small", table="replicated", rank=0, world=1, local_rank=0, epo
         "breakdown_ms": {k: round(v, 4) for k, v in zip(phases, stats[2:])},
         "first_layer_edges_per_s": stats[1] / stats[0], "loss_last_step_per_epoch": [round(v, 4) for v in losses],
         "config": {k: (list(v) if isinstance(v, tuple) else v) for k, v in cfg.items()}, "index_dtype": index_dtype,
-        "autocast_bf16": autocast, "table": table, "data": "synthetic", "scaling": "strong (train ids split over ranks)",
+        "precision": precision, "blocks_built_ahead": bool(ahead), "table": table, "data": "synthetic", "scaling": "strong (train ids split over ranks)",
         "timing": "wall clock around barrier + synchronize delimited epochs, first epoch discarded, max over ranks; breakdown = CUDA "
                   "events on the current stream, mean per step, max over ranks"}
 
@@ -197,7 +209,9 @@ def main():
     ap.add_argument("--index-dtype", default="int64", choices=["int32", "int64"])
     ap.add_argument("--max-steps", type=int, default=0, help="cut every epoch after this many steps (0 = whole epoch)")
     ap.add_argument("--min-timed-steps", type=int, default=0, help="run enough epochs to time at least this many steps")
-    ap.add_argument("--no-autocast", action="store_true")
+    ap.add_argument("--precision", default="tf32", choices=["tf32", "fp32"],
+                    help="tf32: fp32 storage, tf32 tensor-core products (default); fp32: plain")
+    ap.add_argument("--no-ahead", action="store_true", help="build every minibatch inside its step instead of one step early on a side stream")
     ap.add_argument("--table", default="replicated", choices=["replicated", "sharded", "sharded_peer"],
                     help="sharded: every table row-sharded over the ranks, rows fetched per minibatch with an all-to-all exchange; "
                          "sharded_peer: the same shards mapped into every rank, the fused kernel reads remote rows over NVLink")
@@ -214,7 +228,7 @@ def main():
             os.environ.setdefault("MASTER_PORT", "29577")
         dist.init_process_group("nccl", device_id=device, rank=rank, world_size=world)
     rec = train(args.preset, args.table, rank, world, local_rank, args.epochs, args.min_timed_steps, args.batch_size, args.lr,
-                args.dropout, args.index_dtype, args.max_steps, not args.no_autocast)
+                args.dropout, args.index_dtype, args.max_steps, args.precision, not args.no_ahead)
     if rank == 0:
         print(json.dumps(rec), flush=True)
     if dist.is_initialized():

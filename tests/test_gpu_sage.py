@@ -96,3 +96,105 @@ def test_training_learns_a_feature_rule(capi):
             first = float(loss.detach()) if first is None else first
             last = float(loss.detach())
     assert last < 0.5 * first, (first, last)
+
+
+def _two_level_setup(dev="cuda"):
+    from f2cgt_b200 import ops, sage, synth
+    n, D = 30000, 128
+    indptr, indices = synth.power_law_graph(n, 15, 2.1, seed=1, device=dev)
+    g = torch.Generator(device=dev).manual_seed(2)
+    vq_codes = torch.randint(0, 256, (n, 4), generator=g, dtype=torch.uint8, device=dev)
+    vq_cbs = torch.randn(4, 256, 32, generator=g, device=dev)
+    n_hot = 1500
+    hot = torch.randperm(n, generator=g, device=dev)[:n_hot]
+    slot = torch.full((n,), -1, dtype=torch.int32, device=dev)
+    slot[hot] = torch.arange(n_hot, dtype=torch.int32, device=dev)
+    sq_codes = torch.randint(-128, 128, (n_hot, D), generator=g, dtype=torch.int8, device=dev)
+    sq_cb = synth.sq_codebook_from_sample(torch.randn(5000, D, generator=g, device=dev), D)
+    cm = sage.CompressionManager(D, ["sq", "vq"], [(D, 8), (32, 8)], [sq_cb, vq_cbs], [sq_codes, vq_codes], slot)
+    full = ops.vq_decompress(vq_codes, vq_cbs, D)
+    full[hot] = ops.sq_decompress(sq_codes, sq_cb, 8, D, D)
+    return n, D, indptr, indices, cm, full, g
+
+
+def test_sage_gradients_equal_autograd_of_the_plain_network(capi):
+    """The hand-written backward of the layers (rows padded to recurring counts and carried through the network) gives
+    the gradients autograd computes for the same network written with Linear layers on decoded features."""
+    from f2cgt_b200 import sage
+    n, D, indptr, indices, cm, full, g = _two_level_setup()
+    hidden, classes = 64, 10
+    torch.manual_seed(0)
+    model = sage.SAGE(D, hidden, classes, 3, 0.0, cm).cuda()
+    seeds = torch.randperm(n, generator=g, device="cuda")[:300]  # 300: not a multiple of the row bucket
+    loader = sage.GPUSamplingDataloader(indptr, indices, seeds, 300, (5, 4, 3), shuffle=False)
+    input_nodes, _, blocks = next(iter(loader))
+    y = torch.randint(0, classes, (300,), generator=g, device="cuda")
+    got = model(blocks)
+    assert got.shape == (300, classes)
+    torch.nn.functional.cross_entropy(got, y).backward()
+    mine = [p.grad.clone() for p in model.parameters()]
+    model.zero_grad(set_to_none=True)
+    h = full[input_nodes]
+    for i, (layer, b) in enumerate(zip(model.layers, blocks)):
+        n_dst = b["dst_nodes"].numel()
+        h = layer.fc_self(h[:n_dst]) + layer.fc_neigh(torch_mean_aggregate(h, b["indptr"], b["indices_local"]))
+        if i != 2:
+            h = torch.relu(h)
+    assert torch.allclose(got, h, rtol=1e-4, atol=1e-4)
+    torch.nn.functional.cross_entropy(h, y).backward()
+    for a, p in zip(mine, model.parameters()):
+        assert torch.allclose(a, p.grad, rtol=1e-3, atol=1e-5), float((a - p.grad).abs().max())
+
+
+def test_hidden_layer_on_unpadded_input(capi):
+    """SAGEConv called by hand with exactly n_src rows (fewer than the row bucket of its n_dst): output and gradients."""
+    from f2cgt_b200 import sage
+    g = torch.Generator(device="cuda").manual_seed(3)
+    n_src, n_dst, H = 150, 140, 32
+    deg = torch.randint(0, 6, (n_dst,), generator=g, device="cuda")
+    indptr = torch.cat([torch.zeros(1, dtype=torch.int64, device="cuda"), torch.cumsum(deg, 0)])
+    indices = torch.randint(0, n_src, (int(indptr[-1]),), generator=g, device="cuda")
+    block = dict(dst_nodes=torch.arange(n_dst, device="cuda"), indptr=indptr, indices_local=indices)
+    torch.manual_seed(1)
+    layer = sage.SAGEConv(H, 16).cuda()
+    h = torch.randn(n_src, H, generator=g, device="cuda", requires_grad=True)
+    w = torch.randn(n_dst, 16, generator=g, device="cuda")
+    out = layer(block, h)
+    assert out.shape == (n_dst, 16)
+    (out * w).sum().backward()
+    got = [h.grad.clone()] + [p.grad.clone() for p in layer.parameters()]
+    h.grad = None
+    layer.zero_grad(set_to_none=True)
+    ref = layer.fc_self(h[:n_dst]) + layer.fc_neigh(torch_mean_aggregate(h, indptr, indices))
+    (ref * w).sum().backward()
+    assert torch.allclose(out, ref, rtol=1e-5, atol=1e-5)
+    for a, b in zip(got, [h.grad] + [p.grad for p in layer.parameters()]):
+        assert torch.allclose(a, b, rtol=1e-4, atol=1e-5)
+
+
+def test_loader_builds_the_same_minibatches_ahead_or_in_step(capi):
+    """Minibatches built one step early on the side stream (with and without poke() calls in between) are those of the
+    in-step loader, tensor for tensor."""
+    from f2cgt_b200 import sage, synth
+    indptr, indices = synth.power_law_graph(20000, 12, 2.1, seed=7, device="cuda")
+    seeds = torch.arange(0, 5000, device="cuda")
+
+    def run(ahead, poke):
+        loader = sage.GPUSamplingDataloader(indptr, indices, seeds, 512, (4, 3), shuffle=True, rng_seed=5, ahead=ahead)
+        out = []
+        for _epoch in range(2):
+            for input_nodes, output_nodes, blocks in loader:
+                for _ in range(poke):
+                    torch.cuda.synchronize()
+                    loader.poke()
+                out.append([input_nodes.clone(), output_nodes.clone()] +
+                           [b[k][:int(b["indptr"][-1])].clone() if k.startswith("indices") else b[k].clone()
+                            for b in blocks for k in ("indptr", "indices_global", "indices_local", "src_nodes", "dst_nodes")])
+        return out
+    base = run(False, 0)
+    assert len(base) == 2 * 10
+    for ahead, poke in ((True, 0), (True, 1), (True, 3)):
+        other = run(ahead, poke)
+        assert len(other) == len(base)
+        for a, b in zip(base, other):
+            assert all(torch.equal(x, y) for x, y in zip(a, b))
