@@ -535,14 +535,35 @@ def tensor_relabel(tensors):
 
 
 class _PendingBlock:
-    __slots__ = ("sub_indptr", "buf", "n", "host", "event")
+    __slots__ = ("sub_indptr", "keys", "unique", "relabelled", "n", "host", "event")
 
 
-def sample_block_launch(indptr, indices, seeds, num_pick, rng_seed=0, rng_offset=0):
+class BlockBuffers:
+    """Device and pinned memory for ``sample_block_launch`` hops of up to ``max_seeds`` seeds, allocated once.  A loader
+    that builds minibatches on a stream of its own keeps two sets of these instead of going through the caching
+    allocator every hop (no per-hop allocation, no cross-stream bookkeeping; and on a device that has peers mapped a
+    fresh device allocation costs milliseconds)."""
+
+    def __init__(self, max_seeds, num_pick, dtype, device):
+        self.max_seeds, self.num_pick, self.dtype = int(max_seeds), int(num_pick), dtype
+        self.cap = self.max_seeds * (self.num_pick + 1)
+        ws_bytes = lib.f2c_sample_block_workspace(self.max_seeds, self.num_pick, _DT[dtype])
+        if ws_bytes <= 0:
+            raise RuntimeError("sample_block: num_pick must be in [1, 64]")
+        self.ws = torch.empty((ws_bytes,), dtype=torch.uint8, device=device)
+        self.sub_indptr = torch.empty((self.max_seeds + 1,), dtype=dtype, device=device)
+        self.ids = torch.empty((3, self.cap), dtype=dtype, device=device)  # keys, unique, relabelled
+        self.header = torch.empty((4,), dtype=torch.int64, device=device)
+        self.host = torch.empty((4,), dtype=torch.int64, pin_memory=True)
+        self.event = torch.cuda.Event()
+
+
+def sample_block_launch(indptr, indices, seeds, num_pick, rng_seed=0, rng_offset=0, buffers=None):
     """First half of ``sample_block``: queues the hop on the current stream, starts the copy of its three counters to pinned
     host memory and returns without waiting.  ``sample_block_finish`` of the returned object gives the result; its
     ``event`` tells (``query()``) whether that would block.  A loader uses the pair to build the next minibatch on a
-    side stream while the current one trains."""
+    side stream while the current one trains.  ``buffers``: a ``BlockBuffers`` to work in (the results are then views of
+    it, valid until it is used again); default: fresh tensors."""
     _chk(indptr, "indptr", (torch.int32, torch.int64))
     _chk(indices, "indices", (indptr.dtype,))
     _chk(seeds, "seeds", (indptr.dtype,))
@@ -550,21 +571,29 @@ def sample_block_launch(indptr, indices, seeds, num_pick, rng_seed=0, rng_offset
     if n == 0:
         raise RuntimeError("sample_block: needs at least one seed")
     n_keys = n * (int(num_pick) + 1)
-    ws_bytes = lib.f2c_sample_block_workspace(n, int(num_pick), _DT[dt])
-    if ws_bytes <= 0:
-        raise RuntimeError("sample_block: num_pick must be in [1, 64]")
     pend = _PendingBlock()
     with _on(indptr):
-        ws = torch.empty((ws_bytes,), dtype=torch.uint8, device=dev)
-        pend.sub_indptr = torch.empty((n + 1,), dtype=dt, device=dev)
-        pend.buf = buf = torch.empty((3, n_keys), dtype=dt, device=dev)  # keys, unique, relabelled
-        header = torch.empty((4,), dtype=torch.int64, device=dev)
+        if buffers is None:
+            ws_bytes = lib.f2c_sample_block_workspace(n, int(num_pick), _DT[dt])
+            if ws_bytes <= 0:
+                raise RuntimeError("sample_block: num_pick must be in [1, 64]")
+            ws = torch.empty((ws_bytes,), dtype=torch.uint8, device=dev)
+            pend.sub_indptr = torch.empty((n + 1,), dtype=dt, device=dev)
+            ids = torch.empty((3, n_keys), dtype=dt, device=dev)
+            header = torch.empty((4,), dtype=torch.int64, device=dev)
+            pend.host = torch.empty((4,), dtype=torch.int64, pin_memory=True)
+            pend.event = torch.cuda.Event()
+        else:
+            if n > buffers.max_seeds or int(num_pick) != buffers.num_pick or dt != buffers.dtype:
+                raise RuntimeError("sample_block: the buffers were sized for another hop")
+            ws, ws_bytes, ids, header = buffers.ws, buffers.ws.numel(), buffers.ids, buffers.header
+            pend.sub_indptr = buffers.sub_indptr[:n + 1]
+            pend.host, pend.event = buffers.host, buffers.event
+        pend.keys, pend.unique, pend.relabelled = ids[0, :n_keys], ids[1, :n_keys], ids[2, :n_keys]
         check(lib.f2c_sample_block(_ptr(indptr), _ptr(indices), _ptr(seeds), _DT[dt], n, int(num_pick),
-                                   int(rng_seed) & 0xFFFFFFFFFFFFFFFF, int(rng_offset), _ptr(pend.sub_indptr), _ptr(buf[0]), _ptr(buf[1]),
-                                   _ptr(buf[2]), _ptr(header), _ptr(ws), ws_bytes, _stream(indptr)))
-        pend.host = torch.empty((4,), dtype=torch.int64, pin_memory=True)
+                                   int(rng_seed) & 0xFFFFFFFFFFFFFFFF, int(rng_offset), _ptr(pend.sub_indptr), _ptr(pend.keys),
+                                   _ptr(pend.unique), _ptr(pend.relabelled), _ptr(header), _ptr(ws), ws_bytes, _stream(indptr)))
         pend.host.copy_(header, non_blocking=True)
-        pend.event = torch.cuda.Event()
         pend.event.record(torch.cuda.current_stream(dev))
     pend.n = n
     return pend
@@ -578,8 +607,7 @@ def sample_block_finish(pend):
         raise RuntimeError("sample_block: negative id in the graph or the seeds")
     if err != 0:
         raise RuntimeError("sample_block: hash table overflow")
-    n, buf = pend.n, pend.buf
-    return pend.sub_indptr, buf[0, n:], buf[1, :n_unique], buf[2, n:]
+    return pend.sub_indptr, pend.keys[pend.n:], pend.unique[:n_unique], pend.relabelled[pend.n:]
 
 
 def sample_block(indptr, indices, seeds, num_pick, rng_seed=0, rng_offset=0):

@@ -308,7 +308,9 @@ class GPUSamplingDataloader:
     of every step although it needs nothing from the model.  Here ``__next__`` hands out the minibatch built during the
     previous step and queues the first hop of the next; each later hop is queued by ``poke()`` - which the training loop
     calls between its phases and which never blocks - or, at the latest, by the next ``__next__``.  The minibatches are
-    the same either way: sampling draws are keyed by epoch, step and hop."""
+    the same either way: sampling draws are keyed by epoch, step and hop.  In this mode the loader works in two sets of
+    buffers it allocates once (sized for the largest possible hop), used alternately: the tensors of a minibatch are
+    views of one set and stay valid until the next-but-one ``__next__``."""
 
     def __init__(self, indptr, indices, seeds, batchsize, num_picks, rank=0, world=1, shuffle=True, rng_seed=0, ahead=True):
         self.indptr, self.indices = indptr, indices
@@ -319,6 +321,7 @@ class GPUSamplingDataloader:
         self.rank = rank
         self.side = torch.cuda.Stream(device=indptr.device) if ahead else None
         self._gen = self._result = self._wait = None
+        self._sets, self._consumed, self._built = None, [None, None], 0
 
     def __len__(self):
         return (self.seeds.numel() + self.batchsize - 1) // self.batchsize
@@ -338,14 +341,24 @@ class GPUSamplingDataloader:
             self._start()
         return self
 
-    def _hops(self, seeds, step):
+    def _buffer_sets(self):
+        if self._sets is None:
+            n_nodes, bound, sizes = self.indptr.numel() - 1, self.batchsize, []
+            for num_pick in reversed(self.num_picks):
+                sizes.append((bound, num_pick))
+                bound = min(bound * (num_pick + 1), n_nodes)  # a hop's distinct nodes are the next hop's seeds
+            self._sets = [[ops.BlockBuffers(b, k, self.indptr.dtype, self.indptr.device) for b, k in sizes] for _ in range(2)]
+        return self._sets
+
+    def _hops(self, seeds, step, buffers=None):
         """Generator over one minibatch: yields the pending hop after queueing it, returns the minibatch."""
         output_nodes, blocks = seeds, []
         for hop, num_pick in enumerate(reversed(self.num_picks)):
             # one library call and one host read (the number of distinct nodes) per hop; the index tensors carry a tail
             # behind indptr[-1] that no kernel reads
             pending = ops.sample_block_launch(self.indptr, self.indices, seeds, num_pick,
-                                              rng_seed=(self.rng_seed * 7919 + self.epoch) * 65536 + self.rank, rng_offset=step * 8 + hop)
+                                              rng_seed=(self.rng_seed * 7919 + self.epoch) * 65536 + self.rank, rng_offset=step * 8 + hop,
+                                              buffers=None if buffers is None else buffers[hop])
             yield pending
             sub_indptr, sub_indices, unique, local = ops.sample_block_finish(pending)
             blocks.insert(0, dict(dst_nodes=seeds, src_nodes=unique, indptr=sub_indptr, indices_global=sub_indices, indices_local=local))
@@ -357,7 +370,11 @@ class GPUSamplingDataloader:
             self._gen = None
             return
         seeds = self.order[self.curr * self.batchsize:(self.curr + 1) * self.batchsize]
-        self._gen = self._hops(seeds, self.curr)
+        which = self._built % 2
+        self._built += 1
+        if self._consumed[which] is not None:  # the minibatch that last lived in this set: its step must be through
+            self.side.wait_event(self._consumed[which])
+        self._gen = self._hops(seeds, self.curr, self._buffer_sets()[which])
         self.curr += 1
         self._advance()
 
@@ -393,10 +410,11 @@ class GPUSamplingDataloader:
         batch, self._result = self._result, None
         cur = torch.cuda.current_stream(self.indptr.device)
         cur.wait_stream(self.side)
-        input_nodes, output_nodes, blocks = batch
-        for b in blocks:  # allocated on the side stream, used on this one from now on
-            for v in b.values():
-                if torch.is_tensor(v):
-                    v.record_stream(cur)
+        # Everything queued on this stream so far belongs to earlier minibatches: once it has run, the set of the
+        # minibatch handed out before this one may be overwritten (which is what the _start below goes on to do).
+        previous = self._built % 2
+        if self._consumed[previous] is None:
+            self._consumed[previous] = torch.cuda.Event()
+        self._consumed[previous].record(cur)
         self._start()
         return batch
