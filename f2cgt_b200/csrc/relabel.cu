@@ -10,38 +10,9 @@
 //   f2c_relabel_mark    builds the table and writes first[i] = 1 where position i is a first occurrence;
 //   (caller)            rank = exclusive prefix sum of first; n_unique = its total;
 //   f2c_relabel_assign  writes unique[rank[i]] = keys[i] for first occurrences and relabelled[i] = rank[first position of keys[i]].
-#include "common.cuh"
+#include "block_build.cuh"
 
 namespace f2c {
-
-constexpr unsigned long long kEmptyKey = ~0ull;
-
-__device__ __forceinline__ uint64_t hash64(uint64_t x) {  // murmur3 finaliser
-  x ^= x >> 33; x *= 0xff51afd7ed558ccdull; x ^= x >> 33; x *= 0xc4ceb9fe1a85ec53ull; x ^= x >> 33;
-  return x;
-}
-
-// slot of `key` in the table (inserting it when absent); -1 if no slot was found within `cap` probes (cannot
-// happen with cap >= 2 n unless the table is corrupted; the caller flags it)
-__device__ __forceinline__ int64_t find_or_insert(unsigned long long* tab_keys, int64_t cap_mask, unsigned long long key) {
-  int64_t slot = (int64_t)(hash64(key) & (uint64_t)cap_mask);
-  for (int64_t probe = 0; probe <= cap_mask; ++probe) {
-    const unsigned long long prev = atomicCAS(tab_keys + slot, kEmptyKey, key);
-    if (prev == kEmptyKey || prev == key) return slot;
-    slot = (slot + 1) & cap_mask;
-  }
-  return -1;
-}
-__device__ __forceinline__ int64_t find(const unsigned long long* tab_keys, int64_t cap_mask, unsigned long long key) {
-  int64_t slot = (int64_t)(hash64(key) & (uint64_t)cap_mask);
-  for (int64_t probe = 0; probe <= cap_mask; ++probe) {
-    const unsigned long long k = tab_keys[slot];
-    if (k == key) return slot;
-    if (k == kEmptyKey) return -1;
-    slot = (slot + 1) & cap_mask;
-  }
-  return -1;
-}
 
 template <typename IdxT>
 __global__ void __launch_bounds__(256) relabel_insert_kernel(const IdxT* __restrict__ keys, int64_t n, unsigned long long* tab_keys,

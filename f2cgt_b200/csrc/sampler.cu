@@ -9,11 +9,9 @@
 // per seed runs Floyd's subset algorithm (num_pick <= 64 draws, chosen positions kept in registers /
 // local memory); draws come from Philox4x32-10 keyed by the caller's seed with the seed node's
 // position as counter, so a sample is reproducible and independent of launch geometry.
-#include "common.cuh"
+#include "block_build.cuh"
 
 namespace f2c {
-
-constexpr int kMaxPick = 64;
 
 template <typename IdxT>
 __global__ void __launch_bounds__(256) sample_degrees_kernel(const IdxT* __restrict__ indptr, const IdxT* __restrict__ seeds,
@@ -32,29 +30,7 @@ __global__ void __launch_bounds__(256) sample_neighbors_kernel(const IdxT* __res
                                                                uint64_t rng_seed, uint64_t rng_offset) {
   int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n_seeds) return;
-  const int64_t v = (int64_t)seeds[i];
-  const int64_t begin = (int64_t)indptr[v];
-  const int64_t d = (int64_t)indptr[v + 1] - begin;
-  IdxT* out = out_indices + (int64_t)out_indptr[i];
-  if (d <= num_pick) {
-    for (int64_t t = 0; t < d; ++t) out[t] = indices[begin + t];
-    return;
-  }
-  // Floyd: for j = d-k .. d-1: t = U{0..j}; take t unless already taken, then take j.
-  Philox ph(rng_seed, rng_offset);
-  int64_t chosen[kMaxPick];
-  uint4 r = make_uint4(0, 0, 0, 0);
-  for (int s = 0; s < num_pick; ++s) {
-    if ((s & 1) == 0) r = ph((uint64_t)i * (kMaxPick / 2) + (uint64_t)(s >> 1));
-    const uint64_t bits = (s & 1) == 0 ? ((uint64_t)r.x << 32 | r.y) : ((uint64_t)r.z << 32 | r.w);
-    const int64_t j = d - num_pick + s;
-    // multiply-shift maps 64 random bits to [0, j]; the bias is below 2^-32 for any graph that fits in memory
-    int64_t t = (int64_t)__umul64hi(bits, (uint64_t)(j + 1));
-    bool taken = false;
-    for (int q = 0; q < s; ++q) taken |= chosen[q] == t;
-    chosen[s] = taken ? j : t;
-  }
-  for (int s = 0; s < num_pick; ++s) out[s] = indices[begin + chosen[s]];
+  sample_one_seed(indptr, indices, (int64_t)seeds[i], i, out_indices + (int64_t)out_indptr[i], num_pick, rng_seed, rng_offset);
 }
 
 // Entries [out_indptr[n_seeds], capacity) of an over-allocated index buffer get the id of the first seed: a valid,
