@@ -462,19 +462,28 @@ def run_ours(args):
         from f2cgt_b200 import train_graphsage
         del flush
         torch.cuda.empty_cache()
-        for table in ("replicated", "sharded_peer", "sharded"):
-            if table != "replicated" and world == 1:
-                continue
+        what = {
+            "small": ("2,449,029 nodes, mean degree 50", "two-level: hot 5 % SQ 8 bits + VQ 4 x 32 (ratio 128), D = 128, 172 classes, 122,880 "
+                      "training ids split over the ranks, batch 1024, fan-out 12,12,12, dropout 0.5"),
+            "config4": ("111,059,956 nodes, mean degree 14.4 (1.6 G edges, int64 CSC replicated per GPU)", "two-level: hot 5 % SQ 8 bits + VQ 4 x 32, "
+                        "D = 128, 172 classes, 1.2 M training ids split over the ranks, batch 1024, fan-out 12,12,12, dropout 0.5"),
+            "config5": ("65,608,366 nodes, mean degree 54.9 (3.6 G edges, int64 CSC replicated per GPU)", "two-level: hot 2 % SQ 4 bits + VQ 4 x 64, "
+                        "D = 256, 64 classes, 1.2 M training ids split over the ranks, batch 1024 per GPU, fan-out 15,10,5, dropout 0.5"),
+        }
+        # the 2.45 M-node graph with every table placement, then the two large configurations of the metric with the
+        # placement a deployment would use (replicated on one GPU, row-sharded with peer loads on several)
+        runs = [("small", t, dict(epochs=2, min_timed_steps=100)) for t in ("replicated", "sharded_peer", "sharded") if t == "replicated" or world > 1]
+        runs += [(ps, "replicated" if world == 1 else "sharded_peer", dict(epochs=2)) for ps in ("config4", "config5")]
+        for preset, table, kw in runs:
             try:
-                rec = train_graphsage.train("small", table, rank, world, local_rank, epochs=2, min_timed_steps=100)
-                epoch.append({"table": table, "ms_per_step": rec["ms_per_step"], "s_per_epoch": rec["value"], "steps": rec["steps_per_epoch_per_gpu"],
-                              "timed_steps": rec["timed_steps_per_gpu"], "breakdown_ms": rec["breakdown_ms"],
-                              "precision": rec["precision"], "blocks_built_ahead": rec["blocks_built_ahead"],
-                              "graph": "2,449,029 nodes, mean degree 50 (the 111 M-node graph of the two-level configuration is not built here)",
-                              "codecs": "two-level: hot 5 % SQ 8 bits + VQ 4 x 32 (ratio 128), D = 128, 172 classes, 122,880 training ids "
-                                        "split over the ranks, batch 1024, fan-out 12,12,12, dropout 0.5"})
+                rec = train_graphsage.train(preset, table, rank, world, local_rank, **kw)
+                epoch.append({"preset": preset, "table": table, "ms_per_step": rec["ms_per_step"], "s_per_epoch": rec["value"],
+                              "steps": rec["steps_per_epoch_per_gpu"], "timed_steps": rec["timed_steps_per_gpu"],
+                              "breakdown_ms": rec["breakdown_ms"], "precision": rec["precision"],
+                              "blocks_built_ahead": rec["blocks_built_ahead"], "graph": what[preset][0], "codecs": what[preset][1]})
             except Exception as e:  # noqa: BLE001
-                epoch.append({"table": table, "error": repr(e)[:300]})
+                epoch.append({"preset": preset, "table": table, "error": repr(e)[:300]})
+            torch.cuda.empty_cache()
         flush = torch.zeros(64 << 20, dtype=torch.float32, device=device)
 
     if rank == 0:

@@ -313,6 +313,11 @@ class GPUSamplingDataloader:
     views of one set and stay valid until the next-but-one ``__next__``."""
 
     def __init__(self, indptr, indices, seeds, batchsize, num_picks, rank=0, world=1, shuffle=True, rng_seed=0, ahead=True):
+        # one check of the graph per loader (the sampling kernels trust it): offsets that wrapped in a too narrow integer
+        # type show up here
+        first, last = indptr[[0, -1]].tolist()
+        if first != 0 or last != indices.numel():
+            raise ValueError(f"indptr must run from 0 to len(indices) = {indices.numel()} (it runs from {first} to {last})")
         self.indptr, self.indices = indptr, indices
         self.batchsize, self.num_picks = int(batchsize), list(num_picks)
         self.shuffle, self.rng_seed, self.epoch = shuffle, rng_seed, 0

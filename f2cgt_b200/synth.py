@@ -25,6 +25,9 @@ def power_law_graph(num_nodes, avg_degree, exponent=2.1, seed=0, device="cuda", 
     indptr = torch.zeros(num_nodes + 1, dtype=torch.int64, device=device)
     torch.cumsum(deg, 0, out=indptr[1:])
     nnz = int(indptr[-1].item())
+    if nnz > torch.iinfo(index_dtype).max:
+        # the library's CSC has ONE integer type for offsets and ids; offsets beyond its range would wrap silently
+        raise ValueError(f"{nnz} edges do not fit {index_dtype} offsets: build this graph with int64")
     # degree-proportional endpoints: pick a uniformly random stub, then the node that owns it
     indices = torch.empty(nnz, dtype=index_dtype, device=device)
     chunk = 1 << 26
