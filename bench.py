@@ -38,6 +38,7 @@ FAN_OUT = (12, 12, 12)
 BITS = (1, 2, 4)
 COLUMN_SLICE = 128
 N_MINIBATCHES = 6
+HOT_REPLICATED = 0.05  # share of the rows (the most often sampled ones) every GPU keeps beside its shard of the rest
 METRIC = "fused_sq_decompress_spmm_sampled_edges_per_s"
 WORKLOAD = ("SQ 1/2/4-bit packed table 2449029x128 (N(0,1) features), power-law graph (Zipf 2.1, mean degree 50), "
             "6 minibatches of 1024 seeds x fan-out 12,12,12, outermost block, all three widths per step; graph, tables and "
@@ -261,6 +262,43 @@ def sharded_placements(args, capi, tables, blocks, extra, flush, device, rank, w
             assert torch.equal(a, ref), f"peer-load result differs from the replicated table at {b} bits"
     except Exception as e:  # noqa: BLE001
         out["sharded_peer_loads_error"] = repr(e)[:300]
+    # The same partitioning with the HOT_REPLICATED most often sampled rows on every GPU (the reference's loader ranks
+    # nodes by a presampling pass and caches the hottest per GPU: examples/dataloader.py:234-260,273-304; here the rank is
+    # the in-degree, which is what the synthetic graph's sampling probability follows).  The table is numbered hot rows
+    # first - a one-off relabelling of graph, table and block indices outside the timed region.
+    try:
+        import numpy as np
+        deg = torch.from_numpy(np.diff(np.asarray(cpu_workload(need_graph=True)["graph_indptr"]))).to(device)
+        order = torch.argsort(deg, descending=True, stable=True)          # new id -> old id
+        new_id = torch.empty_like(order)
+        new_id[order] = torch.arange(NUM_NODES, device=device)            # old id -> new id
+        n_rep = int(NUM_NODES * HOT_REPLICATED)
+        lo2, hi2 = shard.shard_bounds(NUM_NODES - n_rep, world, rank)
+        heads, tails = {}, {}
+        for b in BITS:
+            renumbered = tables[b][0][order]
+            heads[b] = renumbered[:n_rep].contiguous()
+            tails[b] = shard.PeerTable(renumbered[n_rep + lo2:n_rep + hi2].contiguous(), NUM_NODES - n_rep)
+            del renumbered
+        # ids of the sharded rows start at the next multiple of the shard size (one division locates any row)
+        first_cold = ops.peer_first_cold_id(n_rep, shard.rows_per_rank(NUM_NODES - n_rep, world))
+        new_id = torch.where(new_id < n_rep, new_id, new_id + (first_cold - n_rep))
+        blocks_hot_first = [(ip, new_id[ix]) for ip, ix in blocks]
+        remote = sum(int(((ix >= first_cold) & (((ix - first_cold) < lo2) | ((ix - first_cold) >= hi2))).sum()) for _, ix in blocks_hot_first)
+        out["hot_replicated_remote_edge_share"] = remote / max(sum(ix.numel() for _, ix in blocks), 1)
+
+        def step_hot(i):
+            ip, ix = blocks_hot_first[i]
+            for b in BITS:
+                ops.sq_decompress_spmm_csr_peer(tails[b], tables[b][1], ip, ix, b, COLUMN_SLICE, FEAT_DIM, replicated=heads[b])
+        out["sharded_peer_loads_hot_replicated"] = time_steps(step_hot, blocks, args.steps, args.warmup, flush, torch)
+        ip, ix = blocks_hot_first[0]
+        for b in BITS:
+            a = ops.sq_decompress_spmm_csr_peer(tails[b], tables[b][1], ip, ix, b, COLUMN_SLICE, FEAT_DIM, replicated=heads[b])
+            ref = capi.sq_decompress_spmm_csr(tables[b][0], tables[b][1], blocks[0][0], blocks[0][1], b, COLUMN_SLICE, FEAT_DIM)
+            assert torch.equal(a, ref), f"hot-replicated peer-load result differs from the replicated table at {b} bits"
+    except Exception as e:  # noqa: BLE001
+        out["sharded_peer_loads_hot_replicated_error"] = repr(e)[:300]
     try:
         st = {b: shard.ShardedTable(shards[b], NUM_NODES) for b in BITS}
         plans = [st[BITS[0]].plan(src) for src, _ in extra]  # the id exchange happens when the block is sampled
@@ -436,25 +474,36 @@ def run_ours(args):
     value, value_ms, placement_of_value = placements["replicated"], total_ms, "replicated (one GPU holds the whole table)"
     if world > 1:
         raw = sharded_placements(args, capi, tables, blocks, extra, flush, device, rank, world, torch, dist)
-        for name in ("sharded_peer_loads", "sharded_nccl_all_to_all"):
+        names = ("sharded_peer_loads_hot_replicated", "sharded_peer_loads", "sharded_nccl_all_to_all")
+        for name in names:
             ok = torch.tensor([1.0 if name in raw else 0.0], dtype=torch.float64, device=device)
             dist.all_reduce(ok, op=dist.ReduceOp.MIN)
             if float(ok[0]) == 1.0:
                 placements[name] = reduce_rate(*raw[name])
             elif rank == 0 and name + "_error" in raw:
                 placements[name + "_error"] = raw[name + "_error"]
-        if "sharded_peer_loads" in placements:  # the headline at N > 1: the table really partitioned, 1/N of the rows per GPU
-            value = placements["sharded_peer_loads"]
-            tmax = torch.tensor([raw["sharded_peer_loads"][0]], dtype=torch.float64, device=device)
-            dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
-            value_ms = float(tmax[0])
-            placement_of_value = "row-sharded over the GPUs, the fused kernel reads remote rows over NVLink (peer mappings, no collective)"
-        elif "sharded_nccl_all_to_all" in placements:
-            value = placements["sharded_nccl_all_to_all"]
-            tmax = torch.tensor([raw["sharded_nccl_all_to_all"][0]], dtype=torch.float64, device=device)
-            dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
-            value_ms = float(tmax[0])
-            placement_of_value = "row-sharded over the GPUs, rows fetched with an NCCL all-to-all before the fused kernel"
+        if "hot_replicated_remote_edge_share" in raw:
+            share = torch.tensor([raw["hot_replicated_remote_edge_share"]], dtype=torch.float64, device=device)
+            dist.all_reduce(share, op=dist.ReduceOp.MAX)
+            placements["hot_replicated_remote_edge_share"] = float(share[0])
+        # The headline at N > 1 is a placement in which the table is really partitioned: every GPU holds 1/N of the rows
+        # and, in the first choice, the HOT_REPLICATED hottest rows besides.
+        what = {
+            "sharded_peer_loads_hot_replicated": f"row-sharded over the GPUs with the {HOT_REPLICATED:.0%} most often sampled rows on every GPU "
+                                                 f"({HOT_REPLICATED:.0%} + {1 - HOT_REPLICATED:.0%} / N of the table per GPU); the fused kernel reads "
+                                                 "the remaining remote rows over NVLink (peer mappings, no collective)",
+            "sharded_peer_loads": "row-sharded over the GPUs (1/N of the table per GPU), the fused kernel reads remote rows over NVLink "
+                                  "(peer mappings, no collective)",
+            "sharded_nccl_all_to_all": "row-sharded over the GPUs, rows fetched with an NCCL all-to-all before the fused kernel",
+        }
+        for name in names:
+            if name in placements:
+                value = placements[name]
+                tmax = torch.tensor([raw[name][0]], dtype=torch.float64, device=device)
+                dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
+                value_ms = float(tmax[0])
+                placement_of_value = what[name]
+                break
 
     # ---- GraphSAGE epoch (second half of the metric): replicated and sharded table, same process group
     epoch = []

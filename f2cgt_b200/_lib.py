@@ -53,6 +53,8 @@ SIGNATURES = {
     "f2c_spmm_csr_backward": [p, p, p, ci, p, i64, i64, i64, ci, p],
     "f2c_sq_spmm_csr": [p, ci, p, i64, p, p, ci, p, i64, i64, i64, i64, ci, i64, ci, EP, p],
     "f2c_sq_spmm_csr_peer": [p, ci, i64, ci, p, i64, p, p, ci, p, i64, i64, i64, i64, ci, i64, ci, EP, p],
+    "f2c_peer_hot_first_cold_id": [i64, i64],
+    "f2c_sq_spmm_csr_peer_hot": [p, i64, p, ci, i64, ci, p, i64, p, p, ci, p, i64, i64, i64, i64, ci, i64, ci, EP, p],
     "f2c_shard_create": [p, i64, p, p, p],
     "f2c_shard_free": [p],
     "f2c_shard_open": [p, p],
@@ -82,7 +84,7 @@ SIGNATURES = {
     "f2c_version": [],
 }
 _RESTYPE = {"f2c_last_error": C.c_char_p, "f2c_kmeans_assign_workspace": C.c_int64, "f2c_relabel_capacity": C.c_int64,
-            "f2c_sample_block_workspace": C.c_int64}
+            "f2c_sample_block_workspace": C.c_int64, "f2c_peer_hot_first_cold_id": C.c_int64}
 
 for _name, _args in SIGNATURES.items():
     _fn = getattr(lib, _name)  # AttributeError here = header and library out of step

@@ -60,6 +60,8 @@ struct PeerInfo {
   const void* shard[8];
   int world;
   int64_t rows_per_shard;
+  const void* replicated;   // local copy of the leading (most often sampled) rows, or null
+  int64_t n_replicated;
 };
 
 struct SqParams {
@@ -76,8 +78,11 @@ struct SqParams {
   int logG;
   int code_kind;
   int reduce;
-  // row-sharded table (PEER kernels): row r lives on shard r / rows_per_shard, all shards mapped into this process
-  const uint8_t* shard[8];
+  // row-sharded table (PEER kernels): id r lives in slot r / rows_per_shard of this pointer table, all of it mapped into
+  // this process.  Without replicated rows the slots are the shards.  With n_replicated leading rows kept on every GPU
+  // the first ceil(n_replicated / rows_per_shard) slots point into that local copy and the shards follow: the ids of
+  // the sharded rows start at the next multiple of rows_per_shard, so one division serves both kinds of row.
+  const uint8_t* shard[16];
   uint32_t rows_per_shard;
   unsigned long long shard_magic;  // floor(2^64 / rows_per_shard) + 1: exact 32-bit division by one multiply-high
   int staged;        // 1: rows leave through the shared-memory staging area (feat_dim % 4 == 0)
@@ -401,6 +406,8 @@ static int launch_sq_spmm(const void* codes, int code_dtype, const float* codebo
   //      wavefronts (7.0 M against 4.5 M at 4 bits) that the table decode needs itself, so only the 2-bit shape, whose
   //      rows are cheap to stage and whose prefetch kernel is the most latency-bound, gains.
   const bool stream_by_default = BITS == 2 && peer == nullptr;
+  if (variant == F2C_KERNEL_STREAM && peer != nullptr && peer->n_replicated > 0)
+    return set_error(F2C_ERR_UNSUPPORTED, "%s: the streamed kernel does not serve a table with replicated leading rows", op);
   if ((variant == F2C_KERNEL_AUTO && stream_by_default) || variant == F2C_KERNEL_STREAM) {
     bool served = false;
     int rc = launch_sq_stream(BITS, sizeof(IdxT) == 4 ? F2C_I32 : F2C_I64, codes, code_dtype, codebooks, n_cb, indptr, indices, out, n_dst,
@@ -437,7 +444,11 @@ static int launch_sq_spmm(const void* codes, int code_dtype, const float* codebo
     int copies = BITS >= 4 ? 32 : BITS == 2 ? 16 : 8;
     bool lut = (n_cb == 1 || copies % G == 0) && variant != F2C_KERNEL_PREFETCH_ARITH;
     if (peer != nullptr) {
-      for (int r = 0; r < 8; ++r) p.shard[r] = (const uint8_t*)peer->shard[r < peer->world ? r : 0];
+      const int head_slots = (int)ceil_div(peer->n_replicated, peer->rows_per_shard);
+      for (int k = 0; k < 16; ++k) {
+        if (k < head_slots) p.shard[k] = (const uint8_t*)peer->replicated + (uint64_t)k * peer->rows_per_shard * row_bytes;
+        else p.shard[k] = (const uint8_t*)peer->shard[k - head_slots < peer->world ? k - head_slots : 0];
+      }
       p.rows_per_shard = (uint32_t)peer->rows_per_shard;
       p.shard_magic = ~0ull / (unsigned long long)peer->rows_per_shard + 1ull;
       constexpr int DEC = BITS <= 8 ? DEC_LUT : DEC_ARITH;
@@ -504,11 +515,30 @@ extern "C" int f2c_sq_spmm_csr_peer(const void* const* shard_ptrs_host, int worl
                                     int index_dtype, float* out, int64_t n_dst, int64_t n_src, int64_t src_dim,
                                     int64_t feat_dim, int bits, int64_t column_slice, int reduce,
                                     const f2c_epilogue* epilogue, void* stream) {
+  return f2c_sq_spmm_csr_peer_hot(nullptr, 0, shard_ptrs_host, world, rows_per_shard, code_dtype, codebooks, n_codebooks, indptr, indices,
+                                  index_dtype, out, n_dst, n_src, src_dim, feat_dim, bits, column_slice, reduce, epilogue, stream);
+}
+
+extern "C" int64_t f2c_peer_hot_first_cold_id(int64_t n_replicated, int64_t rows_per_shard) {
+  if (n_replicated <= 0 || rows_per_shard <= 0) return 0;
+  return ceil_div(n_replicated, rows_per_shard) * rows_per_shard;
+}
+
+extern "C" int f2c_sq_spmm_csr_peer_hot(const void* replicated_rows, int64_t n_replicated, const void* const* shard_ptrs_host, int world,
+                                        int64_t rows_per_shard, int code_dtype, const float* codebooks, int64_t n_codebooks,
+                                        const void* indptr, const void* indices, int index_dtype, float* out, int64_t n_dst,
+                                        int64_t n_src, int64_t src_dim, int64_t feat_dim, int bits, int64_t column_slice, int reduce,
+                                        const f2c_epilogue* epilogue, void* stream) {
   const char* op = "sq_decompress_spmm_csr_peer";
   F2C_REQUIRE(n_dst >= 0 && n_src >= 0, F2C_ERR_INVALID, "%s: negative size", op);
   F2C_REQUIRE(world >= 1 && world <= 8, F2C_ERR_LIMIT, "%s: 1 to 8 shards (got %d)", op, world);
-  F2C_REQUIRE(rows_per_shard >= 2 && rows_per_shard < (1ll << 32) && rows_per_shard * world >= n_src, F2C_ERR_INVALID,
-              "%s: %d shards of %lld rows do not cover %lld rows", op, world, (long long)rows_per_shard, (long long)n_src);
+  F2C_REQUIRE(rows_per_shard >= 2 && rows_per_shard < (1ll << 32), F2C_ERR_INVALID, "%s: rows_per_shard must be in [2, 2^32)", op);
+  const int64_t first_cold = f2c_peer_hot_first_cold_id(n_replicated, rows_per_shard);
+  F2C_REQUIRE(n_replicated >= 0 && (n_replicated == 0 || replicated_rows != nullptr) && first_cold / rows_per_shard + world <= 16,
+              F2C_ERR_INVALID, "%s: bad replicated row range (the replicated rows and the shards share 16 slots of rows_per_shard ids)", op);
+  F2C_REQUIRE(first_cold + rows_per_shard * world >= n_src, F2C_ERR_INVALID,
+              "%s: ids up to %lld are not covered by %lld replicated rows and %d shards of %lld rows", op, (long long)n_src,
+              (long long)n_replicated, world, (long long)rows_per_shard);
   F2C_REQUIRE(shard_ptrs_host != nullptr, F2C_ERR_INVALID, "%s: null pointer", op);
   int rc = validate_sq(op, code_dtype, n_codebooks, src_dim, feat_dim, bits, column_slice);
   if (rc) return rc;
@@ -553,6 +583,8 @@ extern "C" int f2c_sq_spmm_csr_peer(const void* const* shard_ptrs_host, int worl
 #undef F2C_PEER_CUDA
   peer.world = world;
   peer.rows_per_shard = rows_per_shard;
+  peer.replicated = replicated_rows;
+  peer.n_replicated = n_replicated;
   DropoutArgs drop = make_dropout(epilogue);
   const int variant = kernel_variant(epilogue);
   cudaStream_t st = (cudaStream_t)stream;

@@ -236,6 +236,27 @@ def cases(b):
     b.run("unpackbits_4bit", lambda: ops.unpackbits(pk, 4, FEAT), nbytes=un.numel() * 1.5, units=un.shape[0], unit_name="rows")
     del big, un, pk, feat
 
+    # ------------------------------------------------ a block hop (sampler + relabel): one cooperative kernel against the
+    #                                                  separate entry points, for the three hops of a fan-out 12,12,12 minibatch
+    if b.wanted("sample_block"):
+        gi, gx = b.graph()
+        gs = torch.Generator(device=dev)
+        gs.manual_seed(1000)
+        seeds = torch.randperm(N, generator=gs, device=dev)[:1024]
+        for hop in range(3):
+            n = seeds.numel()
+            keys = n * 13
+
+            def separate(sd=seeds):
+                ptr, idx = ops.csr_sampling(gi, gx, sd, 12, False, rng_seed=0, rng_offset=hop, exact=False)
+                return ops.tensor_relabel([sd, idx])
+
+            b.run(f"sample_block_hop{hop}", lambda sd=seeds: ops.sample_block_launch(gi, gx, sd, 12, rng_seed=0, rng_offset=hop),
+                  units=n, unit_name="seeds", note=f"{n} seeds x 12 picks = {keys} keys, one cooperative kernel, no host read")
+            b.run(f"sample_block_hop{hop}_separate_entry_points", separate, units=n, unit_name="seeds",
+                  note="csr_sampling(exact=False) + tensor_relabel: 12 kernels, 3 memsets, one host read inside the timed pair")
+            seeds = ops.sample_block(gi, gx, seeds, 12, rng_seed=0, rng_offset=hop)[2]
+
     # ------------------------------------------------ k-means assignment (configurations 3, 4, 5 sub-vector widths)
     for d in (8, 32, 64):
         x = torch.randn(N, d, generator=g, device=dev)

@@ -237,23 +237,40 @@ def sq_decompress_spmm_csr(compress_feat, codebooks, indptr, indices, target_bit
     return out
 
 
+def peer_first_cold_id(n_replicated, rows_per_shard):
+    """Id of the first sharded row of a table whose ``n_replicated`` hottest rows are kept on every GPU: the next multiple
+    of the shard size (ids between ``n_replicated`` and it are unused)."""
+    return int(lib.f2c_peer_hot_first_cold_id(int(n_replicated), int(rows_per_shard)))
+
+
 def sq_decompress_spmm_csr_peer(peer_table, codebooks, indptr, indices, target_bit, column_slice, feat_dim, reduce="mean",
-                                dropout=None, kernel="auto", out_rows=None):
+                                dropout=None, kernel="auto", out_rows=None, replicated=None):
     """``sq_decompress_spmm_csr`` over a row-sharded table (``f2cgt_b200.shard.PeerTable``): indices are global row ids,
-    remote rows are read by the kernel itself over NVLink."""
+    remote rows are read by the kernel itself over NVLink.
+
+    ``replicated``: a local tensor with the most often sampled rows of a table numbered hot rows first - ids below
+    ``len(replicated)`` read it, id ``peer_first_cold_id(len(replicated), peer_table.rpr) + r`` reads row r of the sharded
+    table (the cold remainder; its ids start at a multiple of the shard size so that one division locates any row)."""
     import ctypes
     _chk(codebooks, "codebooks", (torch.float32,))
     n_dst = _csc(indptr, indices)
     out = _block_out(n_dst, feat_dim, torch.float32, indptr.device, out_rows)
     if len(peer_table.pointers) != peer_table.world:
         raise RuntimeError("the peer table is closed")
+    n_rep = 0
+    if replicated is not None:
+        _chk(replicated, "replicated", (peer_table.dtype,))
+        if replicated.dim() != 2 or replicated.shape[1] != peer_table.row_width or replicated.device != indptr.device:
+            raise RuntimeError("replicated must hold rows of the sharded table's width on the block's device")
+        n_rep = replicated.shape[0]
     ptrs = (ctypes.c_void_p * peer_table.world)(*peer_table.pointers)
     ep = _epilogue(dropout, kernel)
     with _on(indptr):
-        check(lib.f2c_sq_spmm_csr_peer(ptrs, peer_table.world, peer_table.rpr, _DT[peer_table.dtype], _ptr(codebooks),
-                                       codebooks.shape[0], _ptr(indptr), _ptr(indices), _DT[indptr.dtype], _ptr(out), n_dst,
-                                       peer_table.n_rows, peer_table.row_width, feat_dim, target_bit, column_slice,
-                                       _REDUCE[reduce], ep, _stream(indptr)))
+        check(lib.f2c_sq_spmm_csr_peer_hot(_ptr(replicated) if n_rep else 0, n_rep, ptrs, peer_table.world, peer_table.rpr,
+                                           _DT[peer_table.dtype], _ptr(codebooks), codebooks.shape[0], _ptr(indptr), _ptr(indices),
+                                           _DT[indptr.dtype], _ptr(out), n_dst, peer_first_cold_id(n_rep, peer_table.rpr) + peer_table.n_rows,
+                                           peer_table.row_width,
+                                           feat_dim, target_bit, column_slice, _REDUCE[reduce], ep, _stream(indptr)))
     return out
 
 

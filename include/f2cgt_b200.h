@@ -137,6 +137,21 @@ int f2c_sq_spmm_csr_peer(const void* const* shard_ptrs_host, int world, int64_t 
                          int64_t feat_dim, int bits, int64_t column_slice, int reduce,
                          const f2c_epilogue* epilogue, void* stream);
 
+/* The same with the n_replicated most often sampled rows kept on EVERY GPU.  Sampling follows the degree distribution,
+ * so a few per cent of the rows serve most edges (the reference caches its hottest rows per GPU the same way, ranked by a
+ * presampling pass: examples/dataloader.py:234-260,273-304); the kernel then crosses NVLink only for the cold remainder.
+ * Numbering: ids [0, n_replicated) are the replicated rows, read from replicated_rows (device memory of the current GPU,
+ * same row layout); the sharded rows follow from id C = f2c_peer_hot_first_cold_id(n_replicated, rows_per_shard) - the
+ * next multiple of rows_per_shard - so that id C + r is row r of the sharded scheme above and ONE division by
+ * rows_per_shard locates either kind of row (ids between n_replicated and C are unused).  The replicated rows and the
+ * shards share 16 slots of rows_per_shard ids: ceil(n_replicated / rows_per_shard) + world <= 16.  n_src = largest id + 1. */
+int64_t f2c_peer_hot_first_cold_id(int64_t n_replicated, int64_t rows_per_shard);
+int f2c_sq_spmm_csr_peer_hot(const void* replicated_rows, int64_t n_replicated, const void* const* shard_ptrs_host, int world,
+                             int64_t rows_per_shard, int code_dtype, const float* codebooks, int64_t n_codebooks,
+                             const void* indptr, const void* indices, int index_dtype, float* out, int64_t n_dst,
+                             int64_t n_src, int64_t src_dim, int64_t feat_dim, int bits, int64_t column_slice, int reduce,
+                             const f2c_epilogue* epilogue, void* stream);
+
 /* Shard memory that the other ranks of the box can map (no counterpart in the reference).  These five are the only
  * entry points that allocate, free or map device memory.
  *   f2c_shard_create  allocates `bytes` on the current device, copies `rows` (device memory) into it on `stream`

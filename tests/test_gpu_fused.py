@@ -431,6 +431,45 @@ def test_peer_sharded_table_equals_whole_table(capi, oracle, bits, world):
     assert torch.equal(got, want)
 
 
+@pytest.mark.parametrize("bits", [1, 2, 4, 8, 16])
+@pytest.mark.parametrize("world,n_rep", [(2, 1), (3, 100), (8, 400), (4, 700), (2, 850)])
+def test_peer_sharded_table_with_replicated_leading_rows(capi, oracle, bits, world, n_rep):
+    """Hot-first numbering: rows [0, n_rep) from the local copy, row n_rep + r from the sharded remainder (every shard on
+    this GPU here); up to most of the table replicated; more replicated rows than the 16 slots of the pointer table hold are refused."""
+    from f2cgt_b200 import ops, shard
+    rng = np.random.default_rng(bits * 10 + world)
+    n_src, n_dst, D = 1003, 400, 128
+    _, cb, stored = sq_table(oracle, rng, n_src, D, bits, 128)
+    indptr, indices = random_csc(rng, n_dst, n_src, max_deg=20)
+    table = dev(stored)
+    cold = n_src - n_rep
+    rpr = shard.rows_per_rank(cold, world)
+
+    class FakePeers:
+        pass
+    pt = FakePeers()
+    pt.world, pt.rpr, pt.n_rows = world, rpr, cold
+    tail = table[n_rep:]
+    tensors = [tail[r * rpr:(r + 1) * rpr].clone() if r * rpr < cold else table[:1].clone() for r in range(world)]
+    pt.pointers = [t.data_ptr() for t in tensors]
+    pt.dtype, pt.row_width = table.dtype, table.shape[1]
+    head = table[:n_rep].clone()
+    # ids of the sharded rows start at the next multiple of the shard size
+    first_cold = ops.peer_first_cold_id(n_rep, rpr)
+    assert first_cold >= n_rep and first_cold % rpr == 0 and first_cold - n_rep < rpr
+    ids = np.where(indices < n_rep, indices, indices - n_rep + first_cold)
+    got = ops.sq_decompress_spmm_csr_peer(pt, dev(cb), dev(indptr), dev(ids), bits, 128, D, replicated=head)
+    want = capi.sq_decompress_spmm_csr(table, dev(cb), dev(indptr), dev(indices), bits, 128, D)
+    assert torch.equal(got, want)
+    with pytest.raises(RuntimeError):  # the streamed family does not serve this layout and says so
+        ops.sq_decompress_spmm_csr_peer(pt, dev(cb), dev(indptr), dev(ids), bits, 128, D, replicated=head, kernel="stream")
+    if world == 8:
+        with pytest.raises(RuntimeError):  # 900 replicated rows = 69 slots of 13 rows beside 8 shards
+            big = FakePeers()
+            big.world, big.rpr, big.n_rows, big.pointers, big.dtype, big.row_width = 8, 13, 103, pt.pointers, table.dtype, table.shape[1]
+            ops.sq_decompress_spmm_csr_peer(big, dev(cb), dev(indptr), dev(ids), bits, 128, D, replicated=table[:900].clone())
+
+
 @pytest.mark.parametrize("hot_bits,D,n_cb,cs", [(8, 128, 4, 32), (4, 256, 4, 64), (8, 128, 16, 8), (0, 128, 4, 32)])
 @pytest.mark.parametrize("world,hot_first", [(2, False), (3, True), (8, False)])
 def test_two_level_over_sharded_tables_equals_whole_tables(capi, oracle, hot_bits, D, n_cb, cs, world, hot_first):
