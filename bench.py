@@ -273,18 +273,23 @@ def sharded_placements(args, capi, tables, blocks, extra, flush, device, rank, w
         new_id = torch.empty_like(order)
         new_id[order] = torch.arange(NUM_NODES, device=device)            # old id -> new id
         n_rep = int(NUM_NODES * HOT_REPLICATED)
-        lo2, hi2 = shard.shard_bounds(NUM_NODES - n_rep, world, rank)
+        n_rep += (NUM_NODES - n_rep) % world                               # equal shards of the remainder
+        cold = NUM_NODES - n_rep
+        rps = shard.rows_per_rank(cold, world)
+        # ids of the sharded rows start at the next multiple of the shard size (one division locates any row), and
+        # the remainder is dealt round-robin over the shards (by blocks it would leave the warmest rows to shard 0)
+        first_cold = ops.peer_first_cold_id(n_rep, rps)
+        c = new_id - n_rep
+        new_id = torch.where(new_id < n_rep, new_id, first_cold + (c % world) * rps + torch.div(c, world, rounding_mode="floor"))
         heads, tails = {}, {}
         for b in BITS:
             renumbered = tables[b][0][order]
             heads[b] = renumbered[:n_rep].contiguous()
-            tails[b] = shard.PeerTable(renumbered[n_rep + lo2:n_rep + hi2].contiguous(), NUM_NODES - n_rep)
+            tails[b] = shard.PeerTable(renumbered[n_rep + rank::world].contiguous(), cold)
             del renumbered
-        # ids of the sharded rows start at the next multiple of the shard size (one division locates any row)
-        first_cold = ops.peer_first_cold_id(n_rep, shard.rows_per_rank(NUM_NODES - n_rep, world))
-        new_id = torch.where(new_id < n_rep, new_id, new_id + (first_cold - n_rep))
         blocks_hot_first = [(ip, new_id[ix]) for ip, ix in blocks]
-        remote = sum(int(((ix >= first_cold) & (((ix - first_cold) < lo2) | ((ix - first_cold) >= hi2))).sum()) for _, ix in blocks_hot_first)
+        mine_lo = first_cold + rank * rps
+        remote = sum(int(((ix >= first_cold) & ((ix < mine_lo) | (ix >= mine_lo + rps))).sum()) for _, ix in blocks_hot_first)
         out["hot_replicated_remote_edge_share"] = remote / max(sum(ix.numel() for _, ix in blocks), 1)
 
         def step_hot(i):
