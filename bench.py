@@ -11,8 +11,9 @@ the fused kernel once per code width (three launches), gathering rows straight f
 global id.  Successive steps rotate through the six blocks and L2 is flushed between steps (outside the event pair).
 
 Prints ONE JSON line (rank 0).  `value` = sampled edges aggregated per second by the whole job with all inputs
-resident in HBM; at N > 1 the table is ROW-SHARDED over the GPUs (1/N of the rows each) and the kernel reads remote
-rows over NVLink, the replicated and the NCCL all-to-all placements are timed beside it.  `e2e` = the same work called
+resident in HBM; at N > 1 the table is ROW-SHARDED over the GPUs (1/N of the rows each, plus the 5 % most often sampled
+rows on every GPU) and the kernel reads remote rows over NVLink; the purely sharded, the replicated and the NCCL
+all-to-all placements are timed beside it.  `e2e` = the same work called
 through the public module with the block's CSC in pinned host memory and the aggregated rows read back to the host
 inside the timed region.  `epoch` = GraphSAGE training (3 layers, two-level table) seconds per epoch, replicated and
 sharded table.  `--impl reference` times the reference's PyTorch CPU path (oracle/torch_cpu_path.py) on the same
