@@ -219,7 +219,8 @@ def cases(b):
 
     # ------------------------------------------------ plain aggregation, dropout, packing, compress
     if not b.wanted("spmm_csr_f32", "dropout_inplace", "sq_compress_4bit", "packbits_4bit", "unpackbits_4bit") and \
-            not b.wanted(*[f"kmeans_assign_d{d}_{m}" for d in (8, 32, 64) for m in ("l2", "cosine")]):
+            not b.wanted(*[f"kmeans_assign_d{d}_{m}" for d in (8, 32, 64) for m in ("l2", "cosine")]) and \
+            not b.wanted(*[f"sample_block_hop{h}" for h in range(3)]):
         return
     rows = n_dst
     feat = torch.randn(min(N, 1_000_000), FEAT, generator=g, device=dev)
@@ -238,7 +239,7 @@ def cases(b):
 
     # ------------------------------------------------ a block hop (sampler + relabel): one cooperative kernel against the
     #                                                  separate entry points, for the three hops of a fan-out 12,12,12 minibatch
-    if b.wanted("sample_block"):
+    if b.wanted(*[f"sample_block_hop{h}" for h in range(3)]):
         gi, gx = b.graph()
         gs = torch.Generator(device=dev)
         gs.manual_seed(1000)

@@ -48,6 +48,15 @@ def test_argument_validation_needs_no_gpu():
     rc = lib.f2c_dropout(None, 10, 1.5, 1, 0, 0, 0, None)
     assert rc == 1
     assert lib.f2c_kmeans_assign(None, None, None, 10, 0, 8, 0, None, None) == 1
+    # hot-first numbering of a sharded table: the sharded rows' ids start at the next multiple of the shard size
+    assert lib.f2c_peer_hot_first_cold_id(0, 100) == 0 and lib.f2c_peer_hot_first_cold_id(1, 100) == 100
+    assert lib.f2c_peer_hot_first_cold_id(100, 100) == 100 and lib.f2c_peer_hot_first_cold_id(101, 100) == 200
+    # ... and the replicated rows share the kernel's 16 pointer slots with the shards
+    import ctypes as C
+    fake = (C.c_void_p * 8)(*[0x1000] * 8)
+    rc = lib.f2c_sq_spmm_csr_peer_hot(0x1000, 901, fake, 8, 100, _lib.U8, None, 1, None, None, _lib.I64, None, 4, 1700, 64, 128, 4, 128, 0, None, None)
+    assert rc == 1 and b"16 slots" in lib.f2c_last_error()
+    assert lib.f2c_sample_block_workspace(0, 12, _lib.I64) == 0 and lib.f2c_sample_block_workspace(1024, 12, _lib.I64) > 1024 * 13 * 12
     # zero-sized work is a no-op, not an error
     assert lib.f2c_packbits(None, None, 0, 8, 4, None) == 0
     assert lib.f2c_sq_spmm_csr(None, _lib.U8, None, 1, None, None, _lib.I64, None, 0, 9, 64, 128, 4, 128, 0, None, None) == 0
