@@ -552,7 +552,7 @@ def tensor_relabel(tensors):
 
 
 class _PendingBlock:
-    __slots__ = ("sub_indptr", "keys", "unique", "relabelled", "n", "host", "event")
+    __slots__ = ("sub_indptr", "keys", "unique", "relabelled", "n", "host", "event", "n_edges")
 
 
 class BlockBuffers:
@@ -619,7 +619,7 @@ def sample_block_launch(indptr, indices, seeds, num_pick, rng_seed=0, rng_offset
 def sample_block_finish(pend):
     """Second half of ``sample_block``: waits for the hop (host side only) and returns its tensors."""
     pend.event.synchronize()
-    _nnz, n_unique, err, _ = pend.host.tolist()
+    pend.n_edges, n_unique, err, _ = pend.host.tolist()  # n_edges: the hop's edge count, for callers that want it on the host
     if err == 2:
         raise RuntimeError("sample_block: negative id in the graph or the seeds")
     if err != 0:

@@ -14,7 +14,8 @@
   seeds with ``csr_sampling`` + ``tensor_relabel``; yields (input_nodes, output_nodes, blocks).
 
 Blocks are dicts with ``indptr`` (CSC over the destination nodes), ``indices_local`` (positions in ``src_nodes``),
-``indices_global``, ``src_nodes``, ``dst_nodes``; destination nodes are a prefix of the source nodes.
+``indices_global``, ``src_nodes``, ``dst_nodes``, ``n_edges`` (a host integer); destination nodes are a prefix of the
+source nodes.
 """
 import torch
 from torch import nn
@@ -366,7 +367,8 @@ class GPUSamplingDataloader:
                                               buffers=None if buffers is None else buffers[hop])
             yield pending
             sub_indptr, sub_indices, unique, local = ops.sample_block_finish(pending)
-            blocks.insert(0, dict(dst_nodes=seeds, src_nodes=unique, indptr=sub_indptr, indices_global=sub_indices, indices_local=local))
+            blocks.insert(0, dict(dst_nodes=seeds, src_nodes=unique, indptr=sub_indptr, indices_global=sub_indices, indices_local=local,
+                                  n_edges=pending.n_edges))
             seeds = unique
         return seeds, output_nodes, blocks
 
