@@ -534,6 +534,7 @@ extern "C" int f2c_sq_spmm_csr_peer_hot(const void* replicated_rows, int64_t n_r
   F2C_REQUIRE(world >= 1 && world <= 8, F2C_ERR_LIMIT, "%s: 1 to 8 shards (got %d)", op, world);
   F2C_REQUIRE(rows_per_shard >= 2 && rows_per_shard < (1ll << 32), F2C_ERR_INVALID, "%s: rows_per_shard must be in [2, 2^32)", op);
   const int64_t first_cold = f2c_peer_hot_first_cold_id(n_replicated, rows_per_shard);
+  F2C_REQUIRE(n_replicated == 0 || aligned(replicated_rows, 16), F2C_ERR_INVALID, "%s: the replicated rows must be 16-byte aligned", op);
   F2C_REQUIRE(n_replicated >= 0 && (n_replicated == 0 || replicated_rows != nullptr) && first_cold / rows_per_shard + world <= 16,
               F2C_ERR_INVALID, "%s: bad replicated row range (the replicated rows and the shards share 16 slots of rows_per_shard ids)", op);
   F2C_REQUIRE(first_cold + rows_per_shard * world >= n_src, F2C_ERR_INVALID,
