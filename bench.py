@@ -307,17 +307,19 @@ def sharded_placements(args, capi, tables, blocks, extra, flush, device, rank, w
         out["sharded_peer_loads_hot_replicated_error"] = repr(e)[:300]
     try:
         st = {b: shard.ShardedTable(shards[b], NUM_NODES) for b in BITS}
-        plans = [st[BITS[0]].plan(src) for src, _ in extra]  # the id exchange happens when the block is sampled
+        # the id exchange happens when the block is sampled, and so does the renumbering of the block's indices to the
+        # order in which the fetched rows arrive (rows are then used where the exchange puts them, no un-sorting pass)
+        plans = [st[BITS[0]].plan(src) for src, _ in extra]
+        ix_arrival = [plans[i]["position"][extra[i][1]] for i in range(len(extra))]
 
         def step_a2a(i):
             ip, _ = blocks[i]
-            _, ix_local = extra[i]
             for b in BITS:
-                rows = st[b].fetch_rows(plans[i])
-                capi.sq_decompress_spmm_csr(rows, tables[b][1], ip, ix_local, b, COLUMN_SLICE, FEAT_DIM)
+                rows = st[b].fetch_rows(plans[i], ordered=False)
+                capi.sq_decompress_spmm_csr(rows, tables[b][1], ip, ix_arrival[i], b, COLUMN_SLICE, FEAT_DIM)
         out["sharded_nccl_all_to_all"] = time_steps(step_a2a, blocks, args.steps, args.warmup, flush, torch)
-        rows = st[4].fetch_rows(plans[0])
-        a = capi.sq_decompress_spmm_csr(rows, tables[4][1], blocks[0][0], extra[0][1], 4, COLUMN_SLICE, FEAT_DIM)
+        rows = st[4].fetch_rows(plans[0], ordered=False)
+        a = capi.sq_decompress_spmm_csr(rows, tables[4][1], blocks[0][0], ix_arrival[0], 4, COLUMN_SLICE, FEAT_DIM)
         ref = capi.sq_decompress_spmm_csr(tables[4][0], tables[4][1], blocks[0][0], blocks[0][1], 4, COLUMN_SLICE, FEAT_DIM)
         assert torch.equal(a, ref), "all-to-all result differs from the replicated table"
     except Exception as e:  # noqa: BLE001

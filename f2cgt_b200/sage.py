@@ -84,19 +84,24 @@ class ShardedCompressionManager:
     def for_block(self, block):
         src = block["src_nodes"]
         n_dst = block["dst_nodes"].numel()
+        # Fetched rows are used where the exchange puts them (grouped by owner): the block's 8-byte indices are renumbered
+        # to that order once instead of un-sorting every fetched table (4 .. 128 bytes per row, three tables).
         plan = self.level2.plan(src)
-        rows = self.level2.fetch_rows(plan)
-        dst_local = torch.arange(n_dst, dtype=src.dtype, device=src.device)
+        arrival = plan["position"]
+        rows = self.level2.fetch_rows(plan, ordered=False)
+        dst_local = arrival[:n_dst].contiguous()
+        neighbours = arrival[block["indices_local"]]
         if not self.is_two_level:
             local = CompressionManager(self.feat_dim, self.methods, self.configs, self.codebooks, [rows])
-            return local, block["indices_local"], dst_local
-        slots = self.slot.fetch_rows(plan).reshape(-1)  # same ids, same row partition: the plan is shared
+            return local, neighbours, dst_local
+        slots = self.slot.fetch_rows(plan, ordered=False).reshape(-1)  # same ids, same row partition: the plan is shared
         hot_pos = (slots >= 0).nonzero().reshape(-1)
-        hot_rows = self.hot.fetch(slots[hot_pos].to(src.dtype))
+        hot_plan = self.hot.plan(slots[hot_pos].to(src.dtype))
+        hot_rows = self.hot.fetch_rows(hot_plan, ordered=False)
         local_slot = torch.full_like(slots, -1)
-        local_slot[hot_pos] = torch.arange(hot_pos.numel(), dtype=slots.dtype, device=slots.device)
+        local_slot[hot_pos] = hot_plan["position"].to(slots.dtype)
         local = CompressionManager(self.feat_dim, self.methods, self.configs, self.codebooks, [hot_rows, rows], local_slot)
-        return local, block["indices_local"], dst_local
+        return local, neighbours, dst_local
 
 
 class PeerCompressionManager:

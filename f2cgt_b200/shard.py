@@ -102,12 +102,20 @@ class ShardedTable:
             dist.all_gather_object(all_counts, send_counts, group=self.group)
             recv_counts = [all_counts[r][self.rank] for r in range(self.world)]
         wanted = _exchange(sorted_ids, send_counts, recv_counts, self.group)  # ids other ranks want from this shard
-        return dict(order=order, send_counts=send_counts, recv_counts=recv_counts, local_index=wanted - self.lo)
+        # position[j] = where the row of ids[j] lands in the buffer the exchange fills (rows arrive grouped by owner)
+        position = torch.empty_like(order)
+        position[order] = torch.arange(order.numel(), dtype=order.dtype, device=order.device)
+        return dict(order=order, position=position, send_counts=send_counts, recv_counts=recv_counts, local_index=wanted - self.lo)
 
-    def fetch_rows(self, plan):
-        """Owner-side gather + row exchange; returns the rows in the order of the ids given to ``plan``."""
+    def fetch_rows(self, plan, ordered=True):
+        """Owner-side gather + row exchange.  ``ordered=True``: the rows in the order of the ids given to ``plan``.
+        ``ordered=False``: the rows as they arrive (grouped by owner) - the row of ``ids[j]`` is row ``plan["position"][j]``;
+        a caller that renumbers its block indices through ``position`` once (indices are 8 bytes, rows 16 .. 128) saves a
+        pass over every fetched table."""
         rows = self.local.index_select(0, plan["local_index"])
         got = _exchange(rows, plan["recv_counts"], plan["send_counts"], self.group)
+        if not ordered:
+            return got
         out = torch.empty_like(got)
         out[plan["order"]] = got
         return out

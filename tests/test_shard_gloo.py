@@ -32,6 +32,10 @@ def _worker(rank, world, port, n_rows, q):
             ids = torch.randint(0, n_rows, (n_ids,), generator=g2)  # duplicates and any order
             rows = st.fetch(ids)
             assert rows.shape == (n_ids, 16) and torch.equal(rows, table[ids])
+            # the same rows as they arrive (grouped by owner), found through the plan's positions
+            plan = st.plan(ids)
+            arrived = st.fetch_rows(plan, ordered=False)
+            assert arrived.shape == (n_ids, 16) and torch.equal(arrived[plan["position"]], table[ids])
         # every id on one remote rank, and an id outside the table
         other = (rank + 1) % world
         olo, ohi = shard.shard_bounds(n_rows, world, other)
@@ -94,13 +98,24 @@ def _manager_worker(rank, world, port, q):
         g2 = torch.Generator().manual_seed(50 + rank)  # a different block per rank
         for n_src in (700, 1):
             src = torch.randperm(n, generator=g2)[:n_src]
-            block = dict(src_nodes=src, dst_nodes=src[:min(50, n_src)], indices_local=torch.zeros(3, dtype=torch.int64))
+            n_dst = min(50, n_src)
+            ix = torch.randint(0, n_src, (40,), generator=g2)
+            block = dict(src_nodes=src, dst_nodes=src[:n_dst], indices_local=ix)
             local, neigh, dst = parts.for_block(block)
-            assert neigh is block["indices_local"] and torch.equal(dst, torch.arange(block["dst_nodes"].numel()))
-            assert torch.equal(local.tables[1], vq[src])
-            want_hot = slot[src] >= 0
+            # fetched rows stay where the exchange put them; the block's indices and its destination ids are renumbered
+            # to that order, so looking a node up through them finds the node's own rows
+            assert torch.equal(local.tables[1][neigh], vq[src[ix]]) and torch.equal(local.tables[1][dst], vq[src[:n_dst]])
+            assert sorted(dst.tolist() + [-1])[1:] == sorted(set(dst.tolist()))  # distinct positions
+            order = torch.empty(n_src, dtype=torch.int64)   # arrival position -> block-local id
+            for probe in (neigh, dst):
+                assert int(probe.min()) >= 0 and int(probe.max()) < n_src
+            full_pos = parts.level2.plan(src)["position"]   # (collective: every rank calls it)
+            order[full_pos] = torch.arange(n_src)
+            arrived = src[order]
+            assert torch.equal(local.tables[1], vq[arrived])
+            want_hot = slot[arrived] >= 0
             assert torch.equal(local.slot >= 0, want_hot)
-            assert torch.equal(local.tables[0][local.slot[want_hot].long()], hot_rows[slot[src][want_hot].long()])
+            assert torch.equal(local.tables[0][local.slot[want_hot].long()], hot_rows[slot[arrived][want_hot].long()])
             assert local.tables[0].shape[0] == int(want_hot.sum())
         q.put((rank, "ok"))
     except Exception as e:  # noqa: BLE001
