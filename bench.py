@@ -532,6 +532,8 @@ def run_ours(args):
         from f2cgt_b200 import train_graphsage
         del flush
         torch.cuda.empty_cache()
+        # every rank on its own share of the node's CPUs from here on (the training threads start below and inherit it)
+        pinned = train_graphsage.pin_rank_cpus(local_rank, int(os.environ.get("LOCAL_WORLD_SIZE", world)))
         what = {
             "small": ("2,449,029 nodes, mean degree 50", "two-level: hot 5 % SQ 8 bits + VQ 4 x 32 (ratio 128), D = 128, 172 classes, 122,880 "
                       "training ids split over the ranks, batch 1024, fan-out 12,12,12, dropout 0.5"),
@@ -550,7 +552,8 @@ def run_ours(args):
                 epoch.append({"preset": preset, "table": table, "ms_per_step": rec["ms_per_step"], "s_per_epoch": rec["value"],
                               "steps": rec["steps_per_epoch_per_gpu"], "timed_steps": rec["timed_steps_per_gpu"],
                               "breakdown_ms": rec["breakdown_ms"], "precision": rec["precision"],
-                              "blocks_built_ahead": rec["blocks_built_ahead"], "graph": what[preset][0], "codecs": what[preset][1]})
+                              "blocks_built_ahead": rec["blocks_built_ahead"], "cpus_per_rank": len(pinned) if pinned else os.cpu_count(),
+                              "graph": what[preset][0], "codecs": what[preset][1]})
             except Exception as e:  # noqa: BLE001
                 epoch.append({"preset": preset, "table": table, "error": repr(e)[:300]})
             torch.cuda.empty_cache()
