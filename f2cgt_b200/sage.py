@@ -74,19 +74,27 @@ class ShardedCompressionManager:
         from . import shard
         self.feat_dim, self.methods, self.configs, self.codebooks = int(feat_dim), list(methods), list(configs), list(codebooks)
         self.is_two_level = len(self.methods) >= 2
-        self.level2 = shard.ShardedTable(local_tables[-1], table_rows[-1], group)
-        if self.is_two_level:
+        if not self.is_two_level:
+            self.level2 = shard.ShardedTable(local_tables[-1], table_rows[-1], group)
+        else:
             if self.methods != ["sq", "vq"] or local_slot is None:
                 raise ValueError("two-level compression is hot SQ rows over a VQ table, with a slot array")
             self.hot = shard.ShardedTable(local_tables[0], table_rows[0], group)
-            self.slot = shard.ShardedTable(local_slot.reshape(-1, 1), table_rows[-1], group)
+            codes = local_tables[-1]
+            self.code_bytes = codes.shape[1] * codes.element_size()
+            # a node's VQ code row and its slot travel as ONE row of code_bytes + 4 bytes: one gather and one exchange per
+            # minibatch instead of two
+            packed = torch.cat([codes.contiguous().view(torch.uint8).reshape(codes.shape[0], self.code_bytes),
+                                local_slot.to(torch.int32).contiguous().view(torch.uint8).reshape(-1, 4)], dim=1)
+            self.level2 = shard.ShardedTable(packed, table_rows[-1], group)
+            self.code_dtype, self.code_width = codes.dtype, codes.shape[1]
 
     def for_block(self, block):
         src = block["src_nodes"]
         n_dst = block["dst_nodes"].numel()
         # Fetched rows are used where the exchange puts them (grouped by owner): the block's 8-byte indices are renumbered
         # to that order once instead of un-sorting every fetched table (4 .. 128 bytes per row, three tables).
-        plan = self.level2.plan(src)
+        plan = self.level2.plan(src, check=False)  # ids straight from the sampler / slots from our own table
         arrival = plan["position"]
         rows = self.level2.fetch_rows(plan, ordered=False)
         dst_local = arrival[:n_dst].contiguous()
@@ -94,9 +102,10 @@ class ShardedCompressionManager:
         if not self.is_two_level:
             local = CompressionManager(self.feat_dim, self.methods, self.configs, self.codebooks, [rows])
             return local, neighbours, dst_local
-        slots = self.slot.fetch_rows(plan, ordered=False).reshape(-1)  # same ids, same row partition: the plan is shared
+        slots = rows[:, self.code_bytes:].contiguous().view(torch.int32).reshape(-1)
+        rows = rows[:, :self.code_bytes].contiguous().view(self.code_dtype).reshape(-1, self.code_width)
         hot_pos = (slots >= 0).nonzero().reshape(-1)
-        hot_plan = self.hot.plan(slots[hot_pos].to(src.dtype))
+        hot_plan = self.hot.plan(slots[hot_pos].to(src.dtype), check=False)
         hot_rows = self.hot.fetch_rows(hot_plan, ordered=False)
         local_slot = torch.full_like(slots, -1)
         local_slot[hot_pos] = hot_plan["position"].to(slots.dtype)

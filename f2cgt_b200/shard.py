@@ -83,10 +83,11 @@ class ShardedTable:
         self.local = local_rows
         self.lo = lo
 
-    def plan(self, ids):
+    def plan(self, ids, check=True):
         """Everything about a fetch that depends only on the ids (can be computed when the block is sampled):
-        bucketing, the count exchange and the id exchange.  Returns a dict consumed by ``fetch_rows``."""
-        if ids.numel():
+        bucketing, the count exchange and the id exchange.  Returns a dict consumed by ``fetch_rows``.
+        ``check=False`` skips the range test of the ids and its host read (ids that come straight from the sampler)."""
+        if check and ids.numel():
             lo_hi = torch.stack(torch.aminmax(ids)).tolist()  # one host read for both bounds
             if lo_hi[0] < 0 or lo_hi[1] >= self.n_rows:
                 raise IndexError("row id outside the table")
