@@ -198,3 +198,25 @@ def test_loader_builds_the_same_minibatches_ahead_or_in_step(capi):
         assert len(other) == len(base)
         for a, b in zip(base, other):
             assert all(torch.equal(x, y) for x, y in zip(a, b))
+
+
+def test_direct_fused_adam_equals_torch_adam(capi):
+    """The trainer's optimizer calls the fused Adam kernel itself; three steps give torch.optim.Adam(fused=True)'s weights."""
+    from f2cgt_b200 import train_graphsage as tg
+    if not tg.DirectFusedAdam.available():
+        pytest.skip("this torch does not expose the fused Adam kernel")
+    torch.manual_seed(0)
+    a = [torch.randn(64, 32, device="cuda", requires_grad=True), torch.randn(64, device="cuda", requires_grad=True)]
+    b = [t.detach().clone().requires_grad_(True) for t in a]
+    mine, ref = tg.DirectFusedAdam(a, lr=0.003), torch.optim.Adam(b, lr=0.003, fused=True)
+    for step in range(3):
+        g = [torch.randn_like(t) for t in a]
+        for t, u, gg in zip(a, b, g):
+            t.grad, u.grad = gg.clone(), gg.clone()
+        mine.step()
+        ref.step()
+        mine.lr *= 0.978
+        for grp in ref.param_groups:
+            grp["lr"] *= 0.978
+    for t, u in zip(a, b):
+        assert torch.equal(t, u)
