@@ -273,7 +273,7 @@ def sharded_placements(args, capi, tables, blocks, extra, flush, device, rank, w
         order = torch.argsort(deg, descending=True, stable=True)          # new id -> old id
         new_id = torch.empty_like(order)
         new_id[order] = torch.arange(NUM_NODES, device=device)            # old id -> new id
-        n_rep = int(NUM_NODES * HOT_REPLICATED)
+        n_rep = int(NUM_NODES * args.hot_replicated)
         n_rep += (NUM_NODES - n_rep) % world                               # equal shards of the remainder
         cold = NUM_NODES - n_rep
         rps = shard.rows_per_rank(cold, world)
@@ -510,8 +510,8 @@ def run_ours(args):
         # The headline at N > 1 is a placement in which the table is really partitioned: every GPU holds 1/N of the rows
         # and, in the first choice, the HOT_REPLICATED hottest rows besides.
         what = {
-            "sharded_peer_loads_hot_replicated": f"row-sharded over the GPUs with the {HOT_REPLICATED:.0%} most often sampled rows on every GPU "
-                                                 f"({HOT_REPLICATED:.0%} + {1 - HOT_REPLICATED:.0%} / N of the table per GPU); the fused kernel reads "
+            "sharded_peer_loads_hot_replicated": f"row-sharded over the GPUs with the {args.hot_replicated:.0%} most often sampled rows on every GPU "
+                                                 f"({args.hot_replicated:.0%} + {1 - args.hot_replicated:.0%} / N of the table per GPU); the fused kernel reads "
                                                  "the remaining remote rows over NVLink (peer mappings, no collective)",
             "sharded_peer_loads": "row-sharded over the GPUs (1/N of the table per GPU), the fused kernel reads remote rows over NVLink "
                                   "(peer mappings, no collective)",
@@ -753,6 +753,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-epoch", action="store_true", help="skip the GraphSAGE epoch records")
+    ap.add_argument("--hot-replicated", type=float, default=HOT_REPLICATED,
+                    help="N > 1: share of the rows (the most often sampled ones) kept on every GPU beside its shard of the rest")
     args = ap.parse_args()
     # Libraries (NCCL's version banner, for one) write to file descriptor 1; the JSON line must be the only thing
     # on stdout, so everything else is sent to stderr and the line is written to the saved descriptor.
