@@ -66,6 +66,17 @@ def _worker(rank, world, port, q):
                 assert torch.equal(got, want), f"peer loads ({kernel} kernel) differ at {bits} bits"
             print(f"rank {rank} bits {bits}: peer loads ok", file=sys.stderr, flush=True)
             peers.close()  # collective: nobody frees its shard while a peer may still read it
+            # 4. the first 1,500 rows on every GPU, the rest sharded (its ids start at the next multiple of the shard size)
+            n_rep = 1500
+            cold = n_rows - n_rep
+            clo, chi = shard.shard_bounds(cold, world, rank)
+            tail = shard.PeerTable(table[n_rep + clo:n_rep + chi].clone(), cold)
+            first_cold = ops.peer_first_cold_id(n_rep, tail.rpr)
+            ids = torch.where(indices < n_rep, indices, indices + (first_cold - n_rep))
+            got = ops.sq_decompress_spmm_csr_peer(tail, cb, indptr, ids, bits, D, D, replicated=table[:n_rep].clone())
+            torch.cuda.synchronize()
+            assert torch.equal(got, want), f"peer loads with replicated leading rows differ at {bits} bits"
+            tail.close()
         # a table too small to give every rank rows: the last shard is short or empty
         for tiny in (3, 2):
             g = torch.Generator().manual_seed(tiny)
