@@ -182,6 +182,43 @@ def _bucket(n):
     return (n + step - 1) // step * step
 
 
+_PRODUCT_DTYPE = None  # None: the tensors' own dtype (fp32, or tf32 on the tensor cores when torch allows it)
+
+
+class products_in:
+    """``with products_in(torch.bfloat16):`` - the layers' matrix products round their operands to that dtype (storage,
+    aggregation, bias and gradients stay fp32): the bf16 / fp32 mixed precision some configurations ask for.  It costs a
+    cast kernel per operand, so it is slower than the default in a step that is bound by launches."""
+
+    def __init__(self, dtype):
+        self.dtype = dtype
+
+    def __enter__(self):
+        global _PRODUCT_DTYPE
+        self.before, _PRODUCT_DTYPE = _PRODUCT_DTYPE, self.dtype
+
+    def __exit__(self, *exc):
+        global _PRODUCT_DTYPE
+        _PRODUCT_DTYPE = self.before
+
+
+def _mm(a, b):
+    if _PRODUCT_DTYPE is None:
+        return torch.mm(a, b)
+    return torch.mm(a.to(_PRODUCT_DTYPE), b.to(_PRODUCT_DTYPE)).float()
+
+
+def _affine(bias, a, b):
+    if _PRODUCT_DTYPE is None:
+        return torch.addmm(bias, a, b) if bias is not None else torch.mm(a, b)
+    y = _mm(a, b)
+    return y.add_(bias) if bias is not None else y
+
+
+def _addmm_(y, a, b):
+    return y.addmm_(a, b) if _PRODUCT_DTYPE is None else y.add_(_mm(a, b))
+
+
 class _SageProduct(torch.autograd.Function):
     """y = x_self @ w_self^T + x_neigh @ w_neigh^T + bias for inputs that need no gradient (the decoded first layer)."""
 
@@ -189,8 +226,7 @@ class _SageProduct(torch.autograd.Function):
     def forward(ctx, x_self, x_neigh, w_self, w_neigh, bias):
         ctx.save_for_backward(x_self, x_neigh)
         ctx.has_bias = bias is not None
-        y = torch.addmm(bias, x_self, w_self.t()) if bias is not None else torch.mm(x_self, w_self.t())
-        return y.addmm_(x_neigh, w_neigh.t())
+        return _addmm_(_affine(bias, x_self, w_self.t()), x_neigh, w_neigh.t())
 
     @staticmethod
     def backward(ctx, dy):
@@ -198,7 +234,7 @@ class _SageProduct(torch.autograd.Function):
         dy = dy.contiguous()
         dyt = dy.t()
         db = torch.mm(_ones_row(dy.shape[0], dy), dy).reshape(-1) if ctx.has_bias else None
-        return None, None, torch.mm(dyt, x_self), torch.mm(dyt, x_neigh), db
+        return None, None, _mm(dyt, x_self), _mm(dyt, x_neigh), db
 
 
 class _SageLayer(torch.autograd.Function):
@@ -210,8 +246,7 @@ class _SageLayer(torch.autograd.Function):
     def forward(ctx, h, indptr, indices, n_dst, m, w_self, w_neigh, bias):
         neigh = ops.spmm_csr(h, indptr, indices, out_rows=m)
         h_self = h[:m]
-        y = torch.addmm(bias, h_self, w_self.t()) if bias is not None else torch.mm(h_self, w_self.t())
-        y.addmm_(neigh, w_neigh.t())
+        y = _addmm_(_affine(bias, h_self, w_self.t()), neigh, w_neigh.t())
         ctx.save_for_backward(h, neigh, indptr, indices, w_self, w_neigh)
         ctx.n_dst, ctx.m, ctx.has_bias = n_dst, m, bias is not None
         return y
@@ -222,15 +257,15 @@ class _SageLayer(torch.autograd.Function):
         n_dst, m = ctx.n_dst, ctx.m
         dy = dy.contiguous()
         dyt = dy.t()
-        dw_self = torch.mm(dyt, h[:m])
-        dw_neigh = torch.mm(dyt, neigh)
+        dw_self = _mm(dyt, h[:m])
+        dw_neigh = _mm(dyt, neigh)
         db = torch.mm(_ones_row(m, dy), dy).reshape(-1) if ctx.has_bias else None
         dh = None
         if ctx.needs_input_grad[0]:
-            d_neigh = torch.mm(dy, w_neigh)
+            d_neigh = _mm(dy, w_neigh)
             # one scatter kernel (vector reductions into the source rows) instead of building the transposed block
             dh = ops.spmm_csr_backward(d_neigh[:n_dst], indptr, indices, h.shape[0])
-            dh[:m].addmm_(dy, w_self)
+            _addmm_(dh[:m], dy, w_self)
         return dh, None, None, None, None, dw_self, dw_neigh, db
 
 

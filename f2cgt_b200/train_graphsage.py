@@ -146,9 +146,11 @@ def train(preset="small", table="replicated", rank=0, world=1, local_rank=0, epo
     loader = sage.GPUSamplingDataloader(indptr, indices, train_ids, batch_size, cfg["fan_out"], rank, world, shuffle=True, ahead=ahead)
     # The reference trains in fp32 (examples/train_graphsage_nodeclass.py has no autocast).  "tf32": fp32 storage, matrix
     # products on the tensor cores with tf32 inputs and fp32 accumulation - no cast kernels at all, which matters because
-    # the step is bound by the host's launch rate, not by the GPU.  "fp32": plain.
-    if precision not in ("tf32", "fp32"):
-        raise ValueError("precision must be tf32 or fp32")
+    # the step is bound by the host's launch rate, not by the GPU.  "fp32": plain.  "bf16": the layers' products round their
+    # operands to bf16 (sage.products_in), everything else stays fp32 - the mixed precision the two-level configuration names.
+    if precision not in ("tf32", "fp32", "bf16"):
+        raise ValueError("precision must be tf32, fp32 or bf16")
+    product_dtype = torch.bfloat16 if precision == "bf16" else None
     tf32_before = torch.backends.cuda.matmul.allow_tf32
     torch.backends.cuda.matmul.allow_tf32 = precision == "tf32"
     steps = torch.tensor([len(loader)], device=device)
@@ -181,16 +183,19 @@ def train(preset="small", table="replicated", rank=0, world=1, local_rank=0, epo
             ev[1].record()
             blocks[0]["first_layer_input"] = cm.for_block(blocks[0])  # sharded table: the row exchange of this minibatch
             ev[2].record()
-            pred = net(blocks)
+            with sage.products_in(product_dtype):
+                pred = net(blocks)
             loss = F.cross_entropy(pred, y)
             ev[3].record()
             loader.poke()  # next minibatch: one hop further on its own stream, if that needs no waiting
             if flat_grad is None:
                 optimizer.zero_grad(set_to_none=True)
-                loss.backward()
+                with sage.products_in(product_dtype):
+                    loss.backward()
             else:
                 flat_grad.zero_()  # the views stay attached to the parameters
-                loss.backward()
+                with sage.products_in(product_dtype):
+                    loss.backward()
                 dist.all_reduce(flat_grad, op=dist.ReduceOp.AVG)  # NCCL divides inside the collective: no scale kernel
             ev[4].record()
             loader.poke()
@@ -271,8 +276,8 @@ def main():
     ap.add_argument("--index-dtype", default="int64", choices=["int32", "int64"])
     ap.add_argument("--max-steps", type=int, default=0, help="cut every epoch after this many steps (0 = whole epoch)")
     ap.add_argument("--min-timed-steps", type=int, default=0, help="run enough epochs to time at least this many steps")
-    ap.add_argument("--precision", default="tf32", choices=["tf32", "fp32"],
-                    help="tf32: fp32 storage, tf32 tensor-core products (default); fp32: plain")
+    ap.add_argument("--precision", default="tf32", choices=["tf32", "fp32", "bf16"],
+                    help="tf32: fp32 storage, tf32 tensor-core products (default); fp32: plain; bf16: product operands in bf16")
     ap.add_argument("--no-pin", action="store_true", help="do not give every rank its own share of the node's CPUs")
     ap.add_argument("--no-ahead", action="store_true", help="build every minibatch inside its step instead of one step early on a side stream")
     ap.add_argument("--table", default="replicated", choices=["replicated", "sharded", "sharded_peer"],

@@ -220,3 +220,31 @@ def test_direct_fused_adam_equals_torch_adam(capi):
             grp["lr"] *= 0.978
     for t, u in zip(a, b):
         assert torch.equal(t, u)
+
+
+def test_bf16_product_operands_stay_close_to_fp32(capi):
+    """``sage.products_in(torch.bfloat16)``: same network, product operands rounded to bf16, fp32 everywhere else - output
+    and gradients within bf16 rounding of the fp32 run, all finite."""
+    from f2cgt_b200 import sage
+    n, D, indptr, indices, cm, full, g = _two_level_setup()
+    torch.manual_seed(0)
+    model = sage.SAGE(D, 64, 10, 3, 0.0, cm).cuda()
+    seeds = torch.randperm(n, generator=g, device="cuda")[:256]
+    loader = sage.GPUSamplingDataloader(indptr, indices, seeds, 256, (5, 4, 3), shuffle=False)
+    _, _, blocks = next(iter(loader))
+    y = torch.randint(0, 10, (256,), generator=g, device="cuda")
+    want = model(blocks)
+    torch.nn.functional.cross_entropy(want, y).backward()
+    want_grads = [p.grad.clone() for p in model.parameters()]
+    model.zero_grad(set_to_none=True)
+    with sage.products_in(torch.bfloat16):
+        got = model(blocks)
+        torch.nn.functional.cross_entropy(got, y).backward()
+    assert got.dtype == torch.float32 and torch.isfinite(got).all()
+    # bf16 keeps 8 bits of mantissa: ~0.4 % per operand, through three layers of 64- to 128-term dot products
+    scale = float(want.detach().abs().max())
+    assert float((got.detach() - want.detach()).abs().max()) < 0.05 * scale
+    for a, p in zip(want_grads, model.parameters()):
+        assert p.grad.dtype == torch.float32 and torch.isfinite(p.grad).all()
+        assert float((p.grad - a).abs().max()) < 0.15 * float(a.abs().max()) + 1e-6
+    assert sage._PRODUCT_DTYPE is None  # the context manager restored the default
